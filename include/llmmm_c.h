@@ -1,0 +1,129 @@
+/* C ABI of the B200 (sm_100a) GEMM library: FP16/BF16 GEMM with fp32
+ * accumulation, FP8 e4m3 blockwise-quantised GEMM with the output's 1x128
+ * re-quantisation fused in, and the blockwise quantisers that prepare its
+ * operands.
+ *
+ * Every entry point is the C form of a host launcher of the reference project
+ * (file:line given per function, paths relative to the reference root) and
+ * keeps its conventions:
+ *   - all pointers are device pointers owned by the caller; nothing is
+ *     allocated, C is fully overwritten;
+ *   - the work is enqueued on `stream` and the call returns without
+ *     synchronising;
+ *   - matrices are dense row-major with no padding.
+ * Where the reference launchers throw std::runtime_error, these return a
+ * status code; the C++ wrappers under llmmm_b200/src/mm re-throw it.
+ *
+ * There is no CPU path: on a machine without an sm_100 GPU every compute
+ * entry point returns LLMMM_ERR_UNSUPPORTED.
+ */
+#ifndef LLMMM_C_H
+#define LLMMM_C_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* cudaStream_t without requiring the CUDA headers. */
+typedef struct CUstream_st* llmmm_stream_t;
+
+enum {
+  LLMMM_OK              = 0,
+  LLMMM_ERR_SHAPE       = 1, /* shape / alignment not supported ("M or N or K are not aligned.") */
+  LLMMM_ERR_UNSUPPORTED = 2, /* dtype or device not supported ("T is not supported.") */
+  LLMMM_ERR_CUDA        = 3, /* a CUDA runtime / driver call failed; see llmmm_last_error() */
+  LLMMM_ERR_DEVICE_WAIT = 4  /* a bounded device-side wait ran out (llmmm_check_status) */
+};
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* llmmm_last_error(void);
+
+/* Library version string. */
+const char* llmmm_version(void);
+
+/* C[M,N] = A[M,K] * B[K,N]; A, B, C row-major half; fp32 accumulation, one
+ * round-to-nearest conversion of the result.
+ * Replaces LLMMM::fp16_mm<half> (src/mm/fp16/mm.h:9-10, launcher
+ * src/mm/fp16/mm.cu:7-42).  The reference accepts only M%256 == N%256 == 0,
+ * K%16 == 0; this library accepts any M >= 1 with N%8 == 0 and K%8 == 0
+ * (16-byte row pitch) and 16-byte aligned base pointers. */
+int llmmm_fp16_mm_f16(const void* A, const void* B, void* C, int M, int N, int K, llmmm_stream_t stream);
+
+/* Same for __nv_bfloat16: LLMMM::fp16_mm<__nv_bfloat16> (src/mm/fp16/mm.cu:45-46). */
+int llmmm_fp16_mm_bf16(const void* A, const void* B, void* C, int M, int N, int K, llmmm_stream_t stream);
+
+/* FP8 e4m3 blockwise GEMM with fused 1x128 output quantisation.
+ *   A            [M,K]          e4m3, row-major (K contiguous)
+ *   A_scale_t    [(K/128), M]   fp32, one scale per row per 128-wide K group
+ *   B_t          [N,K]          e4m3, row-major (K contiguous) = B transposed
+ *   B_scale_t    [(N/128),(K/128)] fp32, one scale per 128x128 block
+ *   C            [M,N]          e4m3 out
+ *   C_scale_t    [(N/128), M]   fp32 out, one scale per row per 128-wide N group
+ * acc[m,n] = sum_kb ( sum_{k in kb} A*B ) * (A_scale_t[kb,m] * B_scale_t[n/128,kb]),
+ * amax over each 1x128 group of acc, C_scale = amax/448, C = e4m3(acc * (448/amax)).
+ * An all-zero group yields scale 0 and zeros (the reference yields NaN there).
+ * Replaces the launchers generated at examples/005.fp8.mm.cu:2466-2577, e.g.
+ * fp8_gemm_blockwise_quant_A_1x128__B_128x128__C_1x128__output_fp8__opt_reg
+ * (same argument order).  Requires N%128 == 0, K%128 == 0; any M >= 1
+ * (the reference requires M%128 == 0).  M <= 64 takes the split-K path and
+ * needs a workspace (see llmmm_set_workspace). */
+int llmmm_fp8_blockwise_mm_e4m3out(const void*    A,
+                                   const float*   A_scale_t,
+                                   const void*    B_t,
+                                   const float*   B_scale_t,
+                                   void*          C,
+                                   float*         C_scale_t,
+                                   int            M,
+                                   int            N,
+                                   int            K,
+                                   llmmm_stream_t stream);
+
+/* Same product with the fp32 accumulator written out unquantised, C [M,N] fp32.
+ * Replaces fp8_gemm_blockwise_quant_A_1x128__B_128x128__output_fp32
+ * (examples/005.fp8.mm.cu:217-246). */
+int llmmm_fp8_blockwise_mm_f32out(const void*    A,
+                                  const float*   A_scale_t,
+                                  const void*    B_t,
+                                  const float*   B_scale_t,
+                                  float*         C,
+                                  int            M,
+                                  int            N,
+                                  int            K,
+                                  llmmm_stream_t stream);
+
+/* Activation quantiser: x [M,K] fp32 -> q [M,K] e4m3, scale [(K/128), M] fp32.
+ * Per row and 128-wide K group: s = amax/448, q = e4m3(s ? x/s : 0).
+ * Replaces fp8_blockwise_symmetric_quantization<1,128,true>
+ * (examples/005.fp8.mm.cu:439-500, launcher :547-563).  Requires K%128 == 0. */
+int llmmm_fp8_quant_1x128(const float* x, void* q, float* scale, int M, int K, llmmm_stream_t stream);
+
+/* Weight quantiser: x [rows,cols] fp32 -> q [rows,cols] e4m3,
+ * scale [(rows/128),(cols/128)] fp32, one scale per 128x128 block.
+ * Replaces fp8_blockwise_symmetric_quantization<128,128,false>
+ * (examples/005.fp8.mm.cu:503-544).  Requires rows%128 == 0, cols%128 == 0. */
+int llmmm_fp8_quant_128x128(const float* x, void* q, float* scale, int rows, int cols, llmmm_stream_t stream);
+
+/* Split-K scratch for the decode-sized (M <= 64) FP8 path.  The reference has
+ * no split-K (README.md:22 lists it as to do) and its launchers allocate
+ * nothing, so the scratch is caller-owned: bytes needed for a given problem,
+ * and registration of a device buffer for the current device.  The buffer is
+ * shared by all later calls on that device; calls that may overlap on the GPU
+ * need separate streams AND separate buffers, or must be serialised. */
+size_t llmmm_fp8_workspace_bytes(int M, int N, int K);
+int    llmmm_set_workspace(void* device_ptr, size_t bytes);
+
+/* Reads the device status word of the current device after synchronising
+ * `stream`.  Returns LLMMM_OK, or LLMMM_ERR_DEVICE_WAIT with the code of the
+ * wait that ran out in llmmm_last_error(); the word is cleared. */
+int llmmm_check_status(llmmm_stream_t stream);
+
+/* Number of kernels launched by this library in the calling process. */
+uint64_t llmmm_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLMMM_C_H */

@@ -1,0 +1,151 @@
+"""ctypes binding of the C ABI declared in include/llmmm_c.h.
+
+The functions here mirror the reference's host launchers (argument order and
+error behaviour): `fp16_mm` is LLMMM::fp16_mm<T> (src/mm/fp16/mm.h:9-10), the
+FP8 functions are the launchers of examples/005.fp8.mm.cu:217-246, 547-563 and
+2466-2577.  A non-zero status from the library is raised as RuntimeError, the
+Python counterpart of the reference's std::runtime_error.
+
+torch is used only to hold device memory and to name the current stream.
+There is no fallback: if the shared library is missing, loading raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent / "libllmmm_b200.so"
+_lib = None
+
+_vp = ctypes.c_void_p
+_i = ctypes.c_int
+
+
+def lib() -> ctypes.CDLL:
+    """Loads libllmmm_b200.so (built in-tree by llmmm_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise RuntimeError(
+                f"{_LIB_PATH} is missing: build it with `python -m llmmm_b200.build`; there is no fallback path")
+        L = ctypes.CDLL(str(_LIB_PATH))
+        L.llmmm_last_error.restype = ctypes.c_char_p
+        L.llmmm_version.restype = ctypes.c_char_p
+        L.llmmm_launch_count.restype = ctypes.c_uint64
+        L.llmmm_fp8_workspace_bytes.restype = ctypes.c_size_t
+        L.llmmm_fp8_workspace_bytes.argtypes = [_i, _i, _i]
+        L.llmmm_set_workspace.argtypes = [_vp, ctypes.c_size_t]
+        L.llmmm_check_status.argtypes = [_vp]
+        for name in ("llmmm_fp16_mm_f16", "llmmm_fp16_mm_bf16"):
+            getattr(L, name).argtypes = [_vp, _vp, _vp, _i, _i, _i, _vp]
+        L.llmmm_fp8_blockwise_mm_e4m3out.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
+        L.llmmm_fp8_blockwise_mm_f32out.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
+        L.llmmm_fp8_quant_1x128.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
+        L.llmmm_fp8_quant_128x128.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
+        _lib = L
+    return _lib
+
+
+EXPORTED_SYMBOLS = (
+    "llmmm_last_error", "llmmm_version", "llmmm_fp16_mm_f16", "llmmm_fp16_mm_bf16",
+    "llmmm_fp8_blockwise_mm_e4m3out", "llmmm_fp8_blockwise_mm_f32out", "llmmm_fp8_quant_1x128",
+    "llmmm_fp8_quant_128x128", "llmmm_fp8_workspace_bytes", "llmmm_set_workspace", "llmmm_check_status",
+    "llmmm_launch_count",
+)
+
+
+def _check(status: int) -> None:
+    if status != 0:
+        raise RuntimeError(f"llmmm status {status}: {lib().llmmm_last_error().decode()}")
+
+
+def _stream(stream) -> int:
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    return stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+
+
+def _dev(t: torch.Tensor, dtype=None) -> int:
+    if not t.is_cuda or not t.is_contiguous():
+        raise RuntimeError("expected a contiguous CUDA tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError(f"expected dtype {dtype}, got {t.dtype}")
+    return t.data_ptr()
+
+
+def launch_count() -> int:
+    return int(lib().llmmm_launch_count())
+
+
+def check_status(stream=None) -> None:
+    _check(lib().llmmm_check_status(_stream(stream)))
+
+
+def fp16_mm(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, M: int, N: int, K: int, stream=None) -> None:
+    """C[M,N] = A[M,K] @ B[K,N] for half / bfloat16 (LLMMM::fp16_mm<T>)."""
+    if A.dtype == torch.float16:
+        fn = lib().llmmm_fp16_mm_f16
+    elif A.dtype == torch.bfloat16:
+        fn = lib().llmmm_fp16_mm_bf16
+    else:
+        raise RuntimeError("T is not supported.")
+    with torch.cuda.device(A.device):
+        _check(fn(_dev(A), _dev(B, A.dtype), _dev(C, A.dtype), M, N, K, _stream(stream)))
+
+
+def fp8_blockwise_mm(A_q, A_s, B_q, B_s, C_q, C_s, M: int, N: int, K: int, stream=None) -> None:
+    """FP8 blockwise GEMM, e4m3 output with fused 1x128 scales
+    (fp8_gemm_blockwise_quant_A_1x128__B_128x128__C_1x128__output_fp8*)."""
+    with torch.cuda.device(A_q.device):
+        _check(lib().llmmm_fp8_blockwise_mm_e4m3out(
+            _dev(A_q), _dev(A_s, torch.float32), _dev(B_q), _dev(B_s, torch.float32), _dev(C_q),
+            _dev(C_s, torch.float32), M, N, K, _stream(stream)))
+
+
+def fp8_blockwise_mm_f32(A_q, A_s, B_q, B_s, C, M: int, N: int, K: int, stream=None) -> None:
+    """FP8 blockwise GEMM, fp32 output
+    (fp8_gemm_blockwise_quant_A_1x128__B_128x128__output_fp32)."""
+    with torch.cuda.device(A_q.device):
+        _check(lib().llmmm_fp8_blockwise_mm_f32out(
+            _dev(A_q), _dev(A_s, torch.float32), _dev(B_q), _dev(B_s, torch.float32), _dev(C, torch.float32),
+            M, N, K, _stream(stream)))
+
+
+def fp8_quant_1x128(x, q, scale, M: int, K: int, stream=None) -> None:
+    """fp8_blockwise_symmetric_quantization<1,128,true>."""
+    with torch.cuda.device(x.device):
+        _check(lib().llmmm_fp8_quant_1x128(_dev(x, torch.float32), _dev(q), _dev(scale, torch.float32), M, K,
+                                           _stream(stream)))
+
+
+def fp8_quant_128x128(x, q, scale, rows: int, cols: int, stream=None) -> None:
+    """fp8_blockwise_symmetric_quantization<128,128,false>."""
+    with torch.cuda.device(x.device):
+        _check(lib().llmmm_fp8_quant_128x128(_dev(x, torch.float32), _dev(q), _dev(scale, torch.float32), rows,
+                                             cols, _stream(stream)))
+
+
+def fp8_workspace_bytes(M: int, N: int, K: int) -> int:
+    return int(lib().llmmm_fp8_workspace_bytes(M, N, K))
+
+
+_workspaces: dict[int, torch.Tensor] = {}
+
+
+def ensure_workspace(M: int, N: int, K: int, device=None) -> None:
+    """Registers a split-K scratch buffer large enough for (M,N,K) on `device`.
+    The buffer is owned here (the library never allocates)."""
+    need = fp8_workspace_bytes(M, N, K)
+    if need == 0:
+        return
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    cur = _workspaces.get(idx)
+    if cur is None or cur.numel() < need:
+        cur = torch.zeros(need, dtype=torch.uint8, device=dev)
+        _workspaces[idx] = cur
+        with torch.cuda.device(dev):
+            torch.cuda.synchronize()
+            _check(lib().llmmm_set_workspace(cur.data_ptr(), cur.numel()))

@@ -1,0 +1,193 @@
+// Host-side state behind the C ABI: error text, device info, the device status
+// word, TMA descriptor encoding through the driver entry point.
+#include <atomic>
+#include <cstring>
+#include <mutex>
+
+#include "host_common.h"
+
+namespace llmmm {
+
+namespace {
+
+thread_local char g_error[512] = "";
+
+// One status word per device that loads the library; written by device-side
+// waits that ran out (see mbar_wait), read by llmmm_check_status().
+__device__ uint32_t g_status_word;
+
+constexpr int MAX_DEVICES = 64;
+DeviceInfo    g_devices[MAX_DEVICES];
+bool          g_device_ready[MAX_DEVICES];
+std::mutex    g_device_mutex;
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*,
+                                   CUtensorMapDataType,
+                                   cuuint32_t,
+                                   void*,
+                                   const cuuint64_t*,
+                                   const cuuint64_t*,
+                                   const cuuint32_t*,
+                                   const cuuint32_t*,
+                                   CUtensorMapInterleave,
+                                   CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+EncodeTiledFn g_encode = nullptr;
+
+EncodeTiledFn get_encode()
+{
+  static std::once_flag once;
+  std::call_once(once, []() {
+    void*                           fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) {
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+  });
+  return g_encode;
+}
+
+}  // namespace
+
+std::atomic<uint64_t> g_launches{0};
+
+int set_error(int code, const char* fmt, ...)
+{
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+const DeviceInfo* device_info()
+{
+  int         dev = -1;
+  cudaError_t e   = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+    set_error(LLMMM_ERR_UNSUPPORTED, "no usable CUDA device: %s", cudaGetErrorString(e));
+    cudaGetLastError();
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_device_mutex);
+  if (!g_device_ready[dev]) {
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, dev);
+    if (e != cudaSuccess) {
+      set_error(LLMMM_ERR_CUDA, "cudaGetDeviceProperties failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    if (prop.major != 10) {
+      set_error(LLMMM_ERR_UNSUPPORTED,
+                "device %d is sm_%d%d; this library contains sm_100a code only and has no fallback",
+                dev,
+                prop.major,
+                prop.minor);
+      return nullptr;
+    }
+    void* sp = nullptr;
+    e        = cudaGetSymbolAddress(&sp, g_status_word);
+    if (e != cudaSuccess) {
+      set_error(LLMMM_ERR_CUDA, "cudaGetSymbolAddress(status) failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    e = cudaMemset(sp, 0, sizeof(uint32_t));
+    if (e != cudaSuccess) {
+      set_error(LLMMM_ERR_CUDA, "clearing the status word failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    g_devices[dev].device   = dev;
+    g_devices[dev].sm_count = prop.multiProcessorCount;
+    g_devices[dev].status   = static_cast<uint32_t*>(sp);
+    g_device_ready[dev]     = true;
+  }
+  return &g_devices[dev];
+}
+
+bool make_tmap_2d(CUtensorMap*        out,
+                  const void*         base,
+                  CUtensorMapDataType dtype,
+                  uint32_t            elem_bytes,
+                  uint64_t            inner,
+                  uint64_t            outer,
+                  uint64_t            row_stride_bytes,
+                  uint32_t            box_inner,
+                  uint32_t            box_outer,
+                  CUtensorMapSwizzle  swizzle)
+{
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) {
+    set_error(LLMMM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    return false;
+  }
+  (void)elem_bytes;
+  cuuint64_t dims[2]    = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2]     = {box_inner, box_outer};
+  cuuint32_t estr[2]    = {1, 1};
+  CUresult   r          = enc(out,
+                   dtype,
+                   2,
+                   const_cast<void*>(base),
+                   dims,
+                   strides,
+                   box,
+                   estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzle,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error(LLMMM_ERR_CUDA,
+              "cuTensorMapEncodeTiled failed (%d) for base=%p dims=(%llu,%llu) stride=%llu box=(%u,%u)",
+              (int)r,
+              base,
+              (unsigned long long)inner,
+              (unsigned long long)outer,
+              (unsigned long long)row_stride_bytes,
+              box_inner,
+              box_outer);
+    return false;
+  }
+  return true;
+}
+
+}  // namespace llmmm
+
+extern "C" {
+
+const char* llmmm_last_error(void)
+{
+  return llmmm::g_error;
+}
+
+const char* llmmm_version(void)
+{
+  return "llmmm-b200 0.1 (sm_100a)";
+}
+
+uint64_t llmmm_launch_count(void)
+{
+  return llmmm::g_launches.load();
+}
+
+int llmmm_check_status(llmmm_stream_t stream)
+{
+  const llmmm::DeviceInfo* info = llmmm::device_info();
+  if (info == nullptr) {
+    return LLMMM_ERR_UNSUPPORTED;
+  }
+  LLMMM_CUDA_TRY(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)));
+  uint32_t word = 0;
+  LLMMM_CUDA_TRY(cudaMemcpy(&word, info->status, sizeof(word), cudaMemcpyDeviceToHost));
+  if (word != 0) {
+    cudaMemset(info->status, 0, sizeof(word));
+    return llmmm::set_error(LLMMM_ERR_DEVICE_WAIT, "a device-side wait ran out, code 0x%x", word);
+  }
+  return LLMMM_OK;
+}
+
+}  // extern "C"

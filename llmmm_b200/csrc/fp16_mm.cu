@@ -1,0 +1,311 @@
+// FP16 / BF16 GEMM for sm_100a:  C[M,N] = A[M,K] * B[K,N], row-major, fp32
+// accumulation in tensor memory, one round-to-nearest conversion of the result.
+//
+// Replaces the reference's LLMMM::fp16_mm<T> (launcher src/mm/fp16/mm.cu:7-42,
+// kernel src/mm/fp16/mm.cuh:10-684, an mma.sync.m16n8k16 + ldmatrix kernel with
+// a 256x256 CTA tile).  Nothing of that kernel's structure is kept:
+//
+//   * persistent grid, one CTA per SM, static round-robin over 128x256 tiles;
+//   * warp 0 (one lane) streams A (K-major) and B (N-major, read in place from
+//     the row-major [K,N] array: no transpose pass) with TMA into a 4-stage
+//     ring of 128-byte-swizzled shared-memory tiles, completion on mbarriers;
+//   * warp 1 (one lane) issues tcgen05.mma.kind::f16 (128x256x16) into one of
+//     two 256-column TMEM accumulators and commits ring slots back to the
+//     producer and finished accumulators to the epilogue;
+//   * warps 4-7 drain an accumulator with tcgen05.ld (each lane owns one
+//     output row), convert to the 16-bit type, stage 32x64 sub-tiles in
+//     swizzled shared memory and write them with TMA stores, while the MMA warp
+//     already fills the other accumulator with the next tile.
+//
+// Edge tiles rely on TMA: out-of-range loads read zeros, stores are clipped.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <type_traits>
+
+#include "host_common.h"
+#include "sm100.cuh"
+
+namespace llmmm {
+
+namespace fp16cfg {
+constexpr int      BM          = 128;
+constexpr int      BN          = 256;
+constexpr int      BK          = 64;  // 64 x 2 B = one 128-byte swizzle row of A
+constexpr int      UMMA_K      = 16;
+constexpr int      STAGES      = 4;
+constexpr int      THREADS     = 256;
+constexpr uint32_t A_BYTES     = BM * BK * 2;         // 16 KB
+constexpr uint32_t B_BOX_BYTES = 64 * BK * 2;         // one 64(n) x 64(k) box: 8 KB
+constexpr uint32_t B_BYTES     = B_BOX_BYTES * (BN / 64);  // 32 KB
+constexpr uint32_t STAGE_TX    = A_BYTES + B_BYTES;
+constexpr uint32_t C_WARP_BUF  = 32 * 128;  // 32 rows x 64 halves
+constexpr uint32_t OFF_A       = 0;
+constexpr uint32_t OFF_B       = OFF_A + STAGES * A_BYTES;
+constexpr uint32_t OFF_C       = OFF_B + STAGES * B_BYTES;
+constexpr uint32_t OFF_BAR     = OFF_C + 4 * 2 * C_WARP_BUF;
+constexpr uint32_t SMEM_BYTES  = OFF_BAR + 256 + 1024;  // + barrier block + alignment slack
+constexpr uint32_t TMEM_COLS   = 512;                   // two 256-column accumulators
+}  // namespace fp16cfg
+
+struct Fp16Bars {
+  uint64_t full[fp16cfg::STAGES];
+  uint64_t empty[fp16cfg::STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+template<typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+
+template<>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b)
+{
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template<>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b)
+{
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template<typename T>
+__global__ void __launch_bounds__(fp16cfg::THREADS, 1) fp16_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
+                                                                        const __grid_constant__ CUtensorMap tm_b,
+                                                                        const __grid_constant__ CUtensorMap tm_c,
+                                                                        int                                 M,
+                                                                        int                                 N,
+                                                                        int                                 K,
+                                                                        uint32_t*                           status)
+{
+  using namespace fp16cfg;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t*  smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Fp16Bars* bars = reinterpret_cast<Fp16Bars*>(smem + OFF_BAR);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int m_tiles   = (M + BM - 1) / BM;
+  const int n_tiles   = (N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int k_iters   = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bars->tmem_full[a], 1);
+      mbar_init(&bars->tmem_empty[a], 4);
+    }
+    bars->abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tm_a);
+    prefetch_tmap(&tm_b);
+    prefetch_tmap(&tm_c);
+  }
+  if (warp == 2) {
+    tmem_alloc<TMEM_COLS>(&bars->tmem_base);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------ TMA producer --
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * BM;
+        const int n0 = (tile / m_tiles) * BN;
+        for (int kb = 0; kb < k_iters; ++kb, ++it) {
+          const uint32_t s  = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          mbar_wait(&bars->empty[s], ph ^ 1, DEV_WAIT_SMEM_EMPTY, abort_flag, status);
+          mbar_arrive_expect_tx(&bars->full[s], STAGE_TX);
+          tma_load_2d(smem + OFF_A + s * A_BYTES, &tm_a, &bars->full[s], kb * BK, m0);
+#pragma unroll
+          for (int j = 0; j < BN / 64; ++j) {
+            tma_load_2d(smem + OFF_B + s * B_BYTES + j * B_BOX_BYTES, &tm_b, &bars->full[s], n0 + j * 64, kb * BK);
+          }
+        }
+      }
+    }
+  }
+  else if (warp == 1) {
+    // -------------------------------------------------------- MMA issuer --
+    if (lane == 0) {
+      constexpr uint32_t kFmt  = std::is_same<T, __half>::value ? 0u : 1u;
+      constexpr uint32_t idesc = make_idesc(kFmt, kFmt, /*a_mn=*/0, /*b_mn=*/1, BM, BN);
+      uint32_t           it    = 0;
+      uint32_t           t     = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
+        const uint32_t acc    = t & 1;
+        const uint32_t acc_ph = (t >> 1) & 1;
+        mbar_wait(&bars->tmem_empty[acc], acc_ph ^ 1, DEV_WAIT_TMEM_EMPTY, abort_flag, status);
+        tc_fence_after_sync();
+        const uint32_t d_addr = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_iters; ++kb, ++it) {
+          const uint32_t s  = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          mbar_wait(&bars->full[s], ph, DEV_WAIT_SMEM_FULL, abort_flag, status);
+          tc_fence_after_sync();
+          const uint64_t da = make_smem_desc_sw128(smem_u32(smem + OFF_A + s * A_BYTES), 0, 1024);
+          const uint64_t db = make_smem_desc_sw128(smem_u32(smem + OFF_B + s * B_BYTES), B_BOX_BYTES, 1024);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            // A: 16 k-elements = 32 B inside the swizzled row; B: 16 k-rows of 128 B.
+            tc_mma_f16(d_addr,
+                       da + (uint64_t)((kk * UMMA_K * 2) >> 4),
+                       db + (uint64_t)((kk * UMMA_K * 128) >> 4),
+                       idesc,
+                       (kb | kk) != 0);
+          }
+          tc_commit(&bars->empty[s]);
+        }
+        tc_commit(&bars->tmem_full[acc]);
+      }
+    }
+  }
+  else if (warp >= 4) {
+    // ---------------------------------------------------------- epilogue --
+    const int      ew       = warp - 4;  // == warp % 4: the TMEM lane quarter this warp may read
+    uint8_t*       cbuf     = smem + OFF_C + ew * 2 * C_WARP_BUF;
+    uint32_t       t        = 0;
+    uint32_t       chunk_it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
+      const int      m0     = (tile % m_tiles) * BM;
+      const int      n0     = (tile / m_tiles) * BN;
+      const uint32_t acc    = t & 1;
+      const uint32_t acc_ph = (t >> 1) & 1;
+      mbar_wait(&bars->tmem_full[acc], acc_ph, DEV_WAIT_TMEM_FULL, abort_flag, status);
+      tc_fence_after_sync();
+      const uint32_t t_addr = tmem_base + acc * BN + ((uint32_t)(ew * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 64; ++c, ++chunk_it) {
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32b_x32(t_addr + c * 64, v0);
+        tmem_ld_32x32b_x32(t_addr + c * 64 + 32, v1);
+        tmem_ld_wait();
+        if (c == BN / 64 - 1) {
+          // the accumulator is drained: hand it back to the MMA warp
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(&bars->tmem_empty[acc]);
+          }
+        }
+        uint8_t* buf = cbuf + (chunk_it & 1) * C_WARP_BUF;
+        // the TMA store issued from this buffer two chunks ago must have read it
+        if (lane == 0) {
+          tma_store_wait_read<1>();
+        }
+        __syncwarp();
+        uint8_t* row = buf + lane * 128;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 q;
+          q.x = pack2<T>(__uint_as_float(v0[j * 8 + 0]), __uint_as_float(v0[j * 8 + 1]));
+          q.y = pack2<T>(__uint_as_float(v0[j * 8 + 2]), __uint_as_float(v0[j * 8 + 3]));
+          q.z = pack2<T>(__uint_as_float(v0[j * 8 + 4]), __uint_as_float(v0[j * 8 + 5]));
+          q.w = pack2<T>(__uint_as_float(v0[j * 8 + 6]), __uint_as_float(v0[j * 8 + 7]));
+          *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = q;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 q;
+          q.x = pack2<T>(__uint_as_float(v1[j * 8 + 0]), __uint_as_float(v1[j * 8 + 1]));
+          q.y = pack2<T>(__uint_as_float(v1[j * 8 + 2]), __uint_as_float(v1[j * 8 + 3]));
+          q.z = pack2<T>(__uint_as_float(v1[j * 8 + 4]), __uint_as_float(v1[j * 8 + 5]));
+          q.w = pack2<T>(__uint_as_float(v1[j * 8 + 6]), __uint_as_float(v1[j * 8 + 7]));
+          *reinterpret_cast<uint4*>(row + (((j + 4) ^ (lane & 7)) << 4)) = q;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const int x = n0 + c * 64;
+          const int y = m0 + ew * 32;
+          if (x < N && y < M) {
+            tma_store_2d(&tm_c, buf, x, y);
+          }
+          tma_store_commit();
+        }
+      }
+    }
+    if (lane == 0) {
+      tma_store_wait_all<0>();
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc<TMEM_COLS>(tmem_base);
+  }
+}
+
+template<typename T>
+static int launch_fp16(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream)
+{
+  using namespace fp16cfg;
+  if (A == nullptr || B == nullptr || C == nullptr) {
+    return set_error(LLMMM_ERR_SHAPE, "null pointer argument");
+  }
+  if (M < 1 || N < 8 || K < 8 || (N % 8) != 0 || (K % 8) != 0) {
+    return set_error(LLMMM_ERR_SHAPE, "M or N or K are not aligned. (need M>=1, N%%8==0, K%%8==0; got %d %d %d)", M, N, K);
+  }
+  if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) {
+    return set_error(LLMMM_ERR_SHAPE, "A, B and C must be 16-byte aligned");
+  }
+  const DeviceInfo* info = device_info();
+  if (info == nullptr) {
+    return LLMMM_ERR_UNSUPPORTED;
+  }
+  constexpr CUtensorMapDataType dt =
+    std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap tm_a, tm_b, tm_c;
+  if (!make_tmap_2d(&tm_a, A, dt, 2, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B)
+      || !make_tmap_2d(&tm_b, B, dt, 2, (uint64_t)N, (uint64_t)K, (uint64_t)N * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B)
+      || !make_tmap_2d(&tm_c, C, dt, 2, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B)) {
+    return LLMMM_ERR_CUDA;
+  }
+  static thread_local bool attr_set[64] = {};
+  if (!attr_set[info->device]) {
+    LLMMM_CUDA_TRY(
+      cudaFuncSetAttribute(fp16_gemm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+    attr_set[info->device] = true;
+  }
+  const int m_tiles = (M + BM - 1) / BM;
+  const int n_tiles = (N + BN - 1) / BN;
+  const int tiles   = m_tiles * n_tiles;
+  const int grid    = tiles < info->sm_count ? tiles : info->sm_count;
+  fp16_gemm_kernel<T><<<grid, THREADS, SMEM_BYTES, stream>>>(tm_a, tm_b, tm_c, M, N, K, info->status);
+  g_launches.fetch_add(1);
+  LLMMM_CUDA_TRY(cudaGetLastError());
+  return LLMMM_OK;
+}
+
+}  // namespace llmmm
+
+extern "C" {
+
+int llmmm_fp16_mm_f16(const void* A, const void* B, void* C, int M, int N, int K, llmmm_stream_t stream)
+{
+  return llmmm::launch_fp16<__half>(A, B, C, M, N, K, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int llmmm_fp16_mm_bf16(const void* A, const void* B, void* C, int M, int N, int K, llmmm_stream_t stream)
+{
+  return llmmm::launch_fp16<__nv_bfloat16>(A, B, C, M, N, K, reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

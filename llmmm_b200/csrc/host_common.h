@@ -1,0 +1,54 @@
+// Host-side helpers shared by the launchers behind the C ABI: error text,
+// per-device state (SM count, device status word), TMA descriptor encoding.
+#pragma once
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/llmmm_c.h"
+
+namespace llmmm {
+
+// Kernels launched by this library in this process (llmmm_launch_count()).
+extern std::atomic<uint64_t> g_launches;
+
+// Records a message for llmmm_last_error() and returns `code`.
+int set_error(int code, const char* fmt, ...);
+
+struct DeviceInfo {
+  int       device;
+  int       sm_count;
+  uint32_t* status;  // device address of the status word of this device
+};
+
+// Info for the current device; queried once per device.  Returns nullptr (and
+// sets the error text) when the device is not an sm_100 part or a CUDA call
+// fails.
+const DeviceInfo* device_info();
+
+// Encodes a 2-D tiled TMA descriptor.  `inner` is the contiguous dimension.
+// Returns false (error text set) when the driver refuses the arguments.
+bool make_tmap_2d(CUtensorMap*        out,
+                  const void*         base,
+                  CUtensorMapDataType dtype,
+                  uint32_t            elem_bytes,
+                  uint64_t            inner,
+                  uint64_t            outer,
+                  uint64_t            row_stride_bytes,
+                  uint32_t            box_inner,
+                  uint32_t            box_outer,
+                  CUtensorMapSwizzle  swizzle);
+
+#define LLMMM_CUDA_TRY(call)                                                                                           \
+  do {                                                                                                                 \
+    cudaError_t e__ = (call);                                                                                          \
+    if (e__ != cudaSuccess) {                                                                                          \
+      return ::llmmm::set_error(LLMMM_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(e__));                      \
+    }                                                                                                                  \
+  } while (0)
+
+}  // namespace llmmm
