@@ -43,6 +43,20 @@ bool make_tmap_2d(CUtensorMap*        out,
                   uint32_t            box_outer,
                   CUtensorMapSwizzle  swizzle);
 
+// Decode-sized (M <= 64) split-K FP8 path (fp8_decode.cu).  Returns -1 when it
+// does not apply, otherwise an LLMMM_* status.
+int launch_decode(bool         out_f32,
+                  const void*  A,
+                  const float* A_s,
+                  const void*  B,
+                  const float* B_s,
+                  void*        C,
+                  float*       C_s,
+                  int          M,
+                  int          N,
+                  int          K,
+                  cudaStream_t stream);
+
 #define LLMMM_CUDA_TRY(call)                                                                                           \
   do {                                                                                                                 \
     cudaError_t e__ = (call);                                                                                          \

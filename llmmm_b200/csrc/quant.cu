@@ -1,0 +1,187 @@
+// FP8 e4m3 blockwise symmetric quantisers for sm_100a (HBM-bound: 4 bytes read
+// and 1 byte written per element).
+//
+// Replace the reference's fp8_blockwise_symmetric_quantization
+// (examples/005.fp8.mm.cu:439-563): <1,128,true> for activations and
+// <128,128,false> for weights.  The arithmetic is kept bit for bit:
+// s = amax/448 (IEEE division), q = e4m3(s ? x/s : 0) (IEEE division, then
+// round-to-nearest-even with saturation).  The layout of the work is new: the
+// reference stages a 128x128 fp32 block in a 64 KB static shared array, which
+// does not even assemble (static shared memory is limited to 48 KB); here the
+// block lives in registers and the scales are written coalesced.
+#include <cuda_fp8.h>
+
+#include "host_common.h"
+
+namespace llmmm {
+
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  }
+  return v;
+}
+
+__device__ __forceinline__ float amax4(float4 v)
+{
+  return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+}
+
+__device__ __forceinline__ uint32_t quant4(float4 v, float s)
+{
+  const float    a  = s != 0.0f ? __fdiv_rn(v.x, s) : 0.0f;
+  const float    b  = s != 0.0f ? __fdiv_rn(v.y, s) : 0.0f;
+  const float    c  = s != 0.0f ? __fdiv_rn(v.z, s) : 0.0f;
+  const float    d  = s != 0.0f ? __fdiv_rn(v.w, s) : 0.0f;
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+// One warp quantises 32 consecutive rows of one 128-wide K group: per row the
+// 32 lanes hold one float4 each (a coalesced 512-byte read), the row amax is a
+// warp reduction, and lane r keeps the scale of row r so that the 32 scales
+// leave as one 128-byte store into scale[(K/128), M].
+constexpr int Q1_ROWS  = 32;
+constexpr int Q1_WARPS = 8;
+
+__global__ void __launch_bounds__(Q1_WARPS * 32)
+  quant_1x128_kernel(const float* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale, int M, int K)
+{
+  const int lane    = threadIdx.x & 31;
+  const int warp    = threadIdx.x >> 5;
+  const int groups  = K / 128;
+  const long long w = (long long)blockIdx.x * Q1_WARPS + warp;
+  const int row_blocks = (M + Q1_ROWS - 1) / Q1_ROWS;
+  if (w >= (long long)row_blocks * groups) {
+    return;
+  }
+  // consecutive warps walk along K first so that a CTA reads long row segments
+  const int g  = (int)(w % groups);
+  const int m0 = (int)(w / groups) * Q1_ROWS;
+
+  float my_scale = 0.0f;
+#pragma unroll 1
+  for (int r0 = 0; r0 < Q1_ROWS; r0 += 8) {
+    float4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int m = m0 + r0 + j;
+      v[j]        = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (m < M) {
+        v[j] = __ldcs(reinterpret_cast<const float4*>(x + (size_t)m * K + (size_t)g * 128) + lane);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int   m    = m0 + r0 + j;
+      const float amax = warp_max(amax4(v[j]));
+      const float s    = __fdiv_rn(amax, 448.0f);
+      if (lane == r0 + j) {
+        my_scale = s;
+      }
+      if (m < M) {
+        reinterpret_cast<uint32_t*>(q + (size_t)m * K + (size_t)g * 128)[lane] = quant4(v[j], s);
+      }
+    }
+  }
+  if (m0 + lane < M) {
+    scale[(size_t)g * M + m0 + lane] = my_scale;
+  }
+}
+
+// One CTA of 256 threads quantises one 128x128 block held in registers
+// (16 float4 per thread): block amax by warp shuffles and an 8-entry shared
+// array, then the conversion straight from registers.
+__global__ void __launch_bounds__(256)
+  quant_128x128_kernel(const float* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale, int rows, int cols)
+{
+  __shared__ float warp_amax[8];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int cb   = blockIdx.x;
+  const int rb   = blockIdx.y;
+  const int CB   = cols / 128;
+
+  float4 v[16];
+  float  amax = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const int r = rb * 128 + j * 8 + warp;
+    v[j]        = __ldcs(reinterpret_cast<const float4*>(x + (size_t)r * cols + (size_t)cb * 128) + lane);
+    amax        = fmaxf(amax, amax4(v[j]));
+  }
+  amax = warp_max(amax);
+  if (lane == 0) {
+    warp_amax[warp] = amax;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    amax = fmaxf(amax, warp_amax[i]);
+  }
+  const float s = __fdiv_rn(amax, 448.0f);
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const int r = rb * 128 + j * 8 + warp;
+    reinterpret_cast<uint32_t*>(q + (size_t)r * cols + (size_t)cb * 128)[lane] = quant4(v[j], s);
+  }
+  if (threadIdx.x == 0) {
+    scale[(size_t)rb * CB + cb] = s;
+  }
+}
+
+}  // namespace llmmm
+
+extern "C" {
+
+int llmmm_fp8_quant_1x128(const float* x, void* q, float* scale, int M, int K, llmmm_stream_t stream)
+{
+  using namespace llmmm;
+  if (x == nullptr || q == nullptr || scale == nullptr) {
+    return set_error(LLMMM_ERR_SHAPE, "null pointer argument");
+  }
+  if (M < 1 || K < 128 || (K % 128) != 0) {
+    return set_error(LLMMM_ERR_SHAPE, "M or K are not aligned. (need M>=1, K%%128==0; got %d %d)", M, K);
+  }
+  if (((uintptr_t)x | (uintptr_t)q) & 15) {
+    return set_error(LLMMM_ERR_SHAPE, "x and q must be 16-byte aligned");
+  }
+  if (device_info() == nullptr) {
+    return LLMMM_ERR_UNSUPPORTED;
+  }
+  const long long warps  = (long long)((M + Q1_ROWS - 1) / Q1_ROWS) * (K / 128);
+  const long long blocks = (warps + Q1_WARPS - 1) / Q1_WARPS;
+  quant_1x128_kernel<<<(unsigned)blocks, Q1_WARPS * 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+    x, static_cast<uint8_t*>(q), scale, M, K);
+  g_launches.fetch_add(1);
+  LLMMM_CUDA_TRY(cudaGetLastError());
+  return LLMMM_OK;
+}
+
+int llmmm_fp8_quant_128x128(const float* x, void* q, float* scale, int rows, int cols, llmmm_stream_t stream)
+{
+  using namespace llmmm;
+  if (x == nullptr || q == nullptr || scale == nullptr) {
+    return set_error(LLMMM_ERR_SHAPE, "null pointer argument");
+  }
+  if (rows < 128 || cols < 128 || (rows % 128) != 0 || (cols % 128) != 0) {
+    return set_error(LLMMM_ERR_SHAPE, "rows or cols are not aligned. (need multiples of 128; got %d %d)", rows, cols);
+  }
+  if (((uintptr_t)x | (uintptr_t)q) & 15) {
+    return set_error(LLMMM_ERR_SHAPE, "x and q must be 16-byte aligned");
+  }
+  if (device_info() == nullptr) {
+    return LLMMM_ERR_UNSUPPORTED;
+  }
+  dim3 grid(cols / 128, rows / 128);
+  quant_128x128_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+    x, static_cast<uint8_t*>(q), scale, rows, cols);
+  g_launches.fetch_add(1);
+  LLMMM_CUDA_TRY(cudaGetLastError());
+  return LLMMM_OK;
+}
+
+}  // extern "C"
