@@ -1,0 +1,420 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: FP8 e4m3 blockwise GEMM with fused 1x128 output
+quantisation at M=N=K=4096 (the configuration the headline metric is quoted
+on), through the C ABI of libllmmm_b200.so.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one GEMM launch over one batch of synthetic operands.  Prints ONE
+JSON line (rank 0).  With N > 1 (launched by torch.distributed.run) every rank
+runs the same 4096-row problem on its own GPU: an M-split of a global
+M = 4096*N with replicated weights, no data-path collective (weak scaling).
+
+`--impl reference` times the CPU restatement of the reference's own arithmetic
+(oracle/, all host threads) on bounded row slabs of the same workload; the
+reference project has no CPU implementation of its own.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+M = N = K = 4096
+FLOP_PER_STEP = 2.0 * M * N * K
+WORKLOAD = ("FP8 e4m3 blockwise GEMM M=N=K=4096: A 1x128 scales, B 128x128 scales, fp32 accumulate with "
+            "per-128-K promotion, C emitted as e4m3 with fused 1x128 scales")
+METRIC = "fp8_blockwise_gemm_4096_tflops"
+UNIT = "TFLOP/s"
+SETS = 6  # rotating operand sets: 6 x 49 MB = 294 MB > 126 MB L2
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d, "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+# ------------------------------------------------------------------ clocks --
+
+class ClockSampler:
+    """Samples SM clock, power and clock-event reasons through NVML (read-only) every 10 ms."""
+
+    def __init__(self, index: int):
+        self.samples = []
+        self.stop_flag = False
+        self.ok = False
+        self.thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception as e:  # noqa: BLE001
+            self.err = repr(e)
+
+    def _reasons(self):
+        nv = self.nv
+        for name in ("nvmlDeviceGetCurrentClocksEventReasons", "nvmlDeviceGetCurrentClocksThrottleReasons"):
+            fn = getattr(nv, name, None)
+            if fn is not None:
+                try:
+                    return int(fn(self.h))
+                except Exception:  # noqa: BLE001
+                    continue
+        return 0
+
+    def _run(self):
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    watts = nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0
+                except Exception:  # noqa: BLE001
+                    watts = 0.0
+                self.samples.append((time.perf_counter(), mhz, watts, self._reasons()))
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(0.01)
+
+    def start(self):
+        if self.ok:
+            self.thread = threading.Thread(target=self._run, daemon=True)
+            self.thread.start()
+
+    def stop(self):
+        self.stop_flag = True
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+
+    def summary(self, t0: float, t1: float, window: str):
+        if not self.ok:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "NVML unavailable: " + getattr(self, "err", "")}
+        names = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+                 0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+                 0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+        inside = [s for s in self.samples if t0 <= s[0] <= t1]
+        use = inside if inside else self.samples
+        bits = 0
+        for s in use:
+            bits |= s[3]
+        reasons = [n for b, n in names.items() if bits & b and n != "gpu_idle"]
+        return {
+            "sm_mhz": statistics.median(s[1] for s in use) if use else None,
+            "sm_max_mhz": self.max_mhz,
+            "power_w_max": max((s[2] for s in use), default=None),
+            "reasons": reasons,
+            "samples": len(use),
+            "window": window,
+        }
+
+
+# --------------------------------------------------------------- reference --
+
+def reference_arm(args) -> int:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    import numpy as np
+    from oracle import oracle as o
+    o.build()
+    cores = o.num_threads()
+    rows = 256  # one step = a 256-row slab of the 4096-row problem (about 0.5 s on 8 cores)
+    rng = np.random.default_rng(0x4C4D4D4D)
+    x = rng.standard_normal((rows, K)).astype(np.float32)
+    w = rng.standard_normal((N, K)).astype(np.float32)
+    A_q, A_s = o.quant_1x128(x)
+    B_q, B_s = o.quant_128x128(w)
+
+    def step():
+        acc = o.fp8_blockwise_acc(A_q, A_s, B_q, B_s)
+        o.c_quant_1x128(acc)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    ms = dt / args.steps * 1e3
+    value = 2.0 * rows * N * K / (ms * 1e-3) / 1e12
+    sample = f"{rows}-row slab of the 4096-row problem per step (M={rows}, N=K=4096), {cores} OpenMP threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 operands, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "the reference project has no CPU code; this is the CPU restatement of its arithmetic (oracle/)",
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ------------------------------------------------------------------ ours ----
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the secondary configurations")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--quick", action="store_true",
+                    help="profiling mode: timed region only (no sustained clock loop, e2e, extra configs or CPU baseline)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+    from llmmm_b200 import capi
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200 GPU: the library has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    capi.lib()  # fails loudly if the CUDA library is missing
+    stream = torch.cuda.current_stream()
+
+    # operands: fp32 N(0,1) sources quantised by the library's own quantisers (1x128 / 128x128)
+    gen = torch.Generator(device=dev).manual_seed(0x4C4D4D4D + 2 + rank)
+    sets = []
+    for _ in range(SETS):
+        x = torch.randn(M, K, device=dev, generator=gen)
+        w = torch.randn(N, K, device=dev, generator=gen)
+        A_q = torch.empty(M, K, dtype=torch.uint8, device=dev)
+        A_s = torch.empty(K // 128, M, device=dev)
+        B_q = torch.empty(N, K, dtype=torch.uint8, device=dev)
+        B_s = torch.empty(N // 128, K // 128, device=dev)
+        capi.fp8_quant_1x128(x, A_q, A_s, M, K)
+        capi.fp8_quant_128x128(w, B_q, B_s, N, K)
+        C_q = torch.empty(M, N, dtype=torch.uint8, device=dev)
+        C_s = torch.empty(N // 128, M, device=dev)
+        sets.append((A_q, A_s, B_q, B_s, C_q, C_s))
+        del x, w
+    torch.cuda.synchronize()
+
+    def step(i):
+        A_q, A_s, B_q, B_s, C_q, C_s = sets[i % SETS]
+        capi.fp8_blockwise_mm(A_q, A_s, B_q, B_s, C_q, C_s, M, N, K)
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    launches0 = capi.launch_count()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    t_begin = time.perf_counter()
+    e0.record(stream)
+    for i in range(args.steps):
+        step(i)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    launches = capi.launch_count() - launches0
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    # sustained loop of the same kernel (about 1 s) so that the clock samples are taken under load
+    t_load = time.perf_counter()
+    reps = 0 if args.quick else max(200, int(1.0 / max(ms_total / args.steps * 1e-3, 1e-6)))
+    for i in range(reps):
+        step(i)
+    torch.cuda.synchronize()
+    t_end = time.perf_counter()
+    sampler.stop()
+    clocks = sampler.summary(t_begin, t_end, "timed region + 1 s sustained loop of the same kernel")
+    capi.check_status()
+
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = world * FLOP_PER_STEP / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end through the public API with host buffers (pinned), copies inside the timed region
+    A_q, A_s, B_q, B_s, C_q, C_s = sets[0]
+    host_in = [t.cpu().pin_memory() for t in (A_q, A_s, B_q, B_s)]
+    host_out = [torch.empty_like(t, device="cpu").pin_memory() for t in (C_q, C_s)]
+    h2d = sum(t.numel() * t.element_size() for t in host_in)
+    d2h = sum(t.numel() * t.element_size() for t in host_out)
+    e2e_steps = 1 if args.quick else max(3, min(args.steps, 30))
+
+    def e2e_step():
+        for h, d in zip(host_in, (A_q, A_s, B_q, B_s)):
+            d.copy_(h, non_blocking=True)
+        capi.fp8_blockwise_mm(A_q, A_s, B_q, B_s, C_q, C_s, M, N, K)
+        for h, d in zip(host_out, (C_q, C_s)):
+            h.copy_(d, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(0 if args.quick else 3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e2e_ms = (time.perf_counter() - t0) / e2e_steps * 1e3
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * FLOP_PER_STEP / (e2e_ms * 1e-3) / 1e12
+
+    peaks, peak_kind = measured_peaks()
+    fp8_peak = 2.0 * float(peaks["bf16_tflops"])
+    achieved = FLOP_PER_STEP / (ms_step * 1e-3) / 1e12
+    roofline = {
+        "bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
+        "traffic": None,
+        "peak_source": f"2 x bf16_tflops ({peak_kind}; the file has no fp8 figure; burst, kernel timed alone)",
+        "frac_of_nominal_4500": achieved / 4500.0,
+        "kernel": "fp8_blockwise_gemm_kernel<false>",
+    }
+    prof = ROOT / "profiles" / "fp8_blockwise_gemm_4096.json"
+    if prof.exists():
+        try:
+            roofline["traffic"] = json.loads(prof.read_text()).get("dram_bytes_per_launch")
+        except Exception:  # noqa: BLE001
+            pass
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp8_e4m3 operands, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "per_gpu": "M=N=K=4096", "sharding": "M-split (independent rows), replicated weights, no collective",
+                   "l2": f"{SETS} rotating operand sets ({SETS * 49} MB) exceed the 126 MB L2"},
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms, "steps": e2e_steps},
+        "gpu_launches": launches,
+        "roofline": roofline,
+    }
+
+    if rank == 0 and world == 1 and not args.no_extra and not args.quick:
+        line["extra"] = extra_configs(torch, capi, dev, peaks)
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.quick:
+        line["cpu_baseline"] = cpu_baseline(sets[0])
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def cpu_baseline(s0):
+    """The oracle's restatement of the reference arithmetic, timed on the host cores on a bounded sample."""
+    from oracle import oracle as o
+    o.build()
+    rows = 1024
+    A_q, A_s, B_q, B_s = (t.cpu().numpy() for t in s0[:4])
+    A_q, A_s = A_q[:rows].copy(), A_s[:, :rows].copy()
+    t0 = time.perf_counter()
+    acc = o.fp8_blockwise_acc(A_q, A_s, B_q, B_s)
+    o.c_quant_1x128(acc)
+    dt = time.perf_counter() - t0
+    return {"value": 2.0 * rows * N * K / dt / 1e12, "unit": UNIT, "cores": o.num_threads(), "kind": "port",
+            "sample": f"first {rows} of the 4096 rows, one pass ({dt:.1f} s)"}
+
+
+def time_graph(torch, fn_list, iters=5):
+    """Median time per call of a CUDA graph that replays fn_list once (launch overhead excluded)."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for f in fn_list:
+            f()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for f in fn_list:
+            f()
+    g.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / len(fn_list))
+    return statistics.median(times)
+
+
+def extra_configs(torch, capi, dev, peaks):
+    """Secondary configurations of the same path: FP16 4096^3 and the Qwen3-4B decode shapes."""
+    out = {}
+    gen = torch.Generator(device=dev).manual_seed(7)
+    # FP16 GEMM 4096^3, rotating sets
+    sets = []
+    for _ in range(3):
+        A = (torch.rand(4096, 4096, device=dev, generator=gen) * 2 - 1).half()
+        B = (torch.rand(4096, 4096, device=dev, generator=gen) * 2 - 1).half()
+        C = torch.empty(4096, 4096, device=dev, dtype=torch.float16)
+        sets.append((A, B, C))
+    fns = [(lambda s=s: capi.fp16_mm(s[0], s[1], s[2], 4096, 4096, 4096)) for s in sets] * 8
+    ms = time_graph(torch, fns)
+    tf = 2.0 * 4096 ** 3 / (ms * 1e-3) / 1e12
+    out["fp16_gemm_4096"] = {"us": ms * 1e3, "tflops": tf, "frac_of_measured_bf16_burst": tf / float(peaks["bf16_tflops"]),
+                             "frac_of_nominal_2250": tf / 2250.0}
+    del sets, fns
+    # decode shapes (HBM-bound): rotate over enough weight copies to exceed L2
+    dec = []
+    for (n, k) in [(6144, 2560), (2560, 4096), (19456, 2560), (2560, 9728)]:
+        copies = max(3, int(300e6 // (n * k)) + 1)
+        ws = [(torch.randint(0, 120, (n, k), dtype=torch.uint8, device=dev), torch.rand(n // 128, k // 128, device=dev))
+              for _ in range(copies)]
+        for m in (1, 16, 64):
+            xq = torch.randint(0, 120, (m, k), dtype=torch.uint8, device=dev)
+            xs = torch.rand(k // 128, m, device=dev)
+            Cq = torch.empty(m, n, dtype=torch.uint8, device=dev)
+            Cs = torch.empty(n // 128, m, device=dev)
+            capi.ensure_workspace(m, n, k)
+            fns = [(lambda w=w: capi.fp8_blockwise_mm(xq, xs, w[0], w[1], Cq, Cs, m, n, k)) for w in ws] * 2
+            ms = time_graph(torch, fns)
+            by = n * k + 4 * (n // 128) * (k // 128) + m * k + 4 * m * k // 128 + m * n + 4 * m * n // 128
+            gbs = by / (ms * 1e-3) / 1e9
+            dec.append({"M": m, "N": n, "K": k, "us": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / float(peaks["hbm_gbs"])})
+        del ws
+    out["qwen3_4b_decode"] = dec
+    capi.check_status()
+    return out
+
+
+if __name__ == "__main__":
+    sys.exit(main())

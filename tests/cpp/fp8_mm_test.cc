@@ -1,0 +1,136 @@
+// Harness driver in the shape of the reference's FP8 example main()
+// (examples/005.fp8.mm.cu:2580-2915): generate fp32 A[M,K] and B_T[N,K],
+// quantise A 1x128 and B_T 128x128 with the drop-in quantisers, run the fused
+// GEMM through the reference launcher names, de-quantise C with
+// q * C_s[n/128*M + m] (:2867-2869) and print max / average errors.
+// Differences: seeded N(0,1) inputs, the comparison is against the oracle's
+// fp64 product of the quantised operands on sampled rows plus the same error
+// measure for the oracle's own fp32 restatement, a pass/fail exit code, and
+// CUDA-event timing.
+//
+// usage: fp8_mm_test [M N K]   (default 4096 4096 4096)
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <random>
+#include <vector>
+
+#include "mm/fp8/mm.h"
+#include "../../oracle/oracle.h"
+
+#define CHECK(call)                                                                                                    \
+  do {                                                                                                                 \
+    cudaError_t e = (call);                                                                                            \
+    if (e != cudaSuccess) {                                                                                            \
+      fprintf(stderr, "CUDA error: %s at %s:%d\n", cudaGetErrorString(e), __FILE__, __LINE__);                         \
+      return 2;                                                                                                        \
+    }                                                                                                                  \
+  } while (0)
+
+int main(int argc, char** argv)
+{
+  int M = 4096, N = 4096, K = 4096;
+  if (argc == 4) {
+    M = atoi(argv[1]);
+    N = atoi(argv[2]);
+    K = atoi(argv[3]);
+  }
+  std::mt19937                    gen(0x4C4D4D4D + 2);
+  std::normal_distribution<float> dis(0.0f, 1.0f);
+  std::vector<float>              A((size_t)M * K), B((size_t)N * K);
+  for (auto& v : A) v = dis(gen);
+  for (auto& v : B) v = dis(gen);
+
+  float *dA, *dB, *dAs, *dBs, *dCs;
+  __nv_fp8_e4m3 *dAq, *dBq, *dCq;
+  CHECK(cudaMalloc(&dA, A.size() * 4));
+  CHECK(cudaMalloc(&dB, B.size() * 4));
+  CHECK(cudaMalloc(&dAq, A.size()));
+  CHECK(cudaMalloc(&dBq, B.size()));
+  CHECK(cudaMalloc(&dCq, (size_t)M * N));
+  CHECK(cudaMalloc(&dAs, (size_t)M * K / 128 * 4));
+  CHECK(cudaMalloc(&dBs, (size_t)N / 128 * K / 128 * 4));
+  CHECK(cudaMalloc(&dCs, (size_t)M * N / 128 * 4));
+  CHECK(cudaMemcpy(dA, A.data(), A.size() * 4, cudaMemcpyDefault));
+  CHECK(cudaMemcpy(dB, B.data(), B.size() * 4, cudaMemcpyDefault));
+
+  fp8_blockwise_symmetric_quantization<1, 128, true>(dA, dAq, dAs, M, K, nullptr);
+  fp8_blockwise_symmetric_quantization<128, 128, false>(dB, dBq, dBs, N, K, nullptr);
+  CHECK(cudaDeviceSynchronize());
+
+  std::vector<uint8_t> Aq(A.size()), Bq(B.size()), Cq((size_t)M * N);
+  std::vector<float>   As((size_t)M * K / 128), Bs((size_t)N / 128 * K / 128), Cs((size_t)M * N / 128);
+  CHECK(cudaMemcpy(Aq.data(), dAq, Aq.size(), cudaMemcpyDefault));
+  CHECK(cudaMemcpy(Bq.data(), dBq, Bq.size(), cudaMemcpyDefault));
+  CHECK(cudaMemcpy(As.data(), dAs, As.size() * 4, cudaMemcpyDefault));
+  CHECK(cudaMemcpy(Bs.data(), dBs, Bs.size() * 4, cudaMemcpyDefault));
+
+  // the quantisers must agree with the oracle byte for byte
+  {
+    std::vector<uint8_t> q(A.size());
+    std::vector<float>   s(As.size());
+    oracle_quant_1x128(A.data(), q.data(), s.data(), M, K);
+    if (q != Aq || s != As) {
+      fprintf(stderr, "activation quantiser differs from the oracle\n");
+      return 1;
+    }
+  }
+
+  bool threw = false;
+  try {
+    fp8_gemm_blockwise_quant_A_1x128__B_128x128__C_1x128__output_fp8__opt_reg(dAq, dAs, dBq, dBs, dCq, dCs, M, N + 64, K, nullptr);
+  }
+  catch (const std::runtime_error&) {
+    threw = true;
+  }
+  if (!threw) {
+    fprintf(stderr, "misaligned N was accepted\n");
+    return 1;
+  }
+
+  CHECK(cudaMemset(dCq, 0, (size_t)M * N));  // as the reference's check macro does (:2854)
+  cudaEvent_t e0, e1;
+  CHECK(cudaEventCreate(&e0));
+  CHECK(cudaEventCreate(&e1));
+  for (int i = 0; i < 3; ++i)
+    fp8_gemm_blockwise_quant_A_1x128__B_128x128__C_1x128__output_fp8__opt_reg(dAq, dAs, dBq, dBs, dCq, dCs, M, N, K, nullptr);
+  CHECK(cudaEventRecord(e0));
+  const int reps = 8;
+  for (int i = 0; i < reps; ++i)
+    fp8_gemm_blockwise_quant_A_1x128__B_128x128__C_1x128__output_fp8__opt_reg(dAq, dAs, dBq, dBs, dCq, dCs, M, N, K, nullptr);
+  CHECK(cudaEventRecord(e1));
+  CHECK(cudaDeviceSynchronize());
+  float ms = 0;
+  CHECK(cudaEventElapsedTime(&ms, e0, e1));
+  CHECK(cudaMemcpy(Cq.data(), dCq, Cq.size(), cudaMemcpyDefault));
+  CHECK(cudaMemcpy(Cs.data(), dCs, Cs.size() * 4, cudaMemcpyDefault));
+
+  const int rows_checked = M < 32 ? M : 32;
+  const int stride       = M / rows_checked;
+  double    max_err = 0, max_err_oracle = 0, sum_err = 0, sum_val = 0;
+  std::vector<double>  t0(N);
+  std::vector<float>   t1(N), cs_row(N / 128), lut(256);
+  std::vector<uint8_t> oq(N), codes(256);
+  for (int i = 0; i < 256; ++i) codes[i] = (uint8_t)i;
+  oracle_e4m3_decode(codes.data(), lut.data(), 256);
+  for (int r = 0; r < rows_checked; ++r) {
+    const int m = r * stride;
+    oracle_fp8_blockwise_acc(Aq.data(), As.data(), Bq.data(), Bs.data(), nullptr, t0.data(), M, N, K, m, 1, 1);
+    oracle_fp8_blockwise_acc(Aq.data(), As.data(), Bq.data(), Bs.data(), t1.data(), nullptr, M, N, K, m, 1, 0);
+    oracle_c_quant_1x128(t1.data(), oq.data(), cs_row.data(), 1, N, 1, 0);
+    for (int n = 0; n < N; ++n) {
+      const double deq  = (double)lut[Cq[(size_t)m * N + n]] * Cs[(size_t)(n / 128) * M + m];
+      const double odeq = (double)lut[oq[n]] * cs_row[n / 128];
+      max_err           = std::fmax(max_err, std::fabs(deq - t0[n]));
+      max_err_oracle    = std::fmax(max_err_oracle, std::fabs(odeq - t0[n]));
+      sum_err += std::fabs(deq - t0[n]);
+      sum_val += std::fabs(t0[n]);
+    }
+  }
+  const double tflops = 2.0 * M * N * K / (ms / reps * 1e-3) / 1e12;
+  printf("fp8_mm M=%d N=%d K=%d: %.1f us/launch, %.1f TFLOPS, max_abs_error = %.6f (oracle's own: %.6f), avg_relative_error = %.6f\n",
+         M, N, K, ms / reps * 1e3, tflops, max_err, max_err_oracle, sum_err / sum_val);
+  const bool ok = max_err <= max_err_oracle * 1.25 && llmmm_check_status(nullptr) == LLMMM_OK;
+  printf("%s\n", ok ? "PASS" : "FAIL");
+  return ok ? 0 : 1;
+}
