@@ -69,15 +69,6 @@ __device__ __forceinline__ void epilogue_bar_sync()
   asm volatile("bar.sync 1, 128;" ::: "memory");
 }
 
-__device__ __forceinline__ void tmem_ld_wait_dep16(uint32_t (&r)[16])
-{
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
-               :
-               : "memory");
-}
-
 // unit u of the (group, K-block) grid belongs to CTA ((u+1)*G - 1) / U, the
 // largest c with floor(c*U/G) <= u.
 __device__ __forceinline__ int cta_of_unit(long long u, int G, long long U)
@@ -212,7 +203,7 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
         for (int c = 0; c < MP / 16; ++c) {
           uint32_t v[16];
           tmem_ld_32x32b_x16(tmem_base + p * 64 + t_lane + c * 16, v);
-          tmem_ld_wait_dep16(v);
+          tmem_ld_wait();
           if (c == MP / 16 - 1) {
             tc_fence_before_sync();
             __syncwarp();

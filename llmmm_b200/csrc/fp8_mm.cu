@@ -18,10 +18,13 @@
 //     a 4-stage ring of 128-byte-swizzled tiles;
 //   * warp 1 issues, per K-block, four tcgen05.mma.kind::f8f6f4 (128x256x32)
 //     that start from zero into one of two 256-column TMEM "partial" stages;
-//   * warps 2-9 (256 threads) promote: each thread owns one output row and one
-//     128-column scale group, reads the finished partial with tcgen05.ld and
+//   * warps 4-11 (two warpgroups, 256 threads, given most of the register file
+//     with setmaxnreg) promote: each thread owns one output row and one
+//     128-column scale group, reads the finished partial with tcgen05.ld (the
+//     next 32 columns are in flight while the current 32 are accumulated) and
 //     does acc = fma(partial, A_s*B_s, acc) in registers while the tensor core
-//     fills the other partial stage;
+//     fills the other partial stage; the scale product of the next K-block is
+//     fetched one block ahead;
 //   * after the last K-block the same threads reduce their 128 values to the
 //     group absmax (thread-local: no shuffles in this orientation), convert to
 //     e4m3 and store one 128-byte line each, plus the coalesced scale column.
@@ -39,7 +42,9 @@ constexpr int      BK         = 128;  // one scale block of K = one 128-byte swi
 constexpr int      UMMA_K     = 32;
 constexpr int      STAGES     = 4;
 constexpr int      PROMO_WARPS = 8;
-constexpr int      THREADS    = 64 + PROMO_WARPS * 32;
+constexpr int      THREADS    = 128 + PROMO_WARPS * 32;  // warpgroup 0: TMA / MMA; warpgroups 1-2: promotion
+constexpr int      REGS_CTRL  = 40;                      // register budget after setmaxnreg: control warpgroup
+constexpr int      REGS_PROMO = 232;                     //   and promotion warpgroups (128*40 + 256*232 = 384*168)
 constexpr uint32_t A_BYTES    = BM * BK;
 constexpr uint32_t B_BYTES    = BN * BK;
 constexpr uint32_t STAGE_TX   = A_BYTES + B_BYTES;
@@ -59,18 +64,16 @@ struct Fp8Bars {
   uint32_t abort_flag;
 };
 
-// Orders the consumers of `r` after the completion of the tcgen05.ld that
-// produced them: the registers are passed through the wait as in/out operands.
-__device__ __forceinline__ void tmem_ld_wait_dep(uint32_t (&r)[32])
+template<int REGS>
+__device__ __forceinline__ void setmaxnreg_inc()
 {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
-                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]),
-                 "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]),
-                 "+r"(r[30]), "+r"(r[31])
-               :
-               : "memory");
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS));
+}
+
+template<int REGS>
+__device__ __forceinline__ void setmaxnreg_dec()
+{
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS));
 }
 
 __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d)
@@ -130,6 +133,8 @@ __global__ void __launch_bounds__(fp8cfg::THREADS, 1) fp8_blockwise_gemm_kernel(
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
 
+  if (warp < 4) {
+    setmaxnreg_dec<REGS_CTRL>();
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer --
     if (lane == 0) {
@@ -174,11 +179,12 @@ __global__ void __launch_bounds__(fp8cfg::THREADS, 1) fp8_blockwise_gemm_kernel(
       }
     }
   }
+  }
   else {
+    setmaxnreg_inc<REGS_PROMO>();
     // ------------------------------------------- promotion + epilogue ----
-    const int      pw      = warp - 2;       // 0..7
-    const int      quarter = warp & 3;       // TMEM lane quarter this warp may read
-    const int      half    = pw >> 2;        // which 128-column scale group of the tile
+    const int      quarter = warp & 3;         // TMEM lane quarter this warp may read
+    const int      half    = (warp - 4) >> 2;  // which 128-column scale group of the tile
     const uint32_t t_lane  = ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 128);
     uint32_t       it      = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
@@ -195,31 +201,70 @@ __global__ void __launch_bounds__(fp8cfg::THREADS, 1) fp8_blockwise_gemm_kernel(
         acc[i] = 0.0f;
       }
 
-      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+      // Scale operands are fetched PREFETCH K-blocks ahead of their use: under the TMA load traffic
+      // an L2 hit takes longer than one K-block lasts.  The empty asm pins the first use of a
+      // fetched value to the top of its own iteration, so the wait for it is never moved up to
+      // the load.
+      constexpr int PREFETCH = 4;
+      float         a_pf[PREFETCH], b_pf[PREFETCH];
+#pragma unroll
+      for (int j = 0; j < PREFETCH; ++j) {
+        a_pf[j] = (j < k_blocks) ? __ldg(a_s + (size_t)j * M) : 0.0f;
+        b_pf[j] = (j < k_blocks) ? __ldg(b_s + j) : 0.0f;
+      }
+      for (int kb0 = 0; kb0 < k_blocks; kb0 += PREFETCH) {
+#pragma unroll
+      for (int j = 0; j < PREFETCH; ++j) {
+        const int kb = kb0 + j;
+        if (kb >= k_blocks) {
+          break;
+        }
         const uint32_t p  = it & 1;
         const uint32_t pp = (it >> 1) & 1;
+        float a_cur = a_pf[j], b_cur = b_pf[j];
+        asm volatile("" : "+f"(a_cur), "+f"(b_cur));
         // one fp32 rounding of the scale product, as in the reference
-        const float sc = __fmul_rn(__ldg(a_s + (size_t)kb * M), __ldg(b_s + kb));
+        const float sc = __fmul_rn(a_cur, b_cur);
+        if (kb + PREFETCH < k_blocks) {
+          a_pf[j] = __ldg(a_s + (size_t)(kb + PREFETCH) * M);
+          b_pf[j] = __ldg(b_s + kb + PREFETCH);
+        }
         mbar_wait(&bars->part_full[p], pp, DEV_WAIT_TMEM_FULL, abort_flag, status);
         tc_fence_after_sync();
         const uint32_t t_addr = tmem_base + p * BN + t_lane;
+        uint32_t       v0[32], v1[32];
+        tmem_ld_32x32b_x32(t_addr, v0);
+        tmem_ld_wait();
+        tmem_ld_32x32b_x32(t_addr + 32, v1);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(t_addr + c * 32, v);
-          tmem_ld_wait_dep(v);
-          if (c == 3) {
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-              mbar_arrive(&bars->part_empty[p]);
-            }
-          }
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            acc[c * 32 + i] = __fmaf_rn(__uint_as_float(v[i]), sc, acc[c * 32 + i]);
-          }
+        for (int i = 0; i < 32; ++i) {
+          acc[i] = __fmaf_rn(__uint_as_float(v0[i]), sc, acc[i]);
         }
+        tmem_ld_wait();
+        tmem_ld_32x32b_x32(t_addr + 64, v0);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          acc[32 + i] = __fmaf_rn(__uint_as_float(v1[i]), sc, acc[32 + i]);
+        }
+        tmem_ld_wait();
+        tmem_ld_32x32b_x32(t_addr + 96, v1);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          acc[64 + i] = __fmaf_rn(__uint_as_float(v0[i]), sc, acc[64 + i]);
+        }
+        tmem_ld_wait();
+        // every column of this thread's part of the partial stage has been read
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&bars->part_empty[p]);
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          acc[96 + i] = __fmaf_rn(__uint_as_float(v1[i]), sc, acc[96 + i]);
+        }
+        ++it;
+      }
       }
 
       if (m_ok && g_ok) {
