@@ -50,6 +50,35 @@ EncodeTiledFn get_encode()
   return g_encode;
 }
 
+__global__ void __launch_bounds__(256, 1) pair_probe_kernel() {}
+
+// Number of 2-CTA clusters of a 1-CTA-per-SM kernel that fit on the device at once.
+int pair_capacity(int sm_count)
+{
+  constexpr int smem = 200 * 1024;  // forces one CTA per SM, like the GEMM kernels
+  if (cudaFuncSetAttribute(pair_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim            = dim3(2 * (sm_count / 2));
+  cfg.blockDim           = dim3(256);
+  cfg.dynamicSmemBytes   = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id               = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs                = attr;
+  cfg.numAttrs             = 1;
+  int clusters             = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, pair_probe_kernel, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return clusters < sm_count / 2 ? clusters : sm_count / 2;
+}
+
 }  // namespace
 
 std::atomic<uint64_t> g_launches{0};
@@ -101,6 +130,9 @@ const DeviceInfo* device_info()
     }
     g_devices[dev].device   = dev;
     g_devices[dev].sm_count = prop.multiProcessorCount;
+    // Every kernel here runs one CTA per SM; a pair needs two SMs of one TPC/GPC.  Pairs can be
+    // fewer than sm_count / 2 when a GPC has an odd number of usable SMs.
+    g_devices[dev].max_pairs = pair_capacity(prop.multiProcessorCount);
     g_devices[dev].status   = static_cast<uint32_t*>(sp);
     g_device_ready[dev]     = true;
   }

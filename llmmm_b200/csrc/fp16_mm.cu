@@ -253,6 +253,299 @@ __global__ void __launch_bounds__(fp16cfg::THREADS, 1) fp16_gemm_kernel(const __
   }
 }
 
+// ------------------------------------------------------------ CTA pairs ----
+//
+// Same pipeline for a cluster of two CTAs that share one 256x256 output tile
+// (tcgen05.mma.cta_group::2): CTA r of the pair loads the 128 rows r*128.. of A
+// and the 128 columns r*128.. of B, so every operand byte is fetched from L2
+// once per pair instead of once per CTA.  A CTA streams 32 KB per k-step instead
+// of 48 KB, which is what the single-CTA kernel is limited by.  Only the even
+// CTA issues MMAs; the TMA loads of both CTAs signal its `full` barrier, and its
+// commits arrive on the `empty` / `tmem_full` barriers of both CTAs.
+#ifdef LLMMM_PROFILE
+// Debug build only: cycle counters of the MMA thread of CTA 0 (total, waiting for operands,
+// waiting for a free accumulator, K-steps), read back with llmmm_profile_dump().
+__device__ long long g_prof16[8];
+#endif
+
+namespace fp16pair {
+constexpr int      BM          = 256;  // per pair; 128 per CTA
+constexpr int      BN          = 256;
+constexpr int      BK          = 64;
+constexpr int      UMMA_K      = 16;
+constexpr int      STAGES      = 6;
+constexpr int      THREADS     = 256;
+constexpr uint32_t A_BYTES     = 128 * BK * 2;             // 16 KB: this CTA's rows
+constexpr uint32_t B_BOX_BYTES = 64 * BK * 2;              // 8 KB
+constexpr uint32_t B_BYTES     = B_BOX_BYTES * 2;          // 16 KB: this CTA's 128 columns
+constexpr uint32_t STAGE_TX    = 2 * (A_BYTES + B_BYTES);  // both CTAs' loads land on the leader's barrier
+constexpr uint32_t C_WARP_BUF  = 32 * 128;
+constexpr uint32_t OFF_A       = 0;
+constexpr uint32_t OFF_B       = OFF_A + STAGES * A_BYTES;
+constexpr uint32_t OFF_C       = OFF_B + STAGES * B_BYTES;
+constexpr uint32_t OFF_BAR     = OFF_C + 4 * 2 * C_WARP_BUF;
+constexpr uint32_t SMEM_BYTES  = OFF_BAR + 256 + 1024;
+constexpr uint32_t TMEM_COLS   = 512;
+}  // namespace fp16pair
+
+struct Fp16PairBars {
+  uint64_t full[fp16pair::STAGES];
+  uint64_t empty[fp16pair::STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+template<typename T>
+__global__ void __launch_bounds__(fp16pair::THREADS, 1)
+  fp16_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
+                        const __grid_constant__ CUtensorMap tm_b,
+                        const __grid_constant__ CUtensorMap tm_c,
+                        int                                 M,
+                        int                                 N,
+                        int                                 K,
+                        uint32_t*                           status)
+{
+  using namespace fp16pair;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Fp16PairBars*      bars       = reinterpret_cast<Fp16PairBars*>(smem + OFF_BAR);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  const int      warp     = threadIdx.x >> 5;
+  const int      lane     = threadIdx.x & 31;
+  const uint32_t rank     = cluster_ctarank();  // 0 = leader
+  const int      pair     = blockIdx.x >> 1;
+  const int      n_pairs  = gridDim.x >> 1;
+
+  const int m_tiles   = (M + BM - 1) / BM;
+  const int n_tiles   = (N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int k_iters   = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bars->tmem_full[a], 1);
+      mbar_init(&bars->tmem_empty[a], 8);  // 4 epilogue warps of each CTA
+    }
+    bars->abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tm_a);
+    prefetch_tmap(&tm_b);
+    prefetch_tmap(&tm_c);
+  }
+  if (warp == 2) {
+    tmem_alloc<TMEM_COLS>(&bars->tmem_base);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the pair's barriers exist before any cross-CTA signal
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------ TMA producer --
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = pair; tile < num_tiles; tile += n_pairs) {
+        const int m0 = (tile % m_tiles) * BM + (int)rank * 128;
+        const int n0 = (tile / m_tiles) * BN + (int)rank * 128;
+        for (int kb = 0; kb < k_iters; ++kb, ++it) {
+          const uint32_t s  = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          mbar_wait(&bars->empty[s], ph ^ 1, DEV_WAIT_SMEM_EMPTY, abort_flag, status);
+          const uint32_t full_leader = mapa_shared(smem_u32(&bars->full[s]), 0);
+          if (rank == 0) {
+            mbar_arrive_expect_tx(&bars->full[s], STAGE_TX);
+          }
+          tma_load_2d_pair(smem + OFF_A + s * A_BYTES, &tm_a, full_leader, kb * BK, m0);
+          tma_load_2d_pair(smem + OFF_B + s * B_BYTES, &tm_b, full_leader, n0, kb * BK);
+          tma_load_2d_pair(smem + OFF_B + s * B_BYTES + B_BOX_BYTES, &tm_b, full_leader, n0 + 64, kb * BK);
+        }
+      }
+    }
+  }
+  else if (warp == 1) {
+    // ------------------------------------------- MMA issuer (leader only) --
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t kFmt  = std::is_same<T, __half>::value ? 0u : 1u;
+      constexpr uint32_t idesc = make_idesc(kFmt, kFmt, /*a_mn=*/0, /*b_mn=*/1, BM, BN);
+      uint32_t           it    = 0;
+      uint32_t           t     = 0;
+#ifdef LLMMM_PROFILE
+      long long p_t0 = clock64(), p_full = 0, p_tmem = 0;
+      unsigned long long p_g0 = global_timer_ns();
+#define PROF_T(x) long long x = clock64()
+#else
+#define PROF_T(x)
+#endif
+      for (int tile = pair; tile < num_tiles; tile += n_pairs, ++t) {
+        const uint32_t acc    = t & 1;
+        const uint32_t acc_ph = (t >> 1) & 1;
+        PROF_T(c0);
+        mbar_wait(&bars->tmem_empty[acc], acc_ph ^ 1, DEV_WAIT_TMEM_EMPTY, abort_flag, status);
+        PROF_T(c1);
+#ifdef LLMMM_PROFILE
+        p_tmem += c1 - c0;
+#endif
+        tc_fence_after_sync();
+        const uint32_t d_addr = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_iters; ++kb, ++it) {
+          const uint32_t s  = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          PROF_T(c2);
+          mbar_wait(&bars->full[s], ph, DEV_WAIT_SMEM_FULL, abort_flag, status);
+          PROF_T(c3);
+#ifdef LLMMM_PROFILE
+          p_full += c3 - c2;
+#endif
+          tc_fence_after_sync();
+          const uint64_t da = make_smem_desc_sw128(smem_u32(smem + OFF_A + s * A_BYTES), 0, 1024);
+          const uint64_t db = make_smem_desc_sw128(smem_u32(smem + OFF_B + s * B_BYTES), B_BOX_BYTES, 1024);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            tc_mma_f16_pair(d_addr,
+                            da + (uint64_t)((kk * UMMA_K * 2) >> 4),
+                            db + (uint64_t)((kk * UMMA_K * 128) >> 4),
+                            idesc,
+                            (kb | kk) != 0);
+          }
+          tc_commit_pair(&bars->empty[s]);
+        }
+        tc_commit_pair(&bars->tmem_full[acc]);
+      }
+#ifdef LLMMM_PROFILE
+      if (blockIdx.x == 0) {
+        g_prof16[0] = clock64() - p_t0;
+        g_prof16[1] = (long long)(global_timer_ns() - p_g0);
+        g_prof16[2] = p_full;
+        g_prof16[3] = p_tmem;
+        g_prof16[4] = it;
+      }
+#endif
+    }
+  }
+  else if (warp >= 4) {
+    // ---------------------------------------------------------- epilogue --
+    const int      ew           = warp - 4;
+    uint8_t*       cbuf         = smem + OFF_C + ew * 2 * C_WARP_BUF;
+    uint32_t       t            = 0;
+    uint32_t       chunk_it     = 0;
+    for (int tile = pair; tile < num_tiles; tile += n_pairs, ++t) {
+      const int      m0     = (tile % m_tiles) * BM + (int)rank * 128;
+      const int      n0     = (tile / m_tiles) * BN;
+      const uint32_t acc    = t & 1;
+      const uint32_t acc_ph = (t >> 1) & 1;
+      mbar_wait(&bars->tmem_full[acc], acc_ph, DEV_WAIT_TMEM_FULL, abort_flag, status);
+      tc_fence_after_sync();
+      const uint32_t t_addr = tmem_base + acc * BN + ((uint32_t)(ew * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 64; ++c, ++chunk_it) {
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32b_x32(t_addr + c * 64, v0);
+        tmem_ld_32x32b_x32(t_addr + c * 64 + 32, v1);
+        tmem_ld_wait();
+        if (c == BN / 64 - 1) {
+          // the accumulator is drained: tell the leader's MMA thread
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive_cluster(mapa_shared(smem_u32(&bars->tmem_empty[acc]), 0));
+          }
+        }
+        uint8_t* buf = cbuf + (chunk_it & 1) * C_WARP_BUF;
+        if (lane == 0) {
+          tma_store_wait_read<1>();
+        }
+        __syncwarp();
+        uint8_t* row = buf + lane * 128;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 q;
+          q.x = pack2<T>(__uint_as_float(v0[j * 8 + 0]), __uint_as_float(v0[j * 8 + 1]));
+          q.y = pack2<T>(__uint_as_float(v0[j * 8 + 2]), __uint_as_float(v0[j * 8 + 3]));
+          q.z = pack2<T>(__uint_as_float(v0[j * 8 + 4]), __uint_as_float(v0[j * 8 + 5]));
+          q.w = pack2<T>(__uint_as_float(v0[j * 8 + 6]), __uint_as_float(v0[j * 8 + 7]));
+          *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = q;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 q;
+          q.x = pack2<T>(__uint_as_float(v1[j * 8 + 0]), __uint_as_float(v1[j * 8 + 1]));
+          q.y = pack2<T>(__uint_as_float(v1[j * 8 + 2]), __uint_as_float(v1[j * 8 + 3]));
+          q.z = pack2<T>(__uint_as_float(v1[j * 8 + 4]), __uint_as_float(v1[j * 8 + 5]));
+          q.w = pack2<T>(__uint_as_float(v1[j * 8 + 6]), __uint_as_float(v1[j * 8 + 7]));
+          *reinterpret_cast<uint4*>(row + (((j + 4) ^ (lane & 7)) << 4)) = q;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const int x = n0 + c * 64;
+          const int y = m0 + ew * 32;
+          if (x < N && y < M) {
+            tma_store_2d(&tm_c, buf, x, y);
+          }
+          tma_store_commit();
+        }
+      }
+    }
+    if (lane == 0) {
+      tma_store_wait_all<0>();
+    }
+  }
+
+  // neither CTA may leave while its partner can still signal its barriers or read its tiles
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc<TMEM_COLS>(tmem_base);
+  }
+}
+
+template<typename T>
+static int launch_fp16_pair(const void* A, const void* B, void* C, int M, int N, int K, const DeviceInfo* info, cudaStream_t stream)
+{
+  using namespace fp16pair;
+  constexpr CUtensorMapDataType dt =
+    std::is_same<T, __half>::value ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap tm_a, tm_b, tm_c;
+  if (!make_tmap_2d(&tm_a, A, dt, 2, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, 128, CU_TENSOR_MAP_SWIZZLE_128B)
+      || !make_tmap_2d(&tm_b, B, dt, 2, (uint64_t)N, (uint64_t)K, (uint64_t)N * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B)
+      || !make_tmap_2d(&tm_c, C, dt, 2, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B)) {
+    return LLMMM_ERR_CUDA;
+  }
+  static thread_local bool attr_set[64] = {};
+  if (!attr_set[info->device]) {
+    LLMMM_CUDA_TRY(
+      cudaFuncSetAttribute(fp16_gemm_pair_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+    attr_set[info->device] = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int pairs = tiles < info->max_pairs ? tiles : info->max_pairs;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim            = dim3(2 * pairs);
+  cfg.blockDim           = dim3(THREADS);
+  cfg.dynamicSmemBytes   = SMEM_BYTES;
+  cfg.stream             = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id               = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs                = attr;
+  cfg.numAttrs             = 1;
+  LLMMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, fp16_gemm_pair_kernel<T>, tm_a, tm_b, tm_c, M, N, K, info->status));
+  g_launches.fetch_add(1);
+  return LLMMM_OK;
+}
+
 template<typename T>
 static int launch_fp16(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream)
 {
@@ -278,6 +571,9 @@ static int launch_fp16(const void* A, const void* B, void* C, int M, int N, int 
       || !make_tmap_2d(&tm_c, C, dt, 2, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B)) {
     return LLMMM_ERR_CUDA;
   }
+  if (M > 128 && N > 128 && info->max_pairs > 0) {
+    return launch_fp16_pair<T>(A, B, C, M, N, K, info, stream);
+  }
   static thread_local bool attr_set[64] = {};
   if (!attr_set[info->device]) {
     LLMMM_CUDA_TRY(
@@ -295,6 +591,16 @@ static int launch_fp16(const void* A, const void* B, void* C, int M, int N, int 
 }
 
 }  // namespace llmmm
+
+#ifdef LLMMM_PROFILE
+extern "C" void llmmm_profile_dump16()
+{
+  long long h[8];
+  cudaMemcpyFromSymbol(h, llmmm::g_prof16, sizeof(h));
+  printf("fp16 pair kernel, CTA 0 MMA thread: %.3f GHz, %.1f us, %lld k-steps, %.0f clk/k-step, waiting operands %.0f, waiting accumulator %.0f clk/k-step\n",
+         (double)h[0] / h[1], h[1] / 1e3, h[4], (double)h[0] / h[4], (double)h[2] / h[4], (double)h[3] / h[4]);
+}
+#endif
 
 extern "C" {
 

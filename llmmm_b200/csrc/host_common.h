@@ -22,7 +22,8 @@ int set_error(int code, const char* fmt, ...);
 struct DeviceInfo {
   int       device;
   int       sm_count;
-  uint32_t* status;  // device address of the status word of this device
+  int       max_pairs;  // CTA pairs (clusters of 2, one CTA per SM) that can be resident at once
+  uint32_t* status;     // device address of the status word of this device
 };
 
 // Info for the current device; queried once per device.  Returns nullptr (and

@@ -310,4 +310,86 @@ make_idesc(uint32_t a_fmt, uint32_t b_fmt, uint32_t a_mn_major, uint32_t b_mn_ma
          | ((m >> 4) << 24);
 }
 
+// ------------------------------------------------- CTA pairs (cluster of 2) --
+//
+// With tcgen05.mma.cta_group::2 one thread of the even ("leader") CTA of a pair
+// issues an MMA of M = 256: each CTA's tensor core computes its own 128 rows
+// from its own shared memory A tile, and each CTA supplies half of the N
+// columns of B.  No TMA multicast is involved: every CTA loads exactly the
+// bytes it owns; only mbarrier signals cross the pair.
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t smem_addr, uint32_t rank)
+{
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ void cluster_sync_all()
+{
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// TMA tile load into this CTA's shared memory whose completion is signalled on
+// an mbarrier given by shared::cluster address (this CTA's or its pair's).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int x, int y)
+{
+  asm volatile(
+    "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+    :
+    : "r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(bar_cluster_addr)
+    : "memory");
+}
+
+// Completion of all MMAs issued so far by this thread arrives on the mbarrier
+// at the same shared-memory offset in both CTAs of the pair.
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar)
+{
+  const uint16_t mask = 3;
+  asm volatile(
+    "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+      smem_u32(bar)),
+    "h"(mask)
+    : "memory");
+}
+
+__device__ __forceinline__ void
+tc_mma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+{
+  asm volatile("{\n\t"
+               ".reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+               "}"
+               :
+               : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+
+__device__ __forceinline__ void
+tc_mma_f8_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+{
+  asm volatile("{\n\t"
+               ".reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+               "}"
+               :
+               : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+
 }  // namespace llmmm
