@@ -115,6 +115,31 @@ int llmmm_fp8_quant_128x128(const float* x, void* q, float* scale, int rows, int
 size_t llmmm_fp8_workspace_bytes(int M, int N, int K);
 int    llmmm_set_workspace(void* device_ptr, size_t bytes);
 
+/* Decode-sized FP8 blockwise GEMM for callers that cannot provide scratch memory.
+ * This one has no counterpart in the reference (which has neither split-K nor
+ * any scratch).  It exists for hosts where device allocation is off the table:
+ * servers whose own pool already holds all of device memory, and token loops
+ * that must never reach cudaMalloc/cudaFree because those calls synchronise the
+ * device.  Same arguments and results as llmmm_fp8_blockwise_mm_e4m3out, but the
+ * split-K scratch is a fixed 4,210,688-byte array inside the library image (held
+ * by every GPU that loads the library until the process exits), so:
+ *   - 1 <= M <= 16 and N <= 524288 only; anything larger returns
+ *     LLMMM_ERR_SHAPE with a message naming the limit;
+ *   - no call allocates or frees anything; the first call on a device looks up
+ *     the array's device address (make that first call outside stream capture);
+ *   - all calls on a device share the one array: two calls whose kernels can
+ *     overlap on the GPU (different streams) race; serialise them. */
+int llmmm_fp8_blockwise_mm_e4m3out_noalloc(const void*    A,
+                                           const float*   A_scale_t,
+                                           const void*    B_t,
+                                           const float*   B_scale_t,
+                                           void*          C,
+                                           float*         C_scale_t,
+                                           int            M,
+                                           int            N,
+                                           int            K,
+                                           llmmm_stream_t stream);
+
 /* Reads the device status word of the current device after synchronising
  * `stream`.  Returns LLMMM_OK, or LLMMM_ERR_DEVICE_WAIT with the code of the
  * wait that ran out in llmmm_last_error(); the word is cleared. */

@@ -41,6 +41,7 @@ def lib() -> ctypes.CDLL:
         for name in ("llmmm_fp16_mm_f16", "llmmm_fp16_mm_bf16"):
             getattr(L, name).argtypes = [_vp, _vp, _vp, _i, _i, _i, _vp]
         L.llmmm_fp8_blockwise_mm_e4m3out.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
+        L.llmmm_fp8_blockwise_mm_e4m3out_noalloc.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
         L.llmmm_fp8_blockwise_mm_f32out.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
         L.llmmm_fp8_quant_1x128.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
         L.llmmm_fp8_quant_128x128.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
@@ -52,7 +53,7 @@ EXPORTED_SYMBOLS = (
     "llmmm_last_error", "llmmm_version", "llmmm_fp16_mm_f16", "llmmm_fp16_mm_bf16",
     "llmmm_fp8_blockwise_mm_e4m3out", "llmmm_fp8_blockwise_mm_f32out", "llmmm_fp8_quant_1x128",
     "llmmm_fp8_quant_128x128", "llmmm_fp8_workspace_bytes", "llmmm_set_workspace", "llmmm_check_status",
-    "llmmm_launch_count",
+    "llmmm_launch_count", "llmmm_fp8_blockwise_mm_e4m3out_noalloc",
 )
 
 
@@ -100,6 +101,15 @@ def fp8_blockwise_mm(A_q, A_s, B_q, B_s, C_q, C_s, M: int, N: int, K: int, strea
     (fp8_gemm_blockwise_quant_A_1x128__B_128x128__C_1x128__output_fp8*)."""
     with torch.cuda.device(A_q.device):
         _check(lib().llmmm_fp8_blockwise_mm_e4m3out(
+            _dev(A_q), _dev(A_s, torch.float32), _dev(B_q), _dev(B_s, torch.float32), _dev(C_q),
+            _dev(C_s, torch.float32), M, N, K, _stream(stream)))
+
+
+def fp8_blockwise_mm_noalloc(A_q, A_s, B_q, B_s, C_q, C_s, M: int, N: int, K: int, stream=None) -> None:
+    """Decode-sized (M <= 16) FP8 blockwise GEMM whose split-K scratch is built into the
+    library, for callers that cannot allocate device memory (see include/llmmm_c.h)."""
+    with torch.cuda.device(A_q.device):
+        _check(lib().llmmm_fp8_blockwise_mm_e4m3out_noalloc(
             _dev(A_q), _dev(A_s, torch.float32), _dev(B_q), _dev(B_s, torch.float32), _dev(C_q),
             _dev(C_s, torch.float32), M, N, K, _stream(stream)))
 

@@ -455,3 +455,97 @@ int llmmm_set_workspace(void* device_ptr, size_t bytes)
 }
 
 }  // extern "C"
+
+// ------------------------------------------------ entry point without scratch --
+//
+// Some callers have no way to hand this library a scratch buffer: a serving
+// process that gave every byte of device memory to its own pool at start-up
+// (a later cudaMalloc fails there, or fragments the pool), or a decode loop
+// that must not meet cudaMalloc / cudaFree at all because those calls
+// synchronise the whole device and stall every other stream.  For them the
+// split-K scratch of the decode kernel lives in the library image itself: one
+// fixed array per GPU that loads the library, sized for the smallest
+// activation tile (M <= 16).  Nothing is allocated on any call.
+namespace llmmm {
+namespace {
+
+constexpr int    NOALLOC_MAX_M = 16;
+constexpr size_t NOALLOC_BYTES = deccfg::COUNTER_BYTES + (size_t)deccfg::MAX_CTAS * 2 * 16 * 128 * sizeof(float);
+
+// 16 KB of arrival counters followed by 256 x 2 partial tiles of 16 x 128 fp32: 4,210,688 bytes.
+static __device__ __align__(256) uint8_t g_noalloc_scratch[NOALLOC_BYTES];
+
+// In host code the array's name is only a handle for the runtime; the device
+// address is looked up once per device (with that device current) and kept.
+uint8_t*   g_noalloc_ptr[64];
+bool       g_noalloc_ready[64];
+std::mutex g_noalloc_mutex;
+
+int noalloc_scratch(const DeviceInfo* info, uint8_t** out)
+{
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_ready[info->device]) {
+    uint8_t*    ptr = nullptr;
+    cudaError_t e   = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      return set_error(LLMMM_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed: %s", cudaGetErrorString(e));
+    }
+    g_noalloc_ptr[info->device]   = ptr;
+    g_noalloc_ready[info->device] = true;
+  }
+  *out = g_noalloc_ptr[info->device];
+  return LLMMM_OK;
+}
+
+}  // namespace
+}  // namespace llmmm
+
+extern "C" int llmmm_fp8_blockwise_mm_e4m3out_noalloc(const void*    A,
+                                                      const float*   A_scale_t,
+                                                      const void*    B_t,
+                                                      const float*   B_scale_t,
+                                                      void*          C,
+                                                      float*         C_scale_t,
+                                                      int            M,
+                                                      int            N,
+                                                      int            K,
+                                                      llmmm_stream_t stream)
+{
+  using namespace llmmm;
+  if (A == nullptr || A_scale_t == nullptr || B_t == nullptr || B_scale_t == nullptr || C == nullptr
+      || C_scale_t == nullptr) {
+    return set_error(LLMMM_ERR_SHAPE, "null pointer argument");
+  }
+  if (N < 128 || K < 128 || (N % 128) != 0 || (K % 128) != 0) {
+    return set_error(LLMMM_ERR_SHAPE, "N or K are not aligned. (need N%%128==0, K%%128==0; got %d %d)", N, K);
+  }
+  if (M < 1 || M > NOALLOC_MAX_M || N / 128 > deccfg::MAX_GROUPS) {
+    return set_error(LLMMM_ERR_SHAPE,
+                     "the entry point without scratch takes 1 <= M <= %d and N <= %d (its built-in scratch is %zu bytes); "
+                     "got M=%d N=%d: use llmmm_fp8_blockwise_mm_e4m3out with a caller-owned workspace",
+                     NOALLOC_MAX_M,
+                     deccfg::MAX_GROUPS * 128,
+                     NOALLOC_BYTES,
+                     M,
+                     N);
+  }
+  if (((uintptr_t)A | (uintptr_t)B_t | (uintptr_t)C) & 15) {
+    return set_error(LLMMM_ERR_SHAPE, "A, B and C must be 16-byte aligned");
+  }
+  const DeviceInfo* info = device_info();
+  if (info == nullptr) {
+    return LLMMM_ERR_UNSUPPORTED;
+  }
+  uint8_t* scratch = nullptr;
+  int      rc      = noalloc_scratch(info, &scratch);
+  if (rc != LLMMM_OK) {
+    return rc;
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left.  Partial tiles are always
+  // written before they are read, but the arrival counters of the groups this
+  // call uses must start at zero.
+  LLMMM_CUDA_TRY(cudaMemsetAsync(scratch, 0, (size_t)(N / 128) * sizeof(uint32_t), s));
+  return launch_decode_t<16, false>(A, A_scale_t, B_t, B_scale_t, C, C_scale_t, M, N, K, scratch, info, s);
+}
+
