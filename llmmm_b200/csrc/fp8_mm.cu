@@ -64,6 +64,32 @@ struct Fp8Bars {
   uint32_t abort_flag;
 };
 
+// acc{0,1} = fma(v{0,1}, sc, acc{0,1}) as one packed instruction (fma.rn.f32x2): the same flop rate as two
+// scalar FMAs but half the issue slots, which the TMA and MMA warps sharing the scheduler need.
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi)
+{
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+
+__device__ __forceinline__ void ffma2(float& d0, float& d1, uint32_t a0, uint32_t a1, uint64_t sc2)
+{
+#ifndef LLMMM_FP8_PACKED_FMA
+  // scalar form (default): measured faster here, the packed form costs registers (aligned pairs)
+  float sc;
+  asm("{\n\t.reg .b32 hi;\n\tmov.b64 {%0, hi}, %1;\n\t}" : "=f"(sc) : "l"(sc2));
+  d0 = __fmaf_rn(__uint_as_float(a0), sc, d0);
+  d1 = __fmaf_rn(__uint_as_float(a1), sc, d1);
+  return;
+#endif
+  uint64_t d, a;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(d0), "f"(d1));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "r"(a0), "r"(a1));
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(sc2));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
+}
+
 template<int REGS>
 __device__ __forceinline__ void setmaxnreg_inc()
 {
@@ -205,7 +231,7 @@ __global__ void __launch_bounds__(fp8cfg::THREADS, 1) fp8_blockwise_gemm_kernel(
       // an L2 hit takes longer than one K-block lasts.  The empty asm pins the first use of a
       // fetched value to the top of its own iteration, so the wait for it is never moved up to
       // the load.
-      constexpr int PREFETCH = 4;
+      constexpr int PREFETCH = 2;
       float         a_pf[PREFETCH], b_pf[PREFETCH];
 #pragma unroll
       for (int j = 0; j < PREFETCH; ++j) {
@@ -224,7 +250,8 @@ __global__ void __launch_bounds__(fp8cfg::THREADS, 1) fp8_blockwise_gemm_kernel(
         float a_cur = a_pf[j], b_cur = b_pf[j];
         asm volatile("" : "+f"(a_cur), "+f"(b_cur));
         // one fp32 rounding of the scale product, as in the reference
-        const float sc = __fmul_rn(a_cur, b_cur);
+        const float    sc  = __fmul_rn(a_cur, b_cur);
+        const uint64_t sc2 = pack_f32x2(sc, sc);
         if (kb + PREFETCH < k_blocks) {
           a_pf[j] = __ldg(a_s + (size_t)(kb + PREFETCH) * M);
           b_pf[j] = __ldg(b_s + kb + PREFETCH);
@@ -237,20 +264,20 @@ __global__ void __launch_bounds__(fp8cfg::THREADS, 1) fp8_blockwise_gemm_kernel(
         tmem_ld_wait();
         tmem_ld_32x32b_x32(t_addr + 32, v1);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          acc[i] = __fmaf_rn(__uint_as_float(v0[i]), sc, acc[i]);
+        for (int i = 0; i < 32; i += 2) {
+          ffma2(acc[i], acc[i + 1], v0[i], v0[i + 1], sc2);
         }
         tmem_ld_wait();
         tmem_ld_32x32b_x32(t_addr + 64, v0);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          acc[32 + i] = __fmaf_rn(__uint_as_float(v1[i]), sc, acc[32 + i]);
+        for (int i = 0; i < 32; i += 2) {
+          ffma2(acc[32 + i], acc[32 + i + 1], v1[i], v1[i + 1], sc2);
         }
         tmem_ld_wait();
         tmem_ld_32x32b_x32(t_addr + 96, v1);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          acc[64 + i] = __fmaf_rn(__uint_as_float(v0[i]), sc, acc[64 + i]);
+        for (int i = 0; i < 32; i += 2) {
+          ffma2(acc[64 + i], acc[64 + i + 1], v0[i], v0[i + 1], sc2);
         }
         tmem_ld_wait();
         // every column of this thread's part of the partial stage has been read
@@ -260,8 +287,8 @@ __global__ void __launch_bounds__(fp8cfg::THREADS, 1) fp8_blockwise_gemm_kernel(
           mbar_arrive(&bars->part_empty[p]);
         }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          acc[96 + i] = __fmaf_rn(__uint_as_float(v1[i]), sc, acc[96 + i]);
+        for (int i = 0; i < 32; i += 2) {
+          ffma2(acc[96 + i], acc[96 + i + 1], v1[i], v1[i + 1], sc2);
         }
         ++it;
       }
@@ -307,6 +334,409 @@ __global__ void __launch_bounds__(fp8cfg::THREADS, 1) fp8_blockwise_gemm_kernel(
   }
 }
 
+// ------------------------------------------------------------ CTA pairs ----
+//
+// The same computation for a cluster of two CTAs that share one 256x256 output
+// tile (tcgen05.mma.cta_group::2), used when M > 128.  CTA r loads its own 128
+// rows of A_q and the 128 B_q rows of the tile's scale group r, so a CTA
+// streams 32 KB per K-block instead of 48 KB (6-stage ring) and its shared
+// memory serves 32 KB of operand reads per K-block instead of 48 KB.  Shared
+// memory bandwidth (TMA writes + MMA reads, about 128 B/clk) is what bounds the
+// single-CTA kernel.  Only the even CTA issues MMAs (256x256x32); both CTAs'
+// loads signal its `full` barrier, its commits arrive on both CTAs' `empty` and
+// `part_full` barriers, and both CTAs' promotion warps release a partial stage
+// by arriving on its `part_empty` barrier.
+#ifdef LLMMM_PROFILE
+// Debug build only: cycle counters of CTA 0 (MMA thread: total, waiting for operands, waiting for a
+// free partial stage; promotion warp 4: waiting for a partial, epilogue), see llmmm_profile_dump8().
+__device__ long long g_prof8[16];
+__device__ long long g_trace8[64][8];  // per K-block of CTA 0: clock64 at the hand-off points
+#define PROF8_T(x) long long x = clock64()
+#define PROF8_ADD(dst, a, b) dst += (b) - (a)
+#else
+#define PROF8_T(x)
+#define PROF8_ADD(dst, a, b)
+#endif
+
+namespace fp8pair {
+constexpr int      BM         = 256;  // per pair; 128 rows per CTA
+constexpr int      BN         = 256;
+constexpr int      BK         = 128;
+constexpr int      UMMA_K     = 32;
+constexpr int      STAGES     = 6;
+constexpr int      THREADS    = 384;
+constexpr int      REGS_CTRL  = 40;
+constexpr int      REGS_PROMO = 232;
+constexpr uint32_t A_BYTES    = 128 * BK;                 // 16 KB: this CTA's rows
+constexpr uint32_t B_BYTES    = 128 * BK;                 // 16 KB: this CTA's half of the tile's columns
+constexpr uint32_t STAGE_TX   = 2 * (A_BYTES + B_BYTES);  // both CTAs' loads land on the leader's barrier
+constexpr uint32_t OFF_A      = 0;
+constexpr uint32_t OFF_B      = OFF_A + STAGES * A_BYTES;
+constexpr uint32_t OFF_BAR    = OFF_B + STAGES * B_BYTES;
+constexpr uint32_t SMEM_BYTES = OFF_BAR + 256 + 1024;
+constexpr uint32_t TMEM_COLS  = 512;  // two partial stages of 256 columns
+}  // namespace fp8pair
+
+struct Fp8PairBars {
+  uint64_t full[fp8pair::STAGES];   // used in the leader CTA
+  uint64_t empty[fp8pair::STAGES];  // both CTAs (multicast commit)
+  uint64_t part_full[2];            // both CTAs (multicast commit)
+  uint64_t part_empty[2];           // used in the leader CTA, 16 arrivals
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+template<bool OUT_F32>
+__global__ void __launch_bounds__(fp8pair::THREADS, 1)
+  fp8_blockwise_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
+                                 const __grid_constant__ CUtensorMap tm_b,
+                                 const float* __restrict__ A_s,
+                                 const float* __restrict__ B_s,
+                                 void* __restrict__ C_out,
+                                 float* __restrict__ C_s,
+                                 int       M,
+                                 int       N,
+                                 int       K,
+                                 uint32_t* status)
+{
+  using namespace fp8pair;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Fp8PairBars*       bars       = reinterpret_cast<Fp8PairBars*>(smem + OFF_BAR);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
+
+  const int      warp    = threadIdx.x >> 5;
+  const int      lane    = threadIdx.x & 31;
+  const uint32_t rank    = cluster_ctarank();
+  const int      pair    = blockIdx.x >> 1;
+  const int      n_pairs = gridDim.x >> 1;
+
+  const int m_tiles   = (M + BM - 1) / BM;
+  const int n_tiles   = (N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int k_blocks  = K / BK;
+  const int n_groups  = N / 128;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int p = 0; p < 2; ++p) {
+      mbar_init(&bars->part_full[p], 1);
+      mbar_init(&bars->part_empty[p], 16);  // 8 promotion warps of each CTA
+    }
+    bars->abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tm_a);
+    prefetch_tmap(&tm_b);
+  }
+  if (warp == 2) {
+    tmem_alloc<TMEM_COLS>(&bars->tmem_base);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp < 4) {
+    setmaxnreg_dec<REGS_CTRL>();
+    if (warp == 0) {
+      // ---------------------------------------------------- TMA producer --
+      if (lane == 0) {
+        uint32_t it = 0;
+        for (int tile = pair; tile < num_tiles; tile += n_pairs) {
+          const int m0 = (tile % m_tiles) * BM + (int)rank * 128;
+          const int n0 = (tile / m_tiles) * BN + (int)rank * 128;
+          for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+            const uint32_t s  = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1;
+            mbar_wait(&bars->empty[s], ph ^ 1, DEV_WAIT_SMEM_EMPTY, abort_flag, status);
+            const uint32_t full_leader = mapa_shared(smem_u32(&bars->full[s]), 0);
+            if (rank == 0) {
+              mbar_arrive_expect_tx(&bars->full[s], STAGE_TX);
+            }
+            tma_load_2d_pair(smem + OFF_A + s * A_BYTES, &tm_a, full_leader, kb * BK, m0);
+            tma_load_2d_pair(smem + OFF_B + s * B_BYTES, &tm_b, full_leader, kb * BK, n0);
+          }
+        }
+      }
+    }
+    else if (warp == 1 || warp == 3) {
+      // ------------------------------------ two MMA issuers (leader only) --
+      // Issuing a tcgen05.mma blocks while the tensor pipe's queue is full, so a single issuing
+      // thread cannot poll the barriers of the next K-block while the current one executes.  Two
+      // threads take alternate K-blocks (each owns one TMEM partial stage): one sits in its
+      // barrier waits while the MMAs of the other run.
+      if (lane == 0 && rank == 0) {
+        constexpr uint32_t idesc = make_idesc(/*e4m3*/ 0, 0, 0, 0, BM, BN);
+        const uint32_t     p     = (warp == 1) ? 0u : 1u;  // partial stage and K-block parity of this thread
+#ifdef LLMMM_PROFILE
+        long long p_full = 0, p_part = 0, p_t0 = clock64();
+        unsigned long long p_g0 = global_timer_ns();
+#endif
+        uint32_t it = 0;
+        for (int tile = pair; tile < num_tiles; tile += n_pairs) {
+          for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+            if ((it & 1) != p) {
+              continue;
+            }
+            const uint32_t s  = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1;
+            const uint32_t pp = (it >> 1) & 1;
+            PROF8_T(c0);
+            mbar_wait(&bars->part_empty[p], pp ^ 1, DEV_WAIT_TMEM_EMPTY, abort_flag, status);
+            PROF8_T(c1);
+            mbar_wait(&bars->full[s], ph, DEV_WAIT_SMEM_FULL, abort_flag, status);
+            PROF8_T(c2);
+            PROF8_ADD(p_part, c0, c1);
+            PROF8_ADD(p_full, c1, c2);
+#ifdef LLMMM_PROFILE
+            if (blockIdx.x == 0 && it < 64) {
+              g_trace8[it][0] = c0;  // MMA thread: starts waiting for the partial stage
+              g_trace8[it][1] = c1;  // partial stage free
+              g_trace8[it][2] = c2;  // operands present
+            }
+#endif
+            tc_fence_after_sync();
+            const uint64_t da = make_smem_desc_sw128(smem_u32(smem + OFF_A + s * A_BYTES), 0, 1024);
+            const uint64_t db = make_smem_desc_sw128(smem_u32(smem + OFF_B + s * B_BYTES), 0, 1024);
+#pragma unroll
+            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+              tc_mma_f8_pair(tmem_base + p * BN, da + (uint64_t)((kk * UMMA_K) >> 4), db + (uint64_t)((kk * UMMA_K) >> 4), idesc, kk != 0);
+            }
+            tc_commit_pair(&bars->empty[s]);
+            tc_commit_pair(&bars->part_full[p]);
+#ifdef LLMMM_PROFILE
+            if (blockIdx.x == 0 && it < 64) {
+              g_trace8[it][3] = clock64();  // MMAs and commits issued
+            }
+#endif
+          }
+        }
+#ifdef LLMMM_PROFILE
+        if (blockIdx.x == 0 && p == 0) {
+          g_prof8[0] = clock64() - p_t0;
+          g_prof8[1] = (long long)(global_timer_ns() - p_g0);
+          g_prof8[2] = 2 * p_full;
+          g_prof8[3] = 2 * p_part;
+          g_prof8[4] = it;
+        }
+#endif
+      }
+    }
+  }
+  else {
+    setmaxnreg_inc<REGS_PROMO>();
+    // ------------------------------------------- promotion + epilogue ----
+#ifdef LLMMM_PROFILE
+    long long p_wait = 0, p_epi = 0, p_p0 = clock64();
+#endif
+    const int      quarter = warp & 3;         // TMEM lane quarter this warp may read
+    const int      half    = (warp - 4) >> 2;  // which 128-column scale group of the tile
+    const uint32_t t_lane  = ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 128);
+    const uint32_t empty_leader[2] = {mapa_shared(smem_u32(&bars->part_empty[0]), 0),
+                                      mapa_shared(smem_u32(&bars->part_empty[1]), 0)};
+    uint32_t it = 0;
+    for (int tile = pair; tile < num_tiles; tile += n_pairs) {
+      const int  m    = (tile % m_tiles) * BM + (int)rank * 128 + quarter * 32 + lane;
+      const int  ng   = (tile / m_tiles) * (BN / 128) + half;  // global 128-column group
+      const bool m_ok = m < M;
+      const bool g_ok = ng < n_groups;
+      const float* a_s = A_s + (m_ok ? m : 0);
+      const float* b_s = B_s + (size_t)(g_ok ? ng : 0) * k_blocks;
+
+      float acc[128];
+#pragma unroll
+      for (int i = 0; i < 128; ++i) {
+        acc[i] = 0.0f;
+      }
+
+      // scale operands are fetched PREFETCH K-blocks ahead (an L2 hit under the TMA traffic takes
+      // longer than one K-block); the empty asm pins their first use to their own iteration
+#ifndef LLMMM_FP8_PREFETCH
+#define LLMMM_FP8_PREFETCH 2
+#endif
+      constexpr int PREFETCH = LLMMM_FP8_PREFETCH;
+      float         a_pf[PREFETCH], b_pf[PREFETCH];
+#pragma unroll
+      for (int j = 0; j < PREFETCH; ++j) {
+        a_pf[j] = (j < k_blocks) ? __ldg(a_s + (size_t)j * M) : 0.0f;
+        b_pf[j] = (j < k_blocks) ? __ldg(b_s + j) : 0.0f;
+      }
+      for (int kb0 = 0; kb0 < k_blocks; kb0 += PREFETCH) {
+#pragma unroll
+        for (int j = 0; j < PREFETCH; ++j) {
+          const int kb = kb0 + j;
+          if (kb >= k_blocks) {
+            break;
+          }
+          const uint32_t p  = it & 1;
+          const uint32_t pp = (it >> 1) & 1;
+          float a_cur = a_pf[j], b_cur = b_pf[j];
+          asm volatile("" : "+f"(a_cur), "+f"(b_cur));
+          // one fp32 rounding of the scale product, as in the reference
+          const float    sc  = __fmul_rn(a_cur, b_cur);
+        const uint64_t sc2 = pack_f32x2(sc, sc);
+          if (kb + PREFETCH < k_blocks) {
+            a_pf[j] = __ldg(a_s + (size_t)(kb + PREFETCH) * M);
+            b_pf[j] = __ldg(b_s + kb + PREFETCH);
+          }
+          PROF8_T(d0);
+          mbar_wait(&bars->part_full[p], pp, DEV_WAIT_TMEM_FULL, abort_flag, status);
+          PROF8_T(d1);
+          PROF8_ADD(p_wait, d0, d1);
+#ifdef LLMMM_PROFILE
+          if (blockIdx.x == 0 && threadIdx.x == 128 && it < 64) {
+            g_trace8[it][4] = d0;  // promotion warp 4: starts waiting for the partial
+            g_trace8[it][5] = d1;  // partial observed
+          }
+#endif
+          tc_fence_after_sync();
+          const uint32_t t_addr = tmem_base + p * BN + t_lane;
+          // two loads in flight; the partial stage is handed back as early as possible
+          uint32_t v0[32], v1[32];
+          tmem_ld_32x32b_x32(t_addr, v0);
+          tmem_ld_32x32b_x32(t_addr + 32, v1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            ffma2(acc[i], acc[i + 1], v0[i], v0[i + 1], sc2);
+          }
+          tmem_ld_32x32b_x32(t_addr + 64, v0);
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            ffma2(acc[32 + i], acc[32 + i + 1], v1[i], v1[i + 1], sc2);
+          }
+          tmem_ld_32x32b_x32(t_addr + 96, v1);
+          tmem_ld_wait();
+          // every column of this thread's part of the partial stage has been read
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            if (rank == 0) {
+              mbar_arrive(&bars->part_empty[p]);
+            }
+            else {
+              mbar_arrive_cluster_relaxed(empty_leader[p]);
+            }
+          }
+#ifdef LLMMM_PROFILE
+          if (blockIdx.x == 0 && threadIdx.x == 128 && it < 64) {
+            g_trace8[it][6] = clock64();  // partial stage handed back
+          }
+#endif
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            ffma2(acc[64 + i], acc[64 + i + 1], v0[i], v0[i + 1], sc2);
+          }
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            ffma2(acc[96 + i], acc[96 + i + 1], v1[i], v1[i + 1], sc2);
+          }
+          ++it;
+        }
+      }
+
+      PROF8_T(e0);
+      if (m_ok && g_ok) {
+        if constexpr (OUT_F32) {
+          float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(C_out) + (size_t)m * N + (size_t)ng * 128);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            dst[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+          }
+        }
+        else {
+          float amax = 0.0f;
+#pragma unroll
+          for (int i = 0; i < 128; ++i) {
+            amax = fmaxf(amax, fabsf(acc[i]));
+          }
+          const float scale     = __fdiv_rn(amax, 448.0f);
+          const float scale_inv = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 0.0f;
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(C_out) + (size_t)m * N + (size_t)ng * 128);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            uint4 o;
+            o.x    = pack_e4m3x4(acc[16 * i + 0] * scale_inv, acc[16 * i + 1] * scale_inv, acc[16 * i + 2] * scale_inv, acc[16 * i + 3] * scale_inv);
+            o.y    = pack_e4m3x4(acc[16 * i + 4] * scale_inv, acc[16 * i + 5] * scale_inv, acc[16 * i + 6] * scale_inv, acc[16 * i + 7] * scale_inv);
+            o.z    = pack_e4m3x4(acc[16 * i + 8] * scale_inv, acc[16 * i + 9] * scale_inv, acc[16 * i + 10] * scale_inv, acc[16 * i + 11] * scale_inv);
+            o.w    = pack_e4m3x4(acc[16 * i + 12] * scale_inv, acc[16 * i + 13] * scale_inv, acc[16 * i + 14] * scale_inv, acc[16 * i + 15] * scale_inv);
+            dst[i] = o;
+          }
+          C_s[(size_t)ng * M + m] = scale;
+        }
+      }
+      PROF8_T(e1);
+      PROF8_ADD(p_epi, e0, e1);
+    }
+#ifdef LLMMM_PROFILE
+    if (blockIdx.x == 0 && threadIdx.x == 128) {
+      g_prof8[8]  = clock64() - p_p0;
+      g_prof8[9]  = p_wait;
+      g_prof8[10] = p_epi;
+      g_prof8[11] = it;
+    }
+#endif
+  }
+
+  // neither CTA may leave while its partner can still signal its barriers or read its tiles
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc<TMEM_COLS>(tmem_base);
+  }
+}
+
+template<bool OUT_F32>
+static int launch_fp8_pair(const void*       A,
+                           const float*      A_s,
+                           const void*       B,
+                           const float*      B_s,
+                           void*             C,
+                           float*            C_s,
+                           int               M,
+                           int               N,
+                           int               K,
+                           const DeviceInfo* info,
+                           cudaStream_t      stream)
+{
+  using namespace fp8pair;
+  CUtensorMap tm_a, tm_b;
+  if (!make_tmap_2d(&tm_a, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)M, (uint64_t)K, BK, 128, CU_TENSOR_MAP_SWIZZLE_128B)
+      || !make_tmap_2d(&tm_b, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, 128, CU_TENSOR_MAP_SWIZZLE_128B)) {
+    return LLMMM_ERR_CUDA;
+  }
+  static thread_local bool attr_set[64] = {};
+  if (!attr_set[info->device]) {
+    LLMMM_CUDA_TRY(cudaFuncSetAttribute(
+      fp8_blockwise_gemm_pair_kernel<OUT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+    attr_set[info->device] = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int pairs = tiles < info->max_pairs ? tiles : info->max_pairs;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim            = dim3(2 * pairs);
+  cfg.blockDim           = dim3(THREADS);
+  cfg.dynamicSmemBytes   = SMEM_BYTES;
+  cfg.stream             = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id               = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs                = attr;
+  cfg.numAttrs             = 1;
+  LLMMM_CUDA_TRY(cudaLaunchKernelEx(
+    &cfg, fp8_blockwise_gemm_pair_kernel<OUT_F32>, tm_a, tm_b, A_s, B_s, C, C_s, M, N, K, info->status));
+  g_launches.fetch_add(1);
+  return LLMMM_OK;
+}
+
 template<bool OUT_F32>
 static int launch_fp8(const void*  A,
                       const float* A_s,
@@ -324,6 +754,11 @@ static int launch_fp8(const void*  A,
   if (info == nullptr) {
     return LLMMM_ERR_UNSUPPORTED;
   }
+#ifndef LLMMM_FP8_NO_PAIR
+  if (M > 128 && info->max_pairs > 0) {
+    return launch_fp8_pair<OUT_F32>(A, A_s, B, B_s, C, C_s, M, N, K, info, stream);
+  }
+#endif
   CUtensorMap tm_a, tm_b;
   if (!make_tmap_2d(&tm_a, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)M, (uint64_t)K, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B)
       || !make_tmap_2d(&tm_b, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B)) {
@@ -361,6 +796,30 @@ static int check_fp8_args(const void* A, const void* A_s, const void* B, const v
 }
 
 }  // namespace llmmm
+
+#ifdef LLMMM_PROFILE
+extern "C" void llmmm_profile_trace8()
+{
+  long long t[64][8];
+  cudaMemcpyFromSymbol(t, llmmm::g_trace8, sizeof(t));
+  const long long t0 = t[8][0];
+  printf("K-block: MMA[wait_part free operands issued] PROMO[wait observed released]  (clk relative)\n");
+  for (int i = 8; i < 24; ++i) {
+    printf("%2d: %6lld %6lld %6lld %6lld | %6lld %6lld %6lld\n", i, t[i][0] - t0, t[i][1] - t0, t[i][2] - t0, t[i][3] - t0,
+           t[i][4] - t0, t[i][5] - t0, t[i][6] - t0);
+  }
+}
+
+extern "C" void llmmm_profile_dump8()
+{
+  long long h[16];
+  cudaMemcpyFromSymbol(h, llmmm::g_prof8, sizeof(h));
+  printf("fp8 pair kernel CTA 0: %.3f GHz, %.1f us, %lld K-blocks, %.0f clk/K-block; MMA thread waits: operands %.0f, "
+         "free partial %.0f clk/K-block; promotion warp 4: total %.0f, waiting for partials %.0f, epilogue %.0f clk/K-block\n",
+         (double)h[0] / h[1], h[1] / 1e3, h[4], (double)h[0] / h[4], (double)h[2] / h[4], (double)h[3] / h[4],
+         (double)h[8] / h[11], (double)h[9] / h[11], (double)h[10] / h[11]);
+}
+#endif
 
 extern "C" {
 

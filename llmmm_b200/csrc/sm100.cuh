@@ -338,6 +338,14 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
+// Arrival without release semantics: for hand-offs whose ordering is already given by
+// tcgen05.wait::ld + tcgen05.fence::before_thread_sync ("I have finished reading TMEM").  A
+// cluster-scope release would wait for every outstanding memory operation of the thread.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr)
+{
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
 __device__ __forceinline__ void cluster_sync_all()
 {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
