@@ -106,6 +106,12 @@ int llmmm_fp8_quant_1x128(const float* x, void* q, float* scale, int M, int K, l
  * (examples/005.fp8.mm.cu:503-544).  Requires rows%128 == 0, cols%128 == 0. */
 int llmmm_fp8_quant_128x128(const float* x, void* q, float* scale, int rows, int cols, llmmm_stream_t stream);
 
+/* dst[N,M] = src[M,N] transposed, elements of 1 byte (e4m3) or 4 bytes (float).
+ * Replaces LLMMM::transpose_matrix__aligned_128<T> (src/base/base.h:8-9, src/base/base.cu:125-155), used
+ * to build B_transposed[N,K] from B[K,N] (examples/005.fp8.mm.cu:2657-2660).  Requires M%128 == 0 and
+ * N%128 == 0 ("M or N can't be divided 128." otherwise), elem_bytes 1 or 4. */
+int llmmm_transpose_aligned_128(void* dst, const void* src, int M, int N, int elem_bytes, llmmm_stream_t stream);
+
 /* Split-K scratch for the decode-sized (M <= 64) FP8 path.  The reference has
  * no split-K (README.md:22 lists it as to do) and its launchers allocate
  * nothing, so the scratch is caller-owned: bytes needed for a given problem,

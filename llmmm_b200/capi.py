@@ -45,6 +45,7 @@ def lib() -> ctypes.CDLL:
         L.llmmm_fp8_blockwise_mm_f32out.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
         L.llmmm_fp8_quant_1x128.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
         L.llmmm_fp8_quant_128x128.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
+        L.llmmm_transpose_aligned_128.argtypes = [_vp, _vp, _i, _i, _i, _vp]
         _lib = L
     return _lib
 
@@ -54,6 +55,7 @@ EXPORTED_SYMBOLS = (
     "llmmm_fp8_blockwise_mm_e4m3out", "llmmm_fp8_blockwise_mm_f32out", "llmmm_fp8_quant_1x128",
     "llmmm_fp8_quant_128x128", "llmmm_fp8_workspace_bytes", "llmmm_set_workspace", "llmmm_check_status",
     "llmmm_launch_count", "llmmm_fp8_blockwise_mm_e4m3out_noalloc",
+    "llmmm_transpose_aligned_128",
 )
 
 
@@ -135,6 +137,14 @@ def fp8_quant_128x128(x, q, scale, rows: int, cols: int, stream=None) -> None:
     with torch.cuda.device(x.device):
         _check(lib().llmmm_fp8_quant_128x128(_dev(x, torch.float32), _dev(q), _dev(scale, torch.float32), rows,
                                              cols, _stream(stream)))
+
+
+def transpose_aligned_128(dst: torch.Tensor, src: torch.Tensor, M: int, N: int, stream=None) -> None:
+    """dst[N,M] = src[M,N]^T for 1- or 4-byte elements (LLMMM::transpose_matrix__aligned_128<T>)."""
+    if dst.dtype != src.dtype:
+        raise RuntimeError("dst and src must have the same dtype")
+    with torch.cuda.device(src.device):
+        _check(lib().llmmm_transpose_aligned_128(_dev(dst), _dev(src), M, N, src.element_size(), _stream(stream)))
 
 
 def fp8_workspace_bytes(M: int, N: int, K: int) -> int:

@@ -40,7 +40,8 @@ constexpr uint32_t W_BYTES       = 128 * BK;
 constexpr int      MAX_CTAS      = 256;
 constexpr int      MAX_GROUPS    = 4096;                 // counters: N <= 524288
 constexpr size_t   COUNTER_BYTES = MAX_GROUPS * sizeof(uint32_t);
-constexpr uint32_t TMEM_COLS     = 128;  // two partial stages of up to 64 columns
+constexpr int      PARTS         = 8;    // TMEM partial stages of 64 columns each
+constexpr uint32_t TMEM_COLS     = 512;
 }  // namespace deccfg
 
 template<int MP>
@@ -55,14 +56,30 @@ struct DecodeSmem {
 struct DecodeBars {
   uint64_t full[deccfg::STAGES];
   uint64_t empty[deccfg::STAGES];
-  uint64_t part_full[2];
-  uint64_t part_empty[2];
+  uint64_t part_full[deccfg::PARTS];
+  uint64_t part_empty[deccfg::PARTS];
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t last_flag;
   uint32_t pad;
   float    amax[4][64];
+  float    inv[64];
 };
+
+#ifdef LLMMM_PROFILE
+// Debug build only: %globaltimer at the phases of CTA 0 (see llmmm_profile_dump_decode()).
+__device__ unsigned long long g_prof_dec[16];
+__device__ unsigned long long g_prof_cta[256][4];  // per CTA: entry, promotion loop done, fix-up done, exit
+__device__ unsigned long long g_prof_fin[256][6];  // last segment: published, counted, reduced, amax, stored
+#define PROFF(i) if (et == 0) g_prof_fin[blockIdx.x][i] = global_timer_ns()
+#else
+#define PROFF(i)
+#endif
+#ifdef LLMMM_PROFILE
+#define PROFD(i) if (blockIdx.x == 0) g_prof_dec[i] = global_timer_ns()
+#else
+#define PROFD(i)
+#endif
 
 __device__ __forceinline__ void epilogue_bar_sync()
 {
@@ -71,7 +88,7 @@ __device__ __forceinline__ void epilogue_bar_sync()
 
 // unit u of the (group, K-block) grid belongs to CTA ((u+1)*G - 1) / U, the
 // largest c with floor(c*U/G) <= u.
-__device__ __forceinline__ int cta_of_unit(long long u, int G, long long U)
+__device__ __forceinline__ int cta_of_unit(uint32_t u, uint32_t G, uint32_t U)
 {
   return (int)(((u + 1) * G - 1) / U);
 }
@@ -99,19 +116,25 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    PROFD(0);
+#ifdef LLMMM_PROFILE
+    g_prof_cta[blockIdx.x][0] = global_timer_ns();
+#endif
+  }
 
   const int       KB      = K / BK;
-  const long long U       = (long long)(N / 128) * KB;
-  const int       G       = gridDim.x;
-  const long long u_begin = ((long long)blockIdx.x * U) / G;
-  const long long u_end   = ((long long)(blockIdx.x + 1) * U) / G;
+  const uint32_t  U       = (uint32_t)(N / 128) * (uint32_t)KB;  // the launcher keeps U * 256 below 2^31
+  const uint32_t  G       = gridDim.x;
+  const uint32_t  u_begin = (blockIdx.x * U) / G;
+  const uint32_t  u_end   = ((blockIdx.x + 1) * U) / G;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&bars->full[s], 1);
       mbar_init(&bars->empty[s], 1);
     }
-    for (int p = 0; p < 2; ++p) {
+    for (int p = 0; p < PARTS; ++p) {
       mbar_init(&bars->part_full[p], 1);
       mbar_init(&bars->part_empty[p], 4);
     }
@@ -127,6 +150,9 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
+  if (threadIdx.x == 0) {
+    PROFD(1);
+  }
 
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer --
@@ -134,9 +160,13 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
       const uint64_t pol_w = policy_evict_first();  // weights are read once
       const uint64_t pol_x = policy_evict_last();   // activations are re-read by every CTA
       uint32_t       it    = 0;
-      for (long long u = u_begin; u < u_end; ++u, ++it) {
-        const int      nb = (int)(u / KB);
-        const int      kb = (int)(u % KB);
+      int nb = (int)(u_begin / (uint32_t)KB);
+      int kb = (int)(u_begin % (uint32_t)KB);
+      for (uint32_t u = u_begin; u < u_end; ++u, ++it, ++kb) {
+        if (kb == KB) {
+          kb = 0;
+          ++nb;
+        }
         const uint32_t s  = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
         mbar_wait(&bars->empty[s], ph ^ 1, DEV_WAIT_SMEM_EMPTY, abort_flag, status);
@@ -151,13 +181,16 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(/*e4m3*/ 0, 0, 0, 0, 128, MP);
       uint32_t           it    = 0;
-      for (long long u = u_begin; u < u_end; ++u, ++it) {
+      for (uint32_t u = u_begin; u < u_end; ++u, ++it) {
         const uint32_t s  = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
-        const uint32_t p  = it & 1;
-        const uint32_t pp = (it >> 1) & 1;
+        const uint32_t p  = it % PARTS;
+        const uint32_t pp = (it / PARTS) & 1;
         mbar_wait(&bars->part_empty[p], pp ^ 1, DEV_WAIT_TMEM_EMPTY, abort_flag, status);
         mbar_wait(&bars->full[s], ph, DEV_WAIT_SMEM_FULL, abort_flag, status);
+        if (it == 0) {
+          PROFD(2);
+        }
         tc_fence_after_sync();
         const uint64_t dw = make_smem_desc_sw128(smem_u32(smem + L::OFF_W + s * W_BYTES), 0, 1024);
         const uint64_t dx = make_smem_desc_sw128(smem_u32(smem + L::OFF_X + s * L::X_BYTES), 0, 1024);
@@ -168,6 +201,7 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
         tc_commit(&bars->empty[s]);
         tc_commit(&bars->part_full[p]);
       }
+      PROFD(3);
     }
   }
   else {
@@ -179,48 +213,62 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
     const uint32_t t_lane  = (uint32_t)(quarter * 32) << 16;
     uint32_t       it      = 0;
 
-    long long u = u_begin;
+    uint32_t u = u_begin;
     while (u < u_end) {
-      const int       nb    = (int)(u / KB);
-      const int       kb0   = (int)(u % KB);
-      const long long left  = u_end - u;
-      const int       kb1   = (left < (long long)(KB - kb0)) ? kb0 + (int)left : KB;
-      const bool      whole = (kb0 == 0 && kb1 == KB);
+      const int      nb   = (int)(u / (uint32_t)KB);
+      const int      kb0  = (int)(u % (uint32_t)KB);
+      const uint32_t left = u_end - u;
+      const int      kb1  = (left < (uint32_t)(KB - kb0)) ? kb0 + (int)left : KB;
+      const bool     whole = (kb0 == 0 && kb1 == KB);
 
       float acc[MP];
 #pragma unroll
       for (int i = 0; i < MP; ++i) {
         acc[i] = 0.0f;
       }
+      // Scale operands: lane l of every warp holds A_s[kb, l] and A_s[kb, 32 + l] (fetched one K-block
+      // ahead) times B_s; column m's product is broadcast with a shuffle where it is used.
+      float a_lo = (lane < M) ? __ldg(A_s + (size_t)kb0 * M + lane) : 0.0f;
+      float a_hi = (MP > 32 && lane + 32 < M) ? __ldg(A_s + (size_t)kb0 * M + 32 + lane) : 0.0f;
+      float b_nx = __ldg(B_s + (size_t)nb * KB + kb0);
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
-        const uint32_t p  = it & 1;
-        const uint32_t pp = (it >> 1) & 1;
-        const float    b  = __ldg(B_s + (size_t)nb * KB + kb);
-        const float*   as = A_s + (size_t)kb * M;
+        const uint32_t p  = it % PARTS;
+        const uint32_t pp = (it / PARTS) & 1;
+        // one fp32 rounding of each scale product, as in the reference
+        const float sc_lo = __fmul_rn(a_lo, b_nx);
+        const float sc_hi = __fmul_rn(a_hi, b_nx);
+        if (kb + 1 < kb1) {
+          a_lo = (lane < M) ? __ldg(A_s + (size_t)(kb + 1) * M + lane) : 0.0f;
+          a_hi = (MP > 32 && lane + 32 < M) ? __ldg(A_s + (size_t)(kb + 1) * M + 32 + lane) : 0.0f;
+          b_nx = __ldg(B_s + (size_t)nb * KB + kb + 1);
+        }
         mbar_wait(&bars->part_full[p], pp, DEV_WAIT_TMEM_FULL, abort_flag, status);
         tc_fence_after_sync();
+        uint32_t v[MP];
 #pragma unroll
         for (int c = 0; c < MP / 16; ++c) {
-          uint32_t v[16];
-          tmem_ld_32x32b_x16(tmem_base + p * 64 + t_lane + c * 16, v);
-          tmem_ld_wait();
-          if (c == MP / 16 - 1) {
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-              mbar_arrive(&bars->part_empty[p]);
-            }
-          }
+          tmem_ld_32x32b_x16(tmem_base + p * 64 + t_lane + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&v[c * 16]));
+        }
+        tmem_ld_wait();
+        // the partial is in registers: hand the stage back before any arithmetic
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&bars->part_empty[p]);
+        }
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int   m  = c * 16 + i;
-            const float a  = (m < M) ? __ldg(as + m) : 0.0f;
-            const float sc = __fmul_rn(a, b);  // one fp32 rounding of the scale product
-            acc[m]         = __fmaf_rn(__uint_as_float(v[i]), sc, acc[m]);
-          }
+        for (int m = 0; m < MP; ++m) {
+          const float sc = __shfl_sync(0xffffffffu, (m < 32) ? sc_lo : sc_hi, m & 31);
+          acc[m]         = __fmaf_rn(__uint_as_float(v[m]), sc, acc[m]);
         }
       }
-      u += (kb1 - kb0);
+      u += (uint32_t)(kb1 - kb0);
+      if (et == 0) {
+        PROFD(4);
+#ifdef LLMMM_PROFILE
+        g_prof_cta[blockIdx.x][1] = global_timer_ns();
+#endif
+      }
 
       bool finish = whole;
       if (!whole) {
@@ -229,12 +277,18 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
         float*    dst  = partials + (size_t)slot * (MP * 128);
 #pragma unroll
         for (int i = 0; i < MP; ++i) {
-          __stcg(dst + i * 128 + n_local, acc[i]);
+          if (i < M) {
+            __stcg(dst + i * 128 + n_local, acc[i]);
+          }
         }
         __threadfence();
         epilogue_bar_sync();
-        const int c_lo = cta_of_unit((long long)nb * KB, G, U);
-        const int c_hi = cta_of_unit((long long)(nb + 1) * KB - 1, G, U);
+        if (et == 0) {
+          PROFD(5);
+        }
+        PROFF(0);
+        const int c_lo = cta_of_unit((uint32_t)nb * (uint32_t)KB, G, U);
+        const int c_hi = cta_of_unit((uint32_t)(nb + 1) * (uint32_t)KB - 1, G, U);
         if (et == 0) {
           const uint32_t old = atomicAdd(&counters[nb], 1u);
           const bool     lst = (old == (uint32_t)(c_hi - c_lo));
@@ -244,6 +298,10 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
           bars->last_flag = lst ? 1u : 0u;
         }
         epilogue_bar_sync();
+        if (et == 0) {
+          PROFD(6);
+        }
+        PROFF(1);
         finish = bars->last_flag != 0;
         if (finish) {
           __threadfence();
@@ -251,18 +309,44 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
           for (int i = 0; i < MP; ++i) {
             acc[i] = 0.0f;
           }
-          for (int c = c_lo; c <= c_hi; ++c) {
-            // CTA c's run begins inside this group (slot 0) unless it began earlier (slot 1)
-            const long long cs  = ((long long)c * U) / G;
-            const int       sl  = c * 2 + ((cs / KB) == nb && (cs % KB) != 0 ? 0 : 1);
-            const float*    src = partials + (size_t)sl * (MP * 128);
+          // Contributors are added in ascending CTA order (the result does not depend on who arrived
+          // last); four contributors' loads are in flight together, since each is an L2 round trip.
+          for (int c0 = c_lo; c0 <= c_hi; c0 += 4) {
+            const float* src[4];
 #pragma unroll
-            for (int i = 0; i < MP; ++i) {
-              acc[i] += __ldcg(src + i * 128 + n_local);
+            for (int j = 0; j < 4; ++j) {
+              const int c = (c0 + j <= c_hi) ? c0 + j : c_hi;
+              // CTA c's run begins inside this group (slot 0) unless it began earlier (slot 1)
+              const uint32_t cs = ((uint32_t)c * U) / G;
+              const int      sl = c * 2 + ((int)(cs / (uint32_t)KB) == nb && (cs % (uint32_t)KB) != 0 ? 0 : 1);
+              src[j]             = partials + (size_t)sl * (MP * 128) + n_local;
+            }
+#pragma unroll
+            for (int i0 = 0; i0 < MP; i0 += 16) {
+              if (i0 < M) {
+                float t[4][16];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                  for (int i = 0; i < 16; ++i) {
+                    t[j][i] = (i0 + i < M) ? __ldcg(src[j] + (i0 + i) * 128) : 0.0f;
+                  }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  if (c0 + j <= c_hi) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                      acc[i0 + i] += t[j][i];
+                    }
+                  }
+                }
+              }
             }
           }
         }
         epilogue_bar_sync();  // last_flag may be rewritten by the next segment
+        PROFF(2);
       }
 
       if (finish) {
@@ -277,44 +361,94 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
           }
         }
         else {
-          // group absmax over the 128 lanes: shuffles inside a warp, then 4 warps through shared memory
+          // group absmax over the 128 lanes: one warp-wide integer max per row (the bit pattern of a
+          // non-negative float orders like the float), then 4 warps through shared memory
 #pragma unroll
           for (int i = 0; i < MP; ++i) {
-            float a = fabsf(acc[i]);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-              a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+            if (i < M) {
+              const uint32_t a = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(acc[i])));
+              if (lane == 0) {
+                bars->amax[ew][i] = __uint_as_float(a);
+              }
             }
-            if (lane == 0) {
-              bars->amax[ew][i] = a;
-            }
+          }
+          epilogue_bar_sync();
+          PROFF(3);
+          // thread i finishes row i's absmax and does the two divisions once for everybody
+          if (et < M) {
+            const float amax = fmaxf(fmaxf(bars->amax[0][et], bars->amax[1][et]), fmaxf(bars->amax[2][et], bars->amax[3][et]));
+            bars->inv[et]    = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 0.0f;
+            C_s[(size_t)nb * M + et] = __fdiv_rn(amax, 448.0f);
           }
           epilogue_bar_sync();
           uint8_t* C = reinterpret_cast<uint8_t*>(C_out);
 #pragma unroll
           for (int i = 0; i < MP; ++i) {
             if (i < M) {
-              const float amax = fmaxf(fmaxf(bars->amax[0][i], bars->amax[1][i]), fmaxf(bars->amax[2][i], bars->amax[3][i]));
-              const float inv  = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 0.0f;
-              C[(size_t)i * N + n_glob] = (uint8_t)__nv_cvt_float_to_fp8(acc[i] * inv, __NV_SATFINITE, __NV_E4M3);
-              if (et == i) {
-                C_s[(size_t)nb * M + i] = __fdiv_rn(amax, 448.0f);
-              }
+              C[(size_t)i * N + n_glob] = (uint8_t)__nv_cvt_float_to_fp8(acc[i] * bars->inv[i], __NV_SATFINITE, __NV_E4M3);
             }
           }
-          epilogue_bar_sync();  // bars->amax is reused by the next segment
+          epilogue_bar_sync();  // bars->amax and bars->inv are reused by the next segment
+          PROFF(4);
         }
       }
     }
+#ifdef LLMMM_PROFILE
+    if (et == 0) {
+      g_prof_cta[blockIdx.x][2] = global_timer_ns();
+    }
+#endif
   }
 
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) {
+    PROFD(7);
+  }
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc<TMEM_COLS>(tmem_base);
   }
+  if (threadIdx.x == 32) {
+    PROFD(8);
+#ifdef LLMMM_PROFILE
+    g_prof_cta[blockIdx.x][3] = global_timer_ns();
+#endif
+  }
 }
+
+#ifdef LLMMM_PROFILE
+extern "C" void llmmm_profile_dump_decode()
+{
+  unsigned long long h[16];
+  unsigned long long c[256][4];
+  cudaMemcpyFromSymbol(c, g_prof_cta, sizeof(c));
+  unsigned long long t0 = ~0ull, t_last_entry = 0, t_loop = 0, t_exit = 0;
+  for (int i = 0; i < 148; ++i) {
+    if (c[i][0] == 0) continue;
+    if (c[i][0] < t0) t0 = c[i][0];
+    if (c[i][0] > t_last_entry) t_last_entry = c[i][0];
+    if (c[i][1] > t_loop) t_loop = c[i][1];
+    if (c[i][3] > t_exit) t_exit = c[i][3];
+  }
+  printf("all CTAs (ns from first entry): last entry %llu, last promotion loop done %llu, last exit %llu\n",
+         t_last_entry - t0, t_loop - t0, t_exit - t0);
+  unsigned long long f[256][6];
+  cudaMemcpyFromSymbol(f, g_prof_fin, sizeof(f));
+  int worst = 0;
+  for (int i = 0; i < 148; ++i) {
+    if (c[i][3] > c[worst][3]) worst = i;
+  }
+  printf("slowest CTA %d (ns from first entry): entry %llu loop done %llu | published %llu counted %llu reduced %llu amax %llu stored %llu | "
+         "roles done %llu exit %llu\n",
+         worst, c[worst][0] - t0, c[worst][1] - t0, f[worst][0] - t0, f[worst][1] - t0, f[worst][2] - t0, f[worst][3] - t0,
+         f[worst][4] - t0, c[worst][2] - t0, c[worst][3] - t0);
+  cudaMemcpyFromSymbol(h, g_prof_dec, sizeof(h));
+  printf("decode CTA 0 (ns from kernel entry): set-up done %llu, first operands %llu, MMAs issued %llu, promotion done %llu, "
+         "partial published %llu, arrival counted %llu, all roles done %llu, TMEM freed %llu\n",
+         h[1] - h[0], h[2] - h[0], h[3] - h[0], h[4] - h[0], h[5] - h[0], h[6] - h[0], h[7] - h[0], h[8] - h[0]);
+}
+#endif
 
 // ------------------------------------------------------------ host side ---
 
@@ -393,7 +527,7 @@ int launch_decode(bool         out_f32,
                   int          K,
                   cudaStream_t stream)
 {
-  if (M > 64 || N / 128 > deccfg::MAX_GROUPS) {
+  if (M > 64 || N / 128 > deccfg::MAX_GROUPS || (long long)(N / 128) * (K / 128) * 256 >= (1ll << 31)) {
     return -1;
   }
   const DeviceInfo* info = device_info();
@@ -519,7 +653,8 @@ extern "C" int llmmm_fp8_blockwise_mm_e4m3out_noalloc(const void*    A,
   if (N < 128 || K < 128 || (N % 128) != 0 || (K % 128) != 0) {
     return set_error(LLMMM_ERR_SHAPE, "N or K are not aligned. (need N%%128==0, K%%128==0; got %d %d)", N, K);
   }
-  if (M < 1 || M > NOALLOC_MAX_M || N / 128 > deccfg::MAX_GROUPS) {
+  if (M < 1 || M > NOALLOC_MAX_M || N / 128 > deccfg::MAX_GROUPS
+      || (long long)(N / 128) * (K / 128) * 256 >= (1ll << 31)) {
     return set_error(LLMMM_ERR_SHAPE,
                      "the entry point without scratch takes 1 <= M <= %d and N <= %d (its built-in scratch is %zu bytes); "
                      "got M=%d N=%d: use llmmm_fp8_blockwise_mm_e4m3out with a caller-owned workspace",
