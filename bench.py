@@ -131,6 +131,7 @@ def reference_arm(args) -> int:
     import numpy as np
     from oracle import oracle as o
     o.build()
+    o.set_num_threads(len(os.sched_getaffinity(0)))  # torchrun exports OMP_NUM_THREADS=1; use every core we may
     cores = o.num_threads()
     rows = 256  # one step = a 256-row slab of the 4096-row problem (about 0.5 s on 8 cores)
     rng = np.random.default_rng(0x4C4D4D4D)
@@ -297,18 +298,13 @@ def main() -> int:
     achieved = FLOP_PER_STEP / (ms_step * 1e-3) / 1e12
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
-        "traffic": None,
+        # dram__bytes_read.sum + dram__bytes_write.sum of this kernel on this workload, one ncu capture
+        # (profiles/fp8_blockwise_gemm_4096.md): 34.13 MB + 0.27 MB
+        "traffic": 34.4e6,
         "peak_source": f"2 x bf16_tflops ({peak_kind}; the file has no fp8 figure; burst, kernel timed alone)",
         "frac_of_nominal_4500": achieved / 4500.0,
         "kernel": "fp8_blockwise_gemm_kernel<false>",
     }
-    prof = ROOT / "profiles" / "fp8_blockwise_gemm_4096.json"
-    if prof.exists():
-        try:
-            roofline["traffic"] = json.loads(prof.read_text()).get("dram_bytes_per_launch")
-        except Exception:  # noqa: BLE001
-            pass
-
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -338,6 +334,7 @@ def cpu_baseline(s0):
     """The oracle's restatement of the reference arithmetic, timed on the host cores on a bounded sample."""
     from oracle import oracle as o
     o.build()
+    o.set_num_threads(len(os.sched_getaffinity(0)))
     rows = 1024
     A_q, A_s, B_q, B_s = (t.cpu().numpy() for t in s0[:4])
     A_q, A_s = A_q[:rows].copy(), A_s[:, :rows].copy()

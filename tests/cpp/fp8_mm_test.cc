@@ -76,6 +76,16 @@ int main(int argc, char** argv)
     }
   }
 
+  // decode-sized problems take the split-K path when the caller registers scratch it owns
+  if (size_t ws_bytes = llmmm_fp8_workspace_bytes(M, N, K)) {
+    void* ws = nullptr;
+    CHECK(cudaMalloc(&ws, ws_bytes));
+    if (llmmm_set_workspace(ws, ws_bytes) != LLMMM_OK) {
+      fprintf(stderr, "llmmm_set_workspace: %s\n", llmmm_last_error());
+      return 1;
+    }
+  }
+
   bool threw = false;
   try {
     fp8_gemm_blockwise_quant_A_1x128__B_128x128__C_1x128__output_fp8__opt_reg(dAq, dAs, dBq, dBs, dCq, dCs, M, N + 64, K, nullptr);
