@@ -318,6 +318,10 @@ def main() -> int:
         "roofline": roofline,
     }
 
+    if world > 1 and not args.no_extra and not args.quick:
+        ns = nsplit_config(torch, dist, capi, dev, rank, world)
+        if rank == 0:
+            line["extra"] = {"mlp7b_gate_up_nsplit": ns}
     if rank == 0 and world == 1 and not args.no_extra and not args.quick:
         line["extra"] = extra_configs(torch, capi, dev, peaks)
     if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.quick:
@@ -409,8 +413,70 @@ def extra_configs(torch, capi, dev, peaks):
             dec.append({"M": m, "N": n, "K": k, "us": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / float(peaks["hbm_gbs"])})
         del ws
     out["qwen3_4b_decode"] = dec
+    # HBM-bound helpers of the same path at 4096 x 4096: the two quantisers (4 B read + 1 B written per element,
+    # plus scales) and the transposes (1 B / 4 B read and written)
+    hbm = float(peaks["hbm_gbs"])
+    x = torch.randn(3, 4096, 4096, device=dev, generator=gen)
+    q = torch.empty(3, 4096, 4096, dtype=torch.uint8, device=dev)
+    s1 = torch.empty(32, 4096, device=dev)
+    s2 = torch.empty(32, 32, device=dev)
+    xt = torch.empty(3, 4096, 4096, device=dev)
+    qt = torch.empty(3, 4096, 4096, dtype=torch.uint8, device=dev)
+    cases = {
+        "quant_1x128": ([lambda i=i: capi.fp8_quant_1x128(x[i], q[i], s1, 4096, 4096) for i in range(3)], 5 * 4096 * 4096 + 4 * 32 * 4096),
+        "quant_128x128": ([lambda i=i: capi.fp8_quant_128x128(x[i], q[i], s2, 4096, 4096) for i in range(3)], 5 * 4096 * 4096 + 4 * 32 * 32),
+        "transpose_f32": ([lambda i=i: capi.transpose_aligned_128(xt[i], x[i], 4096, 4096) for i in range(3)], 8 * 4096 * 4096),
+        "transpose_e4m3": ([lambda i=i: capi.transpose_aligned_128(qt[i], q[i], 4096, 4096) for i in range(3)], 2 * 4096 * 4096),
+    }
+    helpers = {}
+    for name, (fns, nbytes) in cases.items():
+        ms = time_graph(torch, fns * 6)
+        helpers[name] = {"us": ms * 1e3, "gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (ms * 1e-3) / 1e9 / hbm}
+    out["hbm_helpers_4096x4096"] = helpers
     capi.check_status()
     return out
+
+
+def nsplit_config(torch, dist, capi, dev, rank, world):
+    """Config 5 of the task (7B-scale gate_up, M=8192, N=37888, K=3584) N-split over the ranks on 128-column
+    group boundaries, replicated activations: per-rank GEMM time, and the optional NCCL all-gather of C_q / C_s."""
+    from llmmm_b200 import shard
+    Mm, Nn, Kk = 8192, 37888, 3584
+    n0, n1 = shard.split_n(Nn, world, rank)
+    nr = n1 - n0
+    gen = torch.Generator(device=dev).manual_seed(11 + rank)
+    A_q = torch.randint(0, 120, (Mm, Kk), dtype=torch.uint8, device=dev, generator=gen)
+    A_s = torch.rand(Kk // 128, Mm, device=dev, generator=gen)
+    B_q = torch.randint(0, 120, (nr, Kk), dtype=torch.uint8, device=dev, generator=gen)
+    B_s = torch.rand(nr // 128, Kk // 128, device=dev, generator=gen)
+    C_q = torch.empty(Mm, nr, dtype=torch.uint8, device=dev)
+    C_s = torch.empty(nr // 128, Mm, device=dev)
+
+    def gemm():
+        capi.fp8_blockwise_mm(A_q, A_s, B_q, B_s, C_q, C_s, Mm, nr, Kk)
+
+    def timed(fn, n):
+        for _ in range(2):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ms_gemm = timed(gemm, 10)
+    ms_both = timed(lambda: (gemm(), shard.all_gather_c_n(C_q, C_s, Nn)), 5)
+    flops = 2.0 * Mm * Nn * Kk
+    return {"shape": "M=8192 N=37888 K=3584, N-split", "ranks": world, "ms_gemm": ms_gemm,
+            "tflops_gemm_total": flops / (ms_gemm * 1e-3) / 1e12, "ms_gemm_plus_allgather": ms_both,
+            "gathered_bytes_per_rank": Mm * Nn + 4 * (Nn // 128) * Mm}
 
 
 if __name__ == "__main__":

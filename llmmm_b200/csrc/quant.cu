@@ -40,11 +40,11 @@ __device__ __forceinline__ uint32_t quant4(float4 v, float s)
   return lo | (hi << 16);
 }
 
-// One warp quantises 32 consecutive rows of one 128-wide K group: per row the
-// 32 lanes hold one float4 each (a coalesced 512-byte read), the row amax is a
-// warp reduction, and lane r keeps the scale of row r so that the 32 scales
-// leave as one 128-byte store into scale[(K/128), M].
-constexpr int Q1_ROWS  = 32;
+// One warp quantises Q1_ROWS consecutive rows of one 128-wide K group: per row
+// the 32 lanes hold one float4 each (a coalesced 512-byte read, all rows' loads in
+// flight together), the row amax is a warp reduction, and lane r keeps the scale
+// of row r so that the scales leave as one 32-byte sector of scale[(K/128), M].
+constexpr int Q1_ROWS  = 8;
 constexpr int Q1_WARPS = 8;
 
 __global__ void __launch_bounds__(Q1_WARPS * 32)
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(Q1_WARPS * 32)
       }
     }
   }
-  if (m0 + lane < M) {
+  if (lane < Q1_ROWS && m0 + lane < M) {
     scale[(size_t)g * M + m0 + lane] = my_scale;
   }
 }
