@@ -1,0 +1,57 @@
+"""Sharded execution on one GPU: the N-split and M-split shards of a GEMM, run one after the other through the
+C ABI, must reproduce the unsharded run bit for bit (the path has no reduction).  Shapes follow the 7B-scale
+MLP configuration (hidden 3584, gate_up N=37888, down K=18944) at a reduced M so that the oracle can check
+sampled rows; 37888 = 296 groups splits evenly over 8 ranks, 3584 = 28 groups does not (4,4,4,4,3,3,3,3)."""
+import numpy as np
+import pytest
+import torch
+
+from llmmm_b200 import shard
+from test_gpu_fp8 import check_against_oracle, full_size_case
+
+pytestmark = pytest.mark.gpu
+
+
+def run(capi, cuda, A_q, A_s, B_q, B_s):
+    M, K = A_q.shape
+    N = B_q.shape[0]
+    capi.ensure_workspace(M, N, K)
+    Cq = torch.full((M, N), 0xAA, dtype=torch.uint8, device=cuda)
+    Cs = torch.full((N // 128, M), float("nan"), device=cuda)
+    capi.fp8_blockwise_mm(A_q, A_s, B_q.contiguous(), B_s.contiguous(), Cq, Cs, M, N, K)
+    return Cq, Cs
+
+
+@pytest.mark.parametrize("shape,world", [((256, 37888, 3584), 8), ((384, 3584, 18944), 8), ((512, 3584, 2048), 3)])
+def test_n_split_is_bitwise_the_unsharded_result(capi, oracle, cuda, shape, world):
+    M, N, K = shape
+    A_q, A_s, B_q, B_s = full_size_case(capi, cuda, M, N, K, 95, 0.02)
+    full_q, full_s = run(capi, cuda, A_q, A_s, B_q, B_s)
+    for rank in range(world):
+        n0, n1 = shard.split_n(N, world, rank)
+        bq, bs = shard.shard_weights_n(B_q, B_s, world, rank)
+        cq, cs = run(capi, cuda, A_q, A_s, bq, bs)
+        assert torch.equal(cq, full_q[:, n0:n1])
+        assert torch.equal(cs, full_s[n0 // 128:n1 // 128])
+    torch.cuda.synchronize()
+    capi.check_status()
+    # and the unsharded result is right: sampled rows against the CPU oracle
+    hA_q, hA_s, hB_q, hB_s = (t.cpu().numpy() for t in (A_q, A_s, B_q, B_s))
+    Cf = torch.empty(M, N, device=cuda)
+    capi.fp8_blockwise_mm_f32(A_q, A_s, B_q, B_s, Cf, M, N, K)
+    check_against_oracle(oracle, hA_q, hA_s, hB_q, hB_s, full_q.cpu().numpy(), full_s.cpu().numpy(), Cf.cpu().numpy(),
+                         rows=(M - 2, 2))
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_m_split_is_bitwise_the_unsharded_result(capi, cuda, world):
+    M, N, K = 1000, 2560, 4096  # ragged row split; shards of 333/334 and 500 rows
+    A_q, A_s, B_q, B_s = full_size_case(capi, cuda, M, N, K, 96, 0.02)
+    full_q, full_s = run(capi, cuda, A_q, A_s, B_q, B_s)
+    for rank in range(world):
+        m0, m1 = shard.split_m(M, world, rank)
+        aq, as_ = shard.shard_activations_m(A_q, A_s, world, rank)
+        cq, cs = run(capi, cuda, aq, as_, B_q, B_s)
+        assert torch.equal(cq, full_q[m0:m1])
+        assert torch.equal(cs, full_s[:, m0:m1])
+    capi.check_status()
