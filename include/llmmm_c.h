@@ -151,6 +151,13 @@ int llmmm_fp8_blockwise_mm_e4m3out_noalloc(const void*    A,
  * wait that ran out in llmmm_last_error(); the word is cleared. */
 int llmmm_check_status(llmmm_stream_t stream);
 
+/* Failure-detection self-test: runs a one-CTA kernel whose only wait is on a barrier that nothing signals,
+ * with a limit of `limit_us` microseconds, and synchronises.  Returns LLMMM_OK when the kernel gave up the
+ * wait and ran to its normal end; the expiry is then visible through llmmm_check_status(), which returns
+ * LLMMM_ERR_DEVICE_WAIT (code 0x1ff) once and clears the word.  Nothing faults or hangs.  The reference has
+ * no counterpart (its kernels contain no waits on other agents). */
+int llmmm_selftest_wait_expiry(unsigned int limit_us, llmmm_stream_t stream);
+
 /* Number of kernels launched by this library in the calling process. */
 uint64_t llmmm_launch_count(void);
 

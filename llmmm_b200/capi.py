@@ -46,6 +46,7 @@ def lib() -> ctypes.CDLL:
         L.llmmm_fp8_quant_1x128.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
         L.llmmm_fp8_quant_128x128.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
         L.llmmm_transpose_aligned_128.argtypes = [_vp, _vp, _i, _i, _i, _vp]
+        L.llmmm_selftest_wait_expiry.argtypes = [ctypes.c_uint, _vp]
         _lib = L
     return _lib
 
@@ -55,7 +56,7 @@ EXPORTED_SYMBOLS = (
     "llmmm_fp8_blockwise_mm_e4m3out", "llmmm_fp8_blockwise_mm_f32out", "llmmm_fp8_quant_1x128",
     "llmmm_fp8_quant_128x128", "llmmm_fp8_workspace_bytes", "llmmm_set_workspace", "llmmm_check_status",
     "llmmm_launch_count", "llmmm_fp8_blockwise_mm_e4m3out_noalloc",
-    "llmmm_transpose_aligned_128",
+    "llmmm_transpose_aligned_128", "llmmm_selftest_wait_expiry",
 )
 
 

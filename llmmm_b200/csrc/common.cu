@@ -5,6 +5,7 @@
 #include <mutex>
 
 #include "host_common.h"
+#include "sm100.cuh"
 
 namespace llmmm {
 
@@ -187,9 +188,60 @@ bool make_tmap_2d(CUtensorMap*        out,
   return true;
 }
 
+// Self-test of the bounded wait: one CTA waits on an mbarrier that nothing ever signals, with a short
+// limit.  The wait must give up, record its code in the status word and let the kernel end normally.
+__device__ uint32_t g_selftest_reached_end;
+
+__global__ void wait_expiry_selftest_kernel(uint32_t* status, unsigned long long limit_ns, uint32_t* reached_end)
+{
+  __shared__ uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    mbar_wait_limit(&bar, 0, DEV_WAIT_SELFTEST, &abort_flag, status, limit_ns);
+    // a second wait of the same CTA returns at once after the first one gave up
+    mbar_wait_limit(&bar, 0, DEV_WAIT_SELFTEST, &abort_flag, status, limit_ns);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *reached_end = 1;
+  }
+}
+
 }  // namespace llmmm
 
 extern "C" {
+
+int llmmm_selftest_wait_expiry(unsigned int limit_us, llmmm_stream_t stream)
+{
+  using namespace llmmm;
+  const DeviceInfo* info = device_info();
+  if (info == nullptr) {
+    return LLMMM_ERR_UNSUPPORTED;
+  }
+  if (limit_us == 0 || limit_us > 1000000) {
+    return set_error(LLMMM_ERR_SHAPE, "limit_us must be in [1, 1000000]");
+  }
+  uint32_t* reached = nullptr;
+  LLMMM_CUDA_TRY(cudaGetSymbolAddress((void**)&reached, g_selftest_reached_end));
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  LLMMM_CUDA_TRY(cudaMemsetAsync(reached, 0, sizeof(uint32_t), s));
+  wait_expiry_selftest_kernel<<<1, 64, 0, s>>>(info->status, (unsigned long long)limit_us * 1000ull, reached);
+  g_launches.fetch_add(1);
+  LLMMM_CUDA_TRY(cudaGetLastError());
+  LLMMM_CUDA_TRY(cudaStreamSynchronize(s));
+  uint32_t done = 0;
+  LLMMM_CUDA_TRY(cudaMemcpy(&done, reached, sizeof(done), cudaMemcpyDeviceToHost));
+  if (done != 1) {
+    return set_error(LLMMM_ERR_CUDA, "the self-test kernel did not reach its end");
+  }
+  return LLMMM_OK;  // the expiry itself is reported by llmmm_check_status()
+}
 
 const char* llmmm_last_error(void)
 {

@@ -21,6 +21,7 @@ enum : uint32_t {
   DEV_WAIT_TMEM_FULL  = 0x103,
   DEV_WAIT_TMEM_EMPTY = 0x104,
   DEV_WAIT_SPLITK     = 0x105,
+  DEV_WAIT_SELFTEST   = 0x1ff,
 };
 
 // Wall-clock limit of one wait, in nanoseconds of %globaltimer.
@@ -89,8 +90,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
 // abort flag and returns; every later wait of the CTA then returns at once, so
 // the kernel always runs to its normal end (where TMEM is released) and the
 // host reads the status word instead of a hung context.
-__device__ __forceinline__ void
-mbar_wait(uint64_t* bar, uint32_t parity, uint32_t code, volatile uint32_t* abort_flag, uint32_t* status)
+__device__ __forceinline__ void mbar_wait_limit(uint64_t*           bar,
+                                                uint32_t            parity,
+                                                uint32_t            code,
+                                                volatile uint32_t*  abort_flag,
+                                                uint32_t*           status,
+                                                unsigned long long  limit_ns)
 {
   if (mbar_try_wait(bar, parity)) {
     return;
@@ -106,13 +111,19 @@ mbar_wait(uint64_t* bar, uint32_t parity, uint32_t code, volatile uint32_t* abor
       if (t0 == 0) {
         t0 = now;
       }
-      else if (now - t0 > WAIT_LIMIT_NS) {
+      else if (now - t0 > limit_ns) {
         *abort_flag = code;
         atomicCAS(status, 0u, code);
         return;
       }
     }
   }
+}
+
+__device__ __forceinline__ void
+mbar_wait(uint64_t* bar, uint32_t parity, uint32_t code, volatile uint32_t* abort_flag, uint32_t* status)
+{
+  mbar_wait_limit(bar, parity, code, abort_flag, status, WAIT_LIMIT_NS);
 }
 
 // ------------------------------------------------------------------ TMA ---
