@@ -83,7 +83,7 @@ def test_general_kernel_small_shapes(capi, oracle, cuda, shape):
 
 
 @pytest.mark.parametrize("M", [1, 2, 15, 16, 17, 33, 64])
-@pytest.mark.parametrize("NK", [(256, 1024), (384, 128), (2560, 4096)])
+@pytest.mark.parametrize("NK", [(256, 1024), (384, 128), (2560, 4096), (19072, 256), (37888, 128)])
 def test_decode_kernel_ragged_m(capi, oracle, cuda, M, NK):
     N, K = NK
     case = make_case(oracle, 41 + M, M, N, K)
