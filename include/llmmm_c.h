@@ -68,8 +68,9 @@ int llmmm_fp16_mm_bf16(const void* A, const void* B, void* C, int M, int N, int 
  * Replaces the launchers generated at examples/005.fp8.mm.cu:2466-2577, e.g.
  * fp8_gemm_blockwise_quant_A_1x128__B_128x128__C_1x128__output_fp8__opt_reg
  * (same argument order).  Requires N%128 == 0, K%128 == 0; any M >= 1
- * (the reference requires M%128 == 0).  M <= 64 takes the split-K path and
- * needs a workspace (see llmmm_set_workspace). */
+ * (the reference requires M%128 == 0).  M <= 64 takes a split-K path; some
+ * shapes need a caller-owned workspace for it (see llmmm_set_workspace), without
+ * one those shapes run on the general kernel. */
 int llmmm_fp8_blockwise_mm_e4m3out(const void*    A,
                                    const float*   A_scale_t,
                                    const void*    B_t,

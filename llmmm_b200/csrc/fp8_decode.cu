@@ -93,7 +93,13 @@ __device__ __forceinline__ int cta_of_unit(uint32_t u, uint32_t G, uint32_t U)
   return (int)(((u + 1) * G - 1) / U);
 }
 
-template<int MP, bool OUT_F32>
+// CLUSTER = false: stream-K over all weight blocks, partial tiles through the caller's scratch (above).
+// CLUSTER = true : one thread-block cluster per output group; CTA r of the C in the cluster takes the r-th
+//   slice of the group's K range, and the partial tiles are added through distributed shared memory: after
+//   a cluster barrier (every CTA's TMA ring is idle) the other CTAs store their partial into the leader's
+//   ring, a second barrier, and the leader adds them in rank order and runs the epilogue.  No scratch, no
+//   atomics, no global round trips; used when the groups times a cluster size of 2-7 fill the GPU.
+template<int MP, bool OUT_F32, bool CLUSTER>
 __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __grid_constant__ CUtensorMap tm_w,
                                                                         const __grid_constant__ CUtensorMap tm_x,
                                                                         const float* __restrict__ A_s,
@@ -126,8 +132,19 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
   const int       KB      = K / BK;
   const uint32_t  U       = (uint32_t)(N / 128) * (uint32_t)KB;  // the launcher keeps U * 256 below 2^31
   const uint32_t  G       = gridDim.x;
-  const uint32_t  u_begin = (blockIdx.x * U) / G;
-  const uint32_t  u_end   = ((blockIdx.x + 1) * U) / G;
+  uint32_t        c_size  = 1, c_rank = 0;
+  uint32_t        u_begin, u_end;
+  if constexpr (CLUSTER) {
+    asm volatile("mov.u32 %0, %%cluster_nctaid.x;" : "=r"(c_size));
+    c_rank = cluster_ctarank();
+    const uint32_t group = blockIdx.x / c_size;
+    u_begin = group * (uint32_t)KB + (c_rank * (uint32_t)KB) / c_size;
+    u_end   = group * (uint32_t)KB + ((c_rank + 1) * (uint32_t)KB) / c_size;
+  }
+  else {
+    u_begin = (blockIdx.x * U) / G;
+    u_end   = ((blockIdx.x + 1) * U) / G;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -175,6 +192,11 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
         tma_load_2d_hint(smem + L::OFF_X + s * L::X_BYTES, &tm_x, &bars->full[s], kb * BK, 0, pol_x);
       }
     }
+    if constexpr (CLUSTER) {
+      __syncwarp();
+      cluster_sync_all();  // every CTA's ring is idle
+      cluster_sync_all();  // partial tiles have been delivered to the leader
+    }
   }
   else if (warp == 1) {
     // -------------------------------------------------------- MMA issuer --
@@ -203,6 +225,11 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
       }
       PROFD(3);
     }
+    if constexpr (CLUSTER) {
+      __syncwarp();
+      cluster_sync_all();
+      cluster_sync_all();
+    }
   }
   else {
     // ------------------------------------------- promotion + epilogue ----
@@ -213,8 +240,10 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
     const uint32_t t_lane  = (uint32_t)(quarter * 32) << 16;
     uint32_t       it      = 0;
 
-    uint32_t u = u_begin;
-    while (u < u_end) {
+    uint32_t u     = u_begin;
+    bool     first = true;  // a cluster CTA runs its one segment even if it is empty: it owes two cluster barriers
+    while (u < u_end || (CLUSTER && first)) {
+      first = false;
       const int      nb   = (int)(u / (uint32_t)KB);
       const int      kb0  = (int)(u % (uint32_t)KB);
       const uint32_t left = u_end - u;
@@ -271,7 +300,32 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
       }
 
       bool finish = whole;
-      if (!whole) {
+      if constexpr (CLUSTER) {
+        float* red = reinterpret_cast<float*>(smem + L::OFF_W);  // the leader's idle ring: [rank-1][row][n]
+        cluster_sync_all();                                      // all MMAs of all CTAs are done: rings idle
+        if (c_rank != 0) {
+          const uint32_t base = mapa_shared(smem_u32(red + ((size_t)(c_rank - 1) * MP) * 128 + n_local), 0);
+#pragma unroll
+          for (int i = 0; i < MP; ++i) {
+            if (i < M) {
+              asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(base + (uint32_t)i * 512u), "f"(acc[i]) : "memory");
+            }
+          }
+        }
+        cluster_sync_all();  // release/acquire at cluster scope: the stores above are visible to the leader
+        finish = (c_rank == 0);
+        if (finish) {
+          for (uint32_t rr = 1; rr < c_size; ++rr) {  // fixed order: the result does not depend on timing
+#pragma unroll
+            for (int i = 0; i < MP; ++i) {
+              if (i < M) {
+                acc[i] += red[((size_t)(rr - 1) * MP + i) * 128 + n_local];
+              }
+            }
+          }
+        }
+      }
+      else if (!whole) {
         // publish this CTA's partial, then see whether it was the last to arrive
         const int slot = blockIdx.x * 2 + (kb0 == 0 ? 1 : 0);  // run begins inside the group -> slot 0
         float*    dst  = partials + (size_t)slot * (MP * 128);
@@ -495,7 +549,7 @@ static int launch_decode_t(const void*       A,
   static thread_local bool attr_set[64] = {};
   if (!attr_set[info->device]) {
     LLMMM_CUDA_TRY(cudaFuncSetAttribute(
-      fp8_decode_kernel<MP, OUT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM_BYTES));
+      fp8_decode_kernel<MP, OUT_F32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM_BYTES));
     attr_set[info->device] = true;
   }
   const long long U = (long long)(N / 128) * (K / BK);
@@ -505,12 +559,116 @@ static int launch_decode_t(const void*       A,
   }
   uint32_t* counters = static_cast<uint32_t*>(ws);
   float*    partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + COUNTER_BYTES);
-  fp8_decode_kernel<MP, OUT_F32><<<G, THREADS, L::SMEM_BYTES, stream>>>(
+  fp8_decode_kernel<MP, OUT_F32, false><<<G, THREADS, L::SMEM_BYTES, stream>>>(
     tm_w, tm_x, A_s, B_s, C, C_s, M, N, K, partials, counters, info->status);
   g_launches.fetch_add(1);
   LLMMM_CUDA_TRY(cudaGetLastError());
   return LLMMM_OK;
 }
+
+template<int MP, bool OUT_F32>
+static int launch_decode_cluster_t(const void*       A,
+                                   const float*      A_s,
+                                   const void*       B,
+                                   const float*      B_s,
+                                   void*             C,
+                                   float*            C_s,
+                                   int               M,
+                                   int               N,
+                                   int               K,
+                                   int               cluster,
+                                   const DeviceInfo* info,
+                                   cudaStream_t      stream)
+{
+  using namespace deccfg;
+  using L = DecodeSmem<MP>;
+  CUtensorMap tm_w, tm_x;
+  if (!make_tmap_2d(&tm_w, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, 128, CU_TENSOR_MAP_SWIZZLE_128B)
+      || !make_tmap_2d(&tm_x, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)M, (uint64_t)K, BK, MP, CU_TENSOR_MAP_SWIZZLE_128B)) {
+    return LLMMM_ERR_CUDA;
+  }
+  static thread_local bool attr_set[64] = {};
+  if (!attr_set[info->device]) {
+    LLMMM_CUDA_TRY(cudaFuncSetAttribute(
+      fp8_decode_kernel<MP, OUT_F32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM_BYTES));
+    attr_set[info->device] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim            = dim3((unsigned)((N / 128) * cluster));
+  cfg.blockDim           = dim3(THREADS);
+  cfg.dynamicSmemBytes   = L::SMEM_BYTES;
+  cfg.stream             = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id               = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs                = attr;
+  cfg.numAttrs             = 1;
+  float*    no_partials = nullptr;
+  uint32_t* no_counters = nullptr;
+  LLMMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, fp8_decode_kernel<MP, OUT_F32, true>, tm_w, tm_x, A_s, B_s, C, C_s, M, N, K,
+                                    no_partials, no_counters, info->status));
+  g_launches.fetch_add(1);
+  return LLMMM_OK;
+}
+
+namespace {
+// How many clusters of `size` CTAs (one CTA per SM, as the decode kernel needs) the device can hold at once.
+int cluster_capacity(const DeviceInfo* info, int size)
+{
+  static std::mutex mu;
+  static int        cache[64][9];
+  static bool       known[64][9];
+  std::lock_guard<std::mutex> lock(mu);
+  if (!known[info->device][size]) {
+    using L = DecodeSmem<64>;
+    int clusters = 0;
+    if (cudaFuncSetAttribute(fp8_decode_kernel<64, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM_BYTES)
+        == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim            = dim3((unsigned)(size * (info->sm_count / size)));
+      cfg.blockDim           = dim3(deccfg::THREADS);
+      cfg.dynamicSmemBytes   = L::SMEM_BYTES;
+      cudaLaunchAttribute attr[1];
+      attr[0].id               = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = (unsigned)size;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs                = attr;
+      cfg.numAttrs             = 1;
+      if (cudaOccupancyMaxActiveClusters(&clusters, fp8_decode_kernel<64, false, true>, &cfg) != cudaSuccess) {
+        clusters = 0;
+      }
+    }
+    cudaGetLastError();
+    cache[info->device][size] = clusters;
+    known[info->device][size] = true;
+  }
+  return cache[info->device][size];
+}
+
+// Largest allowed cluster size for which every output group gets a resident cluster and every CTA at least
+// one K-block; 0 when the cluster path does not apply (then stream-K with scratch is used).
+int choose_cluster(const DeviceInfo* info, int M, int N, int K)
+{
+  const int groups = N / 128, kb = K / 128;
+  // Remote shared-memory stores are slow (measured: two peers delivering 32 KB each take about 4 us), so the
+  // cluster path is used only while the partial tiles are small: not for M > 32, at most 4 CTAs for M > 16.
+  if (M > 32) {
+    return 0;
+  }
+  const int max_size = (M > 16) ? 4 : 7;
+  for (int size = max_size; size >= 2; --size) {
+    if (kb >= size && groups * size <= info->sm_count && cluster_capacity(info, size) >= groups) {
+      // worth it only if the clusters occupy at least half of the SMs; otherwise stream-K spreads the weight
+      // blocks over all of them
+      return (groups * size * 2 >= info->sm_count) ? size : 0;
+    }
+  }
+  return 0;
+}
+}  // namespace
 
 // Returns -1 when the decode path does not apply (M > 64, too many groups, or
 // no scratch buffer large enough is registered): the caller then uses the
@@ -534,6 +692,18 @@ int launch_decode(bool         out_f32,
   if (info == nullptr) {
     return LLMMM_ERR_UNSUPPORTED;
   }
+  const int mp = padded_m(M);
+  if (const int cluster = choose_cluster(info, M, N, K)) {
+#define LLMMM_DECODE_CLUSTER_CASE(MPV)                                                                                 \
+  if (mp == MPV) {                                                                                                     \
+    return out_f32 ? launch_decode_cluster_t<MPV, true>(A, A_s, B, B_s, C, C_s, M, N, K, cluster, info, stream) :      \
+                     launch_decode_cluster_t<MPV, false>(A, A_s, B, B_s, C, C_s, M, N, K, cluster, info, stream);      \
+  }
+    LLMMM_DECODE_CLUSTER_CASE(16)
+    LLMMM_DECODE_CLUSTER_CASE(32)
+    LLMMM_DECODE_CLUSTER_CASE(64)
+#undef LLMMM_DECODE_CLUSTER_CASE
+  }
   Workspace ws;
   {
     std::lock_guard<std::mutex> lock(g_ws_mutex);
@@ -542,7 +712,6 @@ int launch_decode(bool         out_f32,
   if (ws.ptr == nullptr || ws.bytes < decode_workspace_bytes(M)) {
     return -1;
   }
-  const int mp = padded_m(M);
 #define LLMMM_DECODE_CASE(MPV)                                                                                         \
   if (mp == MPV) {                                                                                                     \
     return out_f32 ? launch_decode_t<MPV, true>(A, A_s, B, B_s, C, C_s, M, N, K, ws.ptr, info, stream) :               \
@@ -677,6 +846,10 @@ extern "C" int llmmm_fp8_blockwise_mm_e4m3out_noalloc(const void*    A,
     return rc;
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (const int cluster = choose_cluster(info, M, N, K)) {
+    // same choice as llmmm_fp8_blockwise_mm_e4m3out makes: the cluster kernel needs no scratch at all
+    return launch_decode_cluster_t<16, false>(A, A_scale_t, B_t, B_scale_t, C, C_scale_t, M, N, K, cluster, info, s);
+  }
   // The array keeps whatever the previous call left.  Partial tiles are always
   // written before they are read, but the arrival counters of the groups this
   // call uses must start at zero.
