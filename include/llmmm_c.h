@@ -113,10 +113,17 @@ int llmmm_fp8_quant_128x128(const float* x, void* q, float* scale, int rows, int
  * N%128 == 0 ("M or N can't be divided 128." otherwise), elem_bytes 1 or 4. */
 int llmmm_transpose_aligned_128(void* dst, const void* src, int M, int N, int elem_bytes, llmmm_stream_t stream);
 
-/* Split-K scratch for the decode-sized (M <= 64) FP8 path.  The reference has
- * no split-K (README.md:22 lists it as to do) and its launchers allocate
- * nothing, so the scratch is caller-owned: bytes needed for a given problem,
- * and registration of a device buffer for the current device.  The buffer is
+/* Split-K scratch.  The reference has no split-K (README.md:22 lists it as to
+ * do) and its launchers allocate nothing, so the scratch is caller-owned: bytes
+ * needed for a given problem, and registration of a device buffer for the
+ * current device.  Two paths use it: the decode-sized (M <= 64) FP8 kernel, and,
+ * for M > 128, the FP8 and FP16/BF16 kernels when their last wave of 256x256
+ * tiles would leave most of the GPU idle: those tiles are then cut along K, the
+ * fp32 partial tiles go through the scratch and are added in a fixed order
+ * (results are bitwise stable from call to call, and differ from the unsplit
+ * ones only by the association of fp32 sums).  llmmm_fp8_workspace_bytes gives
+ * the size for an FP8 problem; for FP16/BF16 pass the same M (any N, K >= 128).
+ * Without registered scratch every shape still runs, unsplit.  The buffer is
  * shared by all later calls on that device; calls that may overlap on the GPU
  * need separate streams AND separate buffers, or must be serialised. */
 size_t llmmm_fp8_workspace_bytes(int M, int N, int K);
@@ -161,6 +168,11 @@ int llmmm_selftest_wait_expiry(unsigned int limit_us, llmmm_stream_t stream);
 
 /* Number of kernels launched by this library in the calling process. */
 uint64_t llmmm_launch_count(void);
+
+/* How many of those launches cut the tiles of their last wave along K (possible for M > 128 once scratch
+ * is registered with llmmm_set_workspace; see there).  A diagnostic: lets a caller see that its scratch
+ * registration took effect.  No counterpart in the reference. */
+uint64_t llmmm_split_launch_count(void);
 
 #ifdef __cplusplus
 }

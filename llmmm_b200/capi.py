@@ -34,6 +34,7 @@ def lib() -> ctypes.CDLL:
         L.llmmm_last_error.restype = ctypes.c_char_p
         L.llmmm_version.restype = ctypes.c_char_p
         L.llmmm_launch_count.restype = ctypes.c_uint64
+        L.llmmm_split_launch_count.restype = ctypes.c_uint64
         L.llmmm_fp8_workspace_bytes.restype = ctypes.c_size_t
         L.llmmm_fp8_workspace_bytes.argtypes = [_i, _i, _i]
         L.llmmm_set_workspace.argtypes = [_vp, ctypes.c_size_t]
@@ -55,7 +56,7 @@ EXPORTED_SYMBOLS = (
     "llmmm_last_error", "llmmm_version", "llmmm_fp16_mm_f16", "llmmm_fp16_mm_bf16",
     "llmmm_fp8_blockwise_mm_e4m3out", "llmmm_fp8_blockwise_mm_f32out", "llmmm_fp8_quant_1x128",
     "llmmm_fp8_quant_128x128", "llmmm_fp8_workspace_bytes", "llmmm_set_workspace", "llmmm_check_status",
-    "llmmm_launch_count", "llmmm_fp8_blockwise_mm_e4m3out_noalloc",
+    "llmmm_launch_count", "llmmm_split_launch_count", "llmmm_fp8_blockwise_mm_e4m3out_noalloc",
     "llmmm_transpose_aligned_128", "llmmm_selftest_wait_expiry",
 )
 
@@ -81,6 +82,11 @@ def _dev(t: torch.Tensor, dtype=None) -> int:
 
 def launch_count() -> int:
     return int(lib().llmmm_launch_count())
+
+
+def split_launch_count() -> int:
+    """Launches so far that cut the tiles of their last wave along K (needs registered scratch)."""
+    return int(lib().llmmm_split_launch_count())
 
 
 def check_status(stream=None) -> None:
@@ -153,6 +159,13 @@ def fp8_workspace_bytes(M: int, N: int, K: int) -> int:
 
 
 _workspaces: dict[int, torch.Tensor] = {}
+
+
+def clear_workspace() -> None:
+    """Unregisters the scratch of the current device (every shape still runs, without split-K)."""
+    torch.cuda.synchronize()
+    _check(lib().llmmm_set_workspace(None, 0))
+    _workspaces.pop(torch.cuda.current_device(), None)
 
 
 def ensure_workspace(M: int, N: int, K: int, device=None) -> None:

@@ -5,6 +5,7 @@
 #include <mutex>
 
 #include "host_common.h"
+#include "pair_walk.cuh"
 #include "sm100.cuh"
 
 namespace llmmm {
@@ -83,6 +84,7 @@ int pair_capacity(int sm_count)
 }  // namespace
 
 std::atomic<uint64_t> g_launches{0};
+std::atomic<uint64_t> g_split_launches{0};
 
 int set_error(int code, const char* fmt, ...)
 {
@@ -213,6 +215,54 @@ __global__ void wait_expiry_selftest_kernel(uint32_t* status, unsigned long long
   }
 }
 
+SplitPlan plan_split(const DeviceInfo* info, int tiles, int k_steps, int fixed, int per_way_x2, int min_gain)
+{
+  const int P = info->max_pairs;
+  SplitPlan plan{};
+  plan.dp_tiles    = tiles;
+  plan.split_s     = 1;
+  plan.split_chunk = k_steps;
+  plan.pairs       = tiles < P ? tiles : P;
+#ifndef LLMMM_NO_SPLIT
+  const Workspace ws         = registered_workspace(info->device);
+  const int       tail_tiles = tiles % P;
+  if (ws.ptr == nullptr || ws.bytes <= WS_HEADER_BYTES || tail_tiles == 0
+      || (size_t)tail_tiles * 16 * sizeof(uint32_t) > WS_SK_COUNTER_BYTES) {
+    return plan;
+  }
+  const long long slots    = (long long)((ws.bytes - WS_HEADER_BYTES) / (SPLIT_SLOT_FLOATS * sizeof(float)));
+  const long long avail    = P < slots ? P : slots;
+  int             max_ways = (int)(avail / tail_tiles);
+  max_ways                 = max_ways < SPLIT_MAX_WAYS ? max_ways : SPLIT_MAX_WAYS;
+  int ways = 0, chunk = k_steps, best = k_steps - min_gain;
+  for (int w = 2; w <= max_ways; ++w) {
+    const int c   = (k_steps + w - 1) / w;
+    const int est = c + fixed + (per_way_x2 * w) / 2;
+    if (est < best) {
+      best  = est;
+      ways  = (k_steps + c - 1) / c;  // no empty chunks
+      chunk = c;
+    }
+  }
+  if (ways >= 2) {
+    g_split_launches.fetch_add(1);
+    plan.dp_tiles    = tiles - tail_tiles;
+    plan.split_s     = ways;
+    plan.split_chunk = chunk;
+    plan.split_pairs = tail_tiles * ways;
+    plan.pairs       = plan.dp_tiles > 0 ? P : plan.split_pairs;
+    plan.counters    = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ws.ptr) + WS_DECODE_COUNTER_BYTES);
+    plan.partials    = reinterpret_cast<float*>(static_cast<uint8_t*>(ws.ptr) + WS_HEADER_BYTES);
+  }
+#endif
+  return plan;
+}
+
+size_t split_workspace_bytes()
+{
+  return WS_HEADER_BYTES + (size_t)SPLIT_MAX_PAIRS * SPLIT_SLOT_FLOATS * sizeof(float);
+}
+
 }  // namespace llmmm
 
 extern "C" {
@@ -251,6 +301,11 @@ const char* llmmm_last_error(void)
 const char* llmmm_version(void)
 {
   return "llmmm-b200 0.1 (sm_100a)";
+}
+
+uint64_t llmmm_split_launch_count(void)
+{
+  return llmmm::g_split_launches.load();
 }
 
 uint64_t llmmm_launch_count(void)

@@ -23,6 +23,7 @@
 #include <type_traits>
 
 #include "host_common.h"
+#include "pair_walk.cuh"
 #include "sm100.cuh"
 
 namespace llmmm {
@@ -305,6 +306,12 @@ __global__ void __launch_bounds__(fp16pair::THREADS, 1)
                         int                                 M,
                         int                                 N,
                         int                                 K,
+                        int                                 dp_tiles,
+                        int                                 split_pairs,
+                        int                                 split_s,
+                        int                                 split_chunk,
+                        float* __restrict__                 sk_partials,
+                        uint32_t* __restrict__              sk_counters,
                         uint32_t*                           status)
 {
   using namespace fp16pair;
@@ -319,10 +326,8 @@ __global__ void __launch_bounds__(fp16pair::THREADS, 1)
   const int      pair     = blockIdx.x >> 1;
   const int      n_pairs  = gridDim.x >> 1;
 
-  const int m_tiles   = (M + BM - 1) / BM;
-  const int n_tiles   = (N + BN - 1) / BN;
-  const int num_tiles = m_tiles * n_tiles;
-  const int k_iters   = (K + BK - 1) / BK;
+  const int m_tiles = (M + BM - 1) / BM;
+  const int k_iters = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -352,10 +357,12 @@ __global__ void __launch_bounds__(fp16pair::THREADS, 1)
     // ------------------------------------------------------ TMA producer --
     if (lane == 0) {
       uint32_t it = 0;
-      for (int tile = pair; tile < num_tiles; tile += n_pairs) {
+      PairWalk walk(pair, n_pairs, k_iters, dp_tiles, split_pairs, split_s, split_chunk);
+      int      tile, kb0, kb1;
+      while (walk.next(tile, kb0, kb1)) {
         const int m0 = (tile % m_tiles) * BM + (int)rank * 128;
         const int n0 = (tile / m_tiles) * BN + (int)rank * 128;
-        for (int kb = 0; kb < k_iters; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s  = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           mbar_wait(&bars->empty[s], ph ^ 1, DEV_WAIT_SMEM_EMPTY, abort_flag, status);
@@ -384,7 +391,9 @@ __global__ void __launch_bounds__(fp16pair::THREADS, 1)
 #else
 #define PROF_T(x)
 #endif
-      for (int tile = pair; tile < num_tiles; tile += n_pairs, ++t) {
+      PairWalk walk(pair, n_pairs, k_iters, dp_tiles, split_pairs, split_s, split_chunk);
+      int      tile, kb0, kb1;
+      for (; walk.next(tile, kb0, kb1); ++t) {
         const uint32_t acc    = t & 1;
         const uint32_t acc_ph = (t >> 1) & 1;
         PROF_T(c0);
@@ -395,7 +404,7 @@ __global__ void __launch_bounds__(fp16pair::THREADS, 1)
 #endif
         tc_fence_after_sync();
         const uint32_t d_addr = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_iters; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s  = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           PROF_T(c2);
@@ -413,7 +422,7 @@ __global__ void __launch_bounds__(fp16pair::THREADS, 1)
                             da + (uint64_t)((kk * UMMA_K * 2) >> 4),
                             db + (uint64_t)((kk * UMMA_K * 128) >> 4),
                             idesc,
-                            (kb | kk) != 0);
+                            (kb != kb0) || (kk != 0));
           }
           tc_commit_pair(&bars->empty[s]);
         }
@@ -436,7 +445,56 @@ __global__ void __launch_bounds__(fp16pair::THREADS, 1)
     uint8_t*       cbuf         = smem + OFF_C + ew * 2 * C_WARP_BUF;
     uint32_t       t            = 0;
     uint32_t       chunk_it     = 0;
-    for (int tile = pair; tile < num_tiles; tile += n_pairs, ++t) {
+    // 64 fp32 values per lane (row `lane`, columns n0 + c*64 ..) -> T, through this warp's swizzled
+    // staging buffer, out with one TMA store
+    auto convert_and_store = [&](const uint32_t(&v0)[32], const uint32_t(&v1)[32], int m0, int n0, int c) {
+      uint8_t* buf = cbuf + (chunk_it & 1) * C_WARP_BUF;
+      if (lane == 0) {
+        tma_store_wait_read<1>();
+      }
+      __syncwarp();
+      uint8_t* row = buf + lane * 128;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 q;
+        q.x = pack2<T>(__uint_as_float(v0[j * 8 + 0]), __uint_as_float(v0[j * 8 + 1]));
+        q.y = pack2<T>(__uint_as_float(v0[j * 8 + 2]), __uint_as_float(v0[j * 8 + 3]));
+        q.z = pack2<T>(__uint_as_float(v0[j * 8 + 4]), __uint_as_float(v0[j * 8 + 5]));
+        q.w = pack2<T>(__uint_as_float(v0[j * 8 + 6]), __uint_as_float(v0[j * 8 + 7]));
+        *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = q;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 q;
+        q.x = pack2<T>(__uint_as_float(v1[j * 8 + 0]), __uint_as_float(v1[j * 8 + 1]));
+        q.y = pack2<T>(__uint_as_float(v1[j * 8 + 2]), __uint_as_float(v1[j * 8 + 3]));
+        q.z = pack2<T>(__uint_as_float(v1[j * 8 + 4]), __uint_as_float(v1[j * 8 + 5]));
+        q.w = pack2<T>(__uint_as_float(v1[j * 8 + 6]), __uint_as_float(v1[j * 8 + 7]));
+        *reinterpret_cast<uint4*>(row + (((j + 4) ^ (lane & 7)) << 4)) = q;
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        const int x = n0 + c * 64;
+        const int y = m0 + ew * 32;
+        if (x < N && y < M) {
+          tma_store_2d(&tm_c, buf, x, y);
+        }
+        tma_store_commit();
+      }
+      ++chunk_it;
+    };
+    auto release_accumulator = [&](uint32_t acc) {
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive_cluster(mapa_shared(smem_u32(&bars->tmem_empty[acc]), 0));
+      }
+    };
+
+    PairWalk walk(pair, n_pairs, k_iters, dp_tiles, split_pairs, split_s, split_chunk);
+    int      tile, kb0, kb1;
+    for (; walk.next(tile, kb0, kb1); ++t) {
       const int      m0     = (tile % m_tiles) * BM + (int)rank * 128;
       const int      n0     = (tile / m_tiles) * BN;
       const uint32_t acc    = t & 1;
@@ -444,55 +502,98 @@ __global__ void __launch_bounds__(fp16pair::THREADS, 1)
       mbar_wait(&bars->tmem_full[acc], acc_ph, DEV_WAIT_TMEM_FULL, abort_flag, status);
       tc_fence_after_sync();
       const uint32_t t_addr = tmem_base + acc * BN + ((uint32_t)(ew * 32) << 16);
+      if (kb1 - kb0 == k_iters) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 64; ++c, ++chunk_it) {
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t v0[32], v1[32];
+          tmem_ld_32x32b_x32(t_addr + c * 64, v0);
+          tmem_ld_32x32b_x32(t_addr + c * 64 + 32, v1);
+          tmem_ld_wait();
+          if (c == BN / 64 - 1) {
+            // the accumulator is drained: tell the leader's MMA thread
+            release_accumulator(acc);
+          }
+          convert_and_store(v0, v1, m0, n0, c);
+        }
+        continue;
+      }
+      // A chunk of a split tile, the last piece of work of this pair.  This warp's 32x256 piece is handled
+      // independently of the other warps: publish the fp32 partial sums (four columns per lane side by
+      // side: 512 contiguous bytes per warp instruction), count the arrival, and if it is the last one
+      // for this piece, add all chunks in the order of their K ranges (this pair's own chunk is still in
+      // tensor memory) and write the tile.  Nothing here waits for another CTA.
+      const int      tt   = tile - dp_tiles;
+      const uint32_t unit = rank * 4 + (uint32_t)ew;
+      constexpr size_t UNIT_FLOAT4 = SPLIT_SLOT_FLOATS / 8 / 4;  // 8 units of 32 rows x 256 columns per slot
+      float4* mine = reinterpret_cast<float4*>(sk_partials + (size_t)pair * SPLIT_SLOT_FLOATS) + unit * UNIT_FLOAT4 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN / 64; ++c) {
         uint32_t v0[32], v1[32];
         tmem_ld_32x32b_x32(t_addr + c * 64, v0);
         tmem_ld_32x32b_x32(t_addr + c * 64 + 32, v1);
         tmem_ld_wait();
-        if (c == BN / 64 - 1) {
-          // the accumulator is drained: tell the leader's MMA thread
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) {
-            mbar_arrive_cluster(mapa_shared(smem_u32(&bars->tmem_empty[acc]), 0));
-          }
-        }
-        uint8_t* buf = cbuf + (chunk_it & 1) * C_WARP_BUF;
-        if (lane == 0) {
-          tma_store_wait_read<1>();
-        }
-        __syncwarp();
-        uint8_t* row = buf + lane * 128;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 q;
-          q.x = pack2<T>(__uint_as_float(v0[j * 8 + 0]), __uint_as_float(v0[j * 8 + 1]));
-          q.y = pack2<T>(__uint_as_float(v0[j * 8 + 2]), __uint_as_float(v0[j * 8 + 3]));
-          q.z = pack2<T>(__uint_as_float(v0[j * 8 + 4]), __uint_as_float(v0[j * 8 + 5]));
-          q.w = pack2<T>(__uint_as_float(v0[j * 8 + 6]), __uint_as_float(v0[j * 8 + 7]));
-          *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = q;
+        for (int j = 0; j < 8; ++j) {
+          __stcg(mine + (c * 16 + j) * 32, make_float4(__uint_as_float(v0[4 * j]), __uint_as_float(v0[4 * j + 1]),
+                                                       __uint_as_float(v0[4 * j + 2]), __uint_as_float(v0[4 * j + 3])));
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 q;
-          q.x = pack2<T>(__uint_as_float(v1[j * 8 + 0]), __uint_as_float(v1[j * 8 + 1]));
-          q.y = pack2<T>(__uint_as_float(v1[j * 8 + 2]), __uint_as_float(v1[j * 8 + 3]));
-          q.z = pack2<T>(__uint_as_float(v1[j * 8 + 4]), __uint_as_float(v1[j * 8 + 5]));
-          q.w = pack2<T>(__uint_as_float(v1[j * 8 + 6]), __uint_as_float(v1[j * 8 + 7]));
-          *reinterpret_cast<uint4*>(row + (((j + 4) ^ (lane & 7)) << 4)) = q;
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          const int x = n0 + c * 64;
-          const int y = m0 + ew * 32;
-          if (x < N && y < M) {
-            tma_store_2d(&tm_c, buf, x, y);
-          }
-          tma_store_commit();
+        for (int j = 0; j < 8; ++j) {
+          __stcg(mine + (c * 16 + 8 + j) * 32, make_float4(__uint_as_float(v1[4 * j]), __uint_as_float(v1[4 * j + 1]),
+                                                           __uint_as_float(v1[4 * j + 2]), __uint_as_float(v1[4 * j + 3])));
         }
       }
+      __threadfence();
+      __syncwarp();
+      uint32_t arrived = 0;
+      if (lane == 0) {
+        arrived = atomicAdd(&sk_counters[tt * 16 + unit], 1u);
+      }
+      arrived = __shfl_sync(0xffffffffu, arrived, 0);
+      if (arrived == (uint32_t)(split_s - 1)) {
+        __threadfence();
+        const int my_chunk = pair % split_s;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t s0[32], s1[32];
+#pragma unroll 1
+          for (int w = 0; w < split_s; ++w) {
+            uint32_t v0[32], v1[32];
+            if (w == my_chunk) {
+              tmem_ld_32x32b_x32(t_addr + c * 64, v0);
+              tmem_ld_32x32b_x32(t_addr + c * 64 + 32, v1);
+              tmem_ld_wait();
+            }
+            else {
+              const float4* src = reinterpret_cast<const float4*>(sk_partials + (size_t)(tt * split_s + w) * SPLIT_SLOT_FLOATS)
+                                  + unit * UNIT_FLOAT4 + lane;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 a = __ldcg(src + (c * 16 + j) * 32);
+                const float4 b = __ldcg(src + (c * 16 + 8 + j) * 32);
+                v0[4 * j]     = __float_as_uint(a.x);
+                v0[4 * j + 1] = __float_as_uint(a.y);
+                v0[4 * j + 2] = __float_as_uint(a.z);
+                v0[4 * j + 3] = __float_as_uint(a.w);
+                v1[4 * j]     = __float_as_uint(b.x);
+                v1[4 * j + 1] = __float_as_uint(b.y);
+                v1[4 * j + 2] = __float_as_uint(b.z);
+                v1[4 * j + 3] = __float_as_uint(b.w);
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              s0[i] = (w == 0) ? v0[i] : __float_as_uint(__uint_as_float(s0[i]) + __uint_as_float(v0[i]));
+              s1[i] = (w == 0) ? v1[i] : __float_as_uint(__uint_as_float(s1[i]) + __uint_as_float(v1[i]));
+            }
+          }
+          convert_and_store(s0, s1, m0, n0, c);
+        }
+        if (lane == 0) {
+          sk_counters[tt * 16 + unit] = 0;  // every launch leaves the counters at zero
+        }
+      }
+      release_accumulator(acc);
     }
     if (lane == 0) {
       tma_store_wait_all<0>();
@@ -528,9 +629,11 @@ static int launch_fp16_pair(const void* A, const void* B, void* C, int M, int N,
     attr_set[info->device] = true;
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  const int pairs = tiles < info->max_pairs ? tiles : info->max_pairs;
+  // estimated cost of a split, in K-steps of 64 (one takes about 0.33 us): publishing a chunk and counting
+  // the arrival about 3 us, reading a chunk back about 1.5 us
+  const SplitPlan plan = plan_split(info, tiles, (K + BK - 1) / BK, /*fixed*/ 10, /*per_way_x2*/ 9, /*min_gain*/ 6);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim            = dim3(2 * pairs);
+  cfg.gridDim            = dim3(2 * plan.pairs);
   cfg.blockDim           = dim3(THREADS);
   cfg.dynamicSmemBytes   = SMEM_BYTES;
   cfg.stream             = stream;
@@ -541,7 +644,9 @@ static int launch_fp16_pair(const void* A, const void* B, void* C, int M, int N,
   attr[0].val.clusterDim.z = 1;
   cfg.attrs                = attr;
   cfg.numAttrs             = 1;
-  LLMMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, fp16_gemm_pair_kernel<T>, tm_a, tm_b, tm_c, M, N, K, info->status));
+  LLMMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, fp16_gemm_pair_kernel<T>, tm_a, tm_b, tm_c, M, N, K, plan.dp_tiles,
+                                    plan.split_pairs, plan.split_s, plan.split_chunk, plan.partials, plan.counters,
+                                    info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
 }

@@ -507,10 +507,7 @@ extern "C" void llmmm_profile_dump_decode()
 // ------------------------------------------------------------ host side ---
 
 namespace {
-struct Workspace {
-  void*  ptr   = nullptr;
-  size_t bytes = 0;
-};
+static_assert(deccfg::COUNTER_BYTES == WS_DECODE_COUNTER_BYTES, "layout of the registered scratch");
 Workspace  g_ws[64];
 std::mutex g_ws_mutex;
 
@@ -522,7 +519,13 @@ int padded_m(int M)
 
 size_t decode_workspace_bytes(int M)
 {
-  return deccfg::COUNTER_BYTES + (size_t)deccfg::MAX_CTAS * 2 * padded_m(M) * 128 * sizeof(float);
+  return WS_HEADER_BYTES + (size_t)deccfg::MAX_CTAS * 2 * padded_m(M) * 128 * sizeof(float);
+}
+
+Workspace registered_workspace(int device)
+{
+  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  return g_ws[device];
 }
 
 template<int MP, bool OUT_F32>
@@ -535,7 +538,8 @@ static int launch_decode_t(const void*       A,
                            int               M,
                            int               N,
                            int               K,
-                           void*             ws,
+                           uint32_t*         counters,
+                           float*            partials,
                            const DeviceInfo* info,
                            cudaStream_t      stream)
 {
@@ -557,8 +561,6 @@ static int launch_decode_t(const void*       A,
   if ((long long)G > U) {
     G = (int)U;
   }
-  uint32_t* counters = static_cast<uint32_t*>(ws);
-  float*    partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + COUNTER_BYTES);
   fp8_decode_kernel<MP, OUT_F32, false><<<G, THREADS, L::SMEM_BYTES, stream>>>(
     tm_w, tm_x, A_s, B_s, C, C_s, M, N, K, partials, counters, info->status);
   g_launches.fetch_add(1);
@@ -704,18 +706,16 @@ int launch_decode(bool         out_f32,
     LLMMM_DECODE_CLUSTER_CASE(64)
 #undef LLMMM_DECODE_CLUSTER_CASE
   }
-  Workspace ws;
-  {
-    std::lock_guard<std::mutex> lock(g_ws_mutex);
-    ws = g_ws[info->device];
-  }
+  const Workspace ws = registered_workspace(info->device);
   if (ws.ptr == nullptr || ws.bytes < decode_workspace_bytes(M)) {
     return -1;
   }
+  uint32_t* counters = static_cast<uint32_t*>(ws.ptr);
+  float*    partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws.ptr) + WS_HEADER_BYTES);
 #define LLMMM_DECODE_CASE(MPV)                                                                                         \
   if (mp == MPV) {                                                                                                     \
-    return out_f32 ? launch_decode_t<MPV, true>(A, A_s, B, B_s, C, C_s, M, N, K, ws.ptr, info, stream) :               \
-                     launch_decode_t<MPV, false>(A, A_s, B, B_s, C, C_s, M, N, K, ws.ptr, info, stream);               \
+    return out_f32 ? launch_decode_t<MPV, true>(A, A_s, B, B_s, C, C_s, M, N, K, counters, partials, info, stream) :   \
+                     launch_decode_t<MPV, false>(A, A_s, B, B_s, C, C_s, M, N, K, counters, partials, info, stream);   \
   }
   LLMMM_DECODE_CASE(16)
   LLMMM_DECODE_CASE(32)
@@ -731,7 +731,13 @@ extern "C" {
 size_t llmmm_fp8_workspace_bytes(int M, int N, int K)
 {
   (void)K;
-  if (M < 1 || M > 64 || N / 128 > llmmm::deccfg::MAX_GROUPS) {
+  if (M < 1 || N < 128) {
+    return 0;
+  }
+  if (M > 128) {
+    return llmmm::split_workspace_bytes();
+  }
+  if (M > 64 || N / 128 > llmmm::deccfg::MAX_GROUPS) {
     return 0;
   }
   return llmmm::decode_workspace_bytes(M);
@@ -745,11 +751,11 @@ int llmmm_set_workspace(void* device_ptr, size_t bytes)
     return LLMMM_ERR_UNSUPPORTED;
   }
   if (device_ptr != nullptr) {
-    if (((uintptr_t)device_ptr & 255) != 0 || bytes < deccfg::COUNTER_BYTES) {
-      return set_error(LLMMM_ERR_SHAPE, "workspace must be 256-byte aligned and at least %zu bytes", deccfg::COUNTER_BYTES);
+    if (((uintptr_t)device_ptr & 255) != 0 || bytes < WS_HEADER_BYTES) {
+      return set_error(LLMMM_ERR_SHAPE, "workspace must be 256-byte aligned and at least %zu bytes", WS_HEADER_BYTES);
     }
     // the arrival counters must start at zero; every launch leaves them at zero again
-    LLMMM_CUDA_TRY(cudaMemset(device_ptr, 0, deccfg::COUNTER_BYTES));
+    LLMMM_CUDA_TRY(cudaMemset(device_ptr, 0, WS_HEADER_BYTES));
   }
   std::lock_guard<std::mutex> lock(g_ws_mutex);
   g_ws[info->device].ptr   = device_ptr;
@@ -854,6 +860,8 @@ extern "C" int llmmm_fp8_blockwise_mm_e4m3out_noalloc(const void*    A,
   // written before they are read, but the arrival counters of the groups this
   // call uses must start at zero.
   LLMMM_CUDA_TRY(cudaMemsetAsync(scratch, 0, (size_t)(N / 128) * sizeof(uint32_t), s));
-  return launch_decode_t<16, false>(A, A_scale_t, B_t, B_scale_t, C, C_scale_t, M, N, K, scratch, info, s);
+  return launch_decode_t<16, false>(A, A_scale_t, B_t, B_scale_t, C, C_scale_t, M, N, K,
+                                    reinterpret_cast<uint32_t*>(scratch),
+                                    reinterpret_cast<float*>(scratch + deccfg::COUNTER_BYTES), info, s);
 }
 

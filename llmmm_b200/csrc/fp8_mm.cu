@@ -31,6 +31,7 @@
 #include <cuda_fp8.h>
 
 #include "host_common.h"
+#include "pair_walk.cuh"
 #include "sm100.cuh"
 
 namespace llmmm {
@@ -351,11 +352,17 @@ __global__ void __launch_bounds__(fp8cfg::THREADS, 1) fp8_blockwise_gemm_kernel(
 // free partial stage; promotion warp 4: waiting for a partial, epilogue), see llmmm_profile_dump8().
 __device__ long long g_prof8[16];
 __device__ long long g_trace8[64][8];  // per K-block of CTA 0: clock64 at the hand-off points
+__device__ unsigned long long g_stamp8[4][16];  // split-tile hand-offs of promotion warp 4 of CTAs 0..3 (ns)
 #define PROF8_T(x) long long x = clock64()
 #define PROF8_ADD(dst, a, b) dst += (b) - (a)
+#define PROF8_STAMP(i)                                                                                                 \
+  if (blockIdx.x < 4 && threadIdx.x == 128) {                                                                          \
+    g_stamp8[blockIdx.x][i] = global_timer_ns();                                                                       \
+  }
 #else
 #define PROF8_T(x)
 #define PROF8_ADD(dst, a, b)
+#define PROF8_STAMP(i)
 #endif
 
 namespace fp8pair {
@@ -365,7 +372,7 @@ constexpr int      BK         = 128;
 constexpr int      UMMA_K     = 32;
 constexpr int      STAGES     = 6;
 constexpr int      THREADS    = 384;
-constexpr int      REGS_CTRL  = 40;
+constexpr int      REGS_CTRL  = 32;  // 32/232 compiles without spills; 40/232 spilt in the promotion loop (+35 % time)
 constexpr int      REGS_PROMO = 232;
 constexpr uint32_t A_BYTES    = 128 * BK;                 // 16 KB: this CTA's rows
 constexpr uint32_t B_BYTES    = 128 * BK;                 // 16 KB: this CTA's half of the tile's columns
@@ -375,6 +382,9 @@ constexpr uint32_t OFF_B      = OFF_A + STAGES * A_BYTES;
 constexpr uint32_t OFF_BAR    = OFF_B + STAGES * B_BYTES;
 constexpr uint32_t SMEM_BYTES = OFF_BAR + 256 + 1024;
 constexpr uint32_t TMEM_COLS  = 512;  // two partial stages of 256 columns
+// split tiles (pair_walk.cuh): a slot holds 16 warp-sized units of 32 rows x 128 columns
+constexpr size_t   SK_UNIT_FLOATS = 32 * 128;
+static_assert(16 * SK_UNIT_FLOATS == SPLIT_SLOT_FLOATS, "one slot per 256x256 tile");
 }  // namespace fp8pair
 
 struct Fp8PairBars {
@@ -397,6 +407,12 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
                                  int       M,
                                  int       N,
                                  int       K,
+                                 int       dp_tiles,
+                                 int       split_pairs,
+                                 int       split_s,
+                                 int       split_chunk,
+                                 float* __restrict__ sk_partials,
+                                 uint32_t* __restrict__ sk_counters,
                                  uint32_t* status)
 {
   using namespace fp8pair;
@@ -411,11 +427,9 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
   const int      pair    = blockIdx.x >> 1;
   const int      n_pairs = gridDim.x >> 1;
 
-  const int m_tiles   = (M + BM - 1) / BM;
-  const int n_tiles   = (N + BN - 1) / BN;
-  const int num_tiles = m_tiles * n_tiles;
-  const int k_blocks  = K / BK;
-  const int n_groups  = N / 128;
+  const int m_tiles  = (M + BM - 1) / BM;
+  const int k_blocks = K / BK;
+  const int n_groups = N / 128;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -446,10 +460,12 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
       // ---------------------------------------------------- TMA producer --
       if (lane == 0) {
         uint32_t it = 0;
-        for (int tile = pair; tile < num_tiles; tile += n_pairs) {
+        PairWalk walk(pair, n_pairs, k_blocks, dp_tiles, split_pairs, split_s, split_chunk);
+        int      tile, kb0, kb1;
+        while (walk.next(tile, kb0, kb1)) {
           const int m0 = (tile % m_tiles) * BM + (int)rank * 128;
           const int n0 = (tile / m_tiles) * BN + (int)rank * 128;
-          for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          for (int kb = kb0; kb < kb1; ++kb, ++it) {
             const uint32_t s  = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1;
             mbar_wait(&bars->empty[s], ph ^ 1, DEV_WAIT_SMEM_EMPTY, abort_flag, status);
@@ -477,12 +493,10 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
         long long p_full = 0, p_part = 0, p_t0 = clock64();
         unsigned long long p_g0 = global_timer_ns();
 #endif
-        uint32_t it = 0;
-        for (int tile = pair; tile < num_tiles; tile += n_pairs) {
-          for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-            if ((it & 1) != p) {
-              continue;
-            }
+        // the MMA threads need no tile identities, only the number of K-blocks this pair works through
+        const uint32_t total = PairWalk(pair, n_pairs, k_blocks, dp_tiles, split_pairs, split_s, split_chunk).total_k_blocks();
+        for (uint32_t it = p; it < total; it += 2) {
+          {
             const uint32_t s  = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1;
             const uint32_t pp = (it >> 1) & 1;
@@ -522,7 +536,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
           g_prof8[1] = (long long)(global_timer_ns() - p_g0);
           g_prof8[2] = 2 * p_full;
           g_prof8[3] = 2 * p_part;
-          g_prof8[4] = it;
+          g_prof8[4] = total;
         }
 #endif
       }
@@ -540,7 +554,10 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
     const uint32_t empty_leader[2] = {mapa_shared(smem_u32(&bars->part_empty[0]), 0),
                                       mapa_shared(smem_u32(&bars->part_empty[1]), 0)};
     uint32_t it = 0;
-    for (int tile = pair; tile < num_tiles; tile += n_pairs) {
+    PairWalk walk(pair, n_pairs, k_blocks, dp_tiles, split_pairs, split_s, split_chunk);
+    int      tile, kb_lo, kb_hi;
+    PROF8_STAMP(0);
+    while (walk.next(tile, kb_lo, kb_hi)) {
       const int  m    = (tile % m_tiles) * BM + (int)rank * 128 + quarter * 32 + lane;
       const int  ng   = (tile / m_tiles) * (BN / 128) + half;  // global 128-column group
       const bool m_ok = m < M;
@@ -563,14 +580,14 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
       float         a_pf[PREFETCH], b_pf[PREFETCH];
 #pragma unroll
       for (int j = 0; j < PREFETCH; ++j) {
-        a_pf[j] = (j < k_blocks) ? __ldg(a_s + (size_t)j * M) : 0.0f;
-        b_pf[j] = (j < k_blocks) ? __ldg(b_s + j) : 0.0f;
+        a_pf[j] = (kb_lo + j < kb_hi) ? __ldg(a_s + (size_t)(kb_lo + j) * M) : 0.0f;
+        b_pf[j] = (kb_lo + j < kb_hi) ? __ldg(b_s + kb_lo + j) : 0.0f;
       }
-      for (int kb0 = 0; kb0 < k_blocks; kb0 += PREFETCH) {
+      for (int kb0 = kb_lo; kb0 < kb_hi; kb0 += PREFETCH) {
 #pragma unroll
         for (int j = 0; j < PREFETCH; ++j) {
           const int kb = kb0 + j;
-          if (kb >= k_blocks) {
+          if (kb >= kb_hi) {
             break;
           }
           const uint32_t p  = it & 1;
@@ -580,7 +597,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
           // one fp32 rounding of the scale product, as in the reference
           const float    sc  = __fmul_rn(a_cur, b_cur);
         const uint64_t sc2 = pack_f32x2(sc, sc);
-          if (kb + PREFETCH < k_blocks) {
+          if (kb + PREFETCH < kb_hi) {
             a_pf[j] = __ldg(a_s + (size_t)(kb + PREFETCH) * M);
             b_pf[j] = __ldg(b_s + kb + PREFETCH);
           }
@@ -628,19 +645,95 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
             g_trace8[it][6] = clock64();  // partial stage handed back
           }
 #endif
+          // The arithmetic on the last two loads must stay behind the hand-back above: the compiler may
+          // move plain FMAs across asm statements, but not asm volatile statements across one another, so
+          // the scale is passed through an empty one.
+          uint64_t sc2_late = sc2;
+          asm volatile("" : "+l"(sc2_late));
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            ffma2(acc[64 + i], acc[64 + i + 1], v0[i], v0[i + 1], sc2);
+            ffma2(acc[64 + i], acc[64 + i + 1], v0[i], v0[i + 1], sc2_late);
           }
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            ffma2(acc[96 + i], acc[96 + i + 1], v1[i], v1[i + 1], sc2);
+            ffma2(acc[96 + i], acc[96 + i + 1], v1[i], v1[i + 1], sc2_late);
           }
           ++it;
         }
       }
 
       PROF8_T(e0);
+      if (kb_hi - kb_lo < k_blocks) {
+        // A chunk of a split tile, the last piece of work of this pair.  This warp's 32x128 piece is handled
+        // independently of the other warps: publish the partial sum (four columns per lane side by side:
+        // a warp writes 512 contiguous bytes per instruction), count the arrival, and if it is the last
+        // one for this piece, add the chunks in the order of their K ranges and finish the tile.  Nothing
+        // here waits for another CTA.
+        const int      tt   = tile - dp_tiles;
+        const uint32_t unit = rank * 8 + (uint32_t)(warp - 4);
+        float4* mine = reinterpret_cast<float4*>(sk_partials + (size_t)pair * SPLIT_SLOT_FLOATS + unit * SK_UNIT_FLOATS) + lane;
+        PROF8_STAMP(1);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          __stcg(mine + i * 32, make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]));
+        }
+        PROF8_STAMP(2);
+        __threadfence();
+        __syncwarp();
+        uint32_t arrived = 0;
+        if (lane == 0) {
+          arrived = atomicAdd(&sk_counters[tt * 16 + unit], 1u);
+        }
+        arrived = __shfl_sync(0xffffffffu, arrived, 0);
+        PROF8_STAMP(4);
+        if (arrived != (uint32_t)(split_s - 1)) {
+          continue;  // another warp finishes this piece
+        }
+        __threadfence();
+        if (split_s == 2) {
+          // two chunks: a + b == b + a bit for bit, so this warp's own chunk can stay in its registers
+          const float4* src = reinterpret_cast<const float4*>(sk_partials + (size_t)(pair ^ 1) * SPLIT_SLOT_FLOATS
+                                                              + unit * SK_UNIT_FLOATS) + lane;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float4 v = __ldcg(src + i * 32);
+            acc[4 * i] += v.x;
+            acc[4 * i + 1] += v.y;
+            acc[4 * i + 2] += v.z;
+            acc[4 * i + 3] += v.w;
+          }
+        }
+        else {
+          for (int c = 0; c < split_s; ++c) {
+            const float4* src = reinterpret_cast<const float4*>(sk_partials + (size_t)(tt * split_s + c) * SPLIT_SLOT_FLOATS
+                                                                + unit * SK_UNIT_FLOATS) + lane;
+            if (c == 0) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const float4 v = __ldcg(src + i * 32);
+                acc[4 * i]     = v.x;
+                acc[4 * i + 1] = v.y;
+                acc[4 * i + 2] = v.z;
+                acc[4 * i + 3] = v.w;
+              }
+            }
+            else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const float4 v = __ldcg(src + i * 32);
+                acc[4 * i] += v.x;
+                acc[4 * i + 1] += v.y;
+                acc[4 * i + 2] += v.z;
+                acc[4 * i + 3] += v.w;
+              }
+            }
+          }
+        }
+        if (lane == 0) {
+          sk_counters[tt * 16 + unit] = 0;  // every launch leaves the counters at zero
+        }
+        PROF8_STAMP(5);
+      }
       if (m_ok && g_ok) {
         if constexpr (OUT_F32) {
           float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(C_out) + (size_t)m * N + (size_t)ng * 128);
@@ -672,6 +765,9 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
       }
       PROF8_T(e1);
       PROF8_ADD(p_epi, e0, e1);
+      if (kb_hi - kb_lo < k_blocks) {
+        PROF8_STAMP(6);
+      }
     }
 #ifdef LLMMM_PROFILE
     if (blockIdx.x == 0 && threadIdx.x == 128) {
@@ -718,10 +814,13 @@ static int launch_fp8_pair(const void*       A,
       fp8_blockwise_gemm_pair_kernel<OUT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
     attr_set[info->device] = true;
   }
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  const int pairs = tiles < info->max_pairs ? tiles : info->max_pairs;
+  const int tiles    = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int k_blocks = K / BK;
+  // estimated cost of a split, in K-blocks (one takes about 0.58 us): publishing a chunk and counting the
+  // arrival about 3 us, reading a chunk back about 1.5 us
+  const SplitPlan plan = plan_split(info, tiles, k_blocks, /*fixed*/ 4, /*per_way_x2*/ 5, /*min_gain*/ 3);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim            = dim3(2 * pairs);
+  cfg.gridDim            = dim3(2 * plan.pairs);
   cfg.blockDim           = dim3(THREADS);
   cfg.dynamicSmemBytes   = SMEM_BYTES;
   cfg.stream             = stream;
@@ -733,7 +832,8 @@ static int launch_fp8_pair(const void*       A,
   cfg.attrs                = attr;
   cfg.numAttrs             = 1;
   LLMMM_CUDA_TRY(cudaLaunchKernelEx(
-    &cfg, fp8_blockwise_gemm_pair_kernel<OUT_F32>, tm_a, tm_b, A_s, B_s, C, C_s, M, N, K, info->status));
+    &cfg, fp8_blockwise_gemm_pair_kernel<OUT_F32>, tm_a, tm_b, A_s, B_s, C, C_s, M, N, K, plan.dp_tiles,
+    plan.split_pairs, plan.split_s, plan.split_chunk, plan.partials, plan.counters, info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
 }
@@ -808,6 +908,18 @@ extern "C" void llmmm_profile_trace8()
   for (int i = 8; i < 24; ++i) {
     printf("%2d: %6lld %6lld %6lld %6lld | %6lld %6lld %6lld\n", i, t[i][0] - t0, t[i][1] - t0, t[i][2] - t0, t[i][3] - t0,
            t[i][4] - t0, t[i][5] - t0, t[i][6] - t0);
+  }
+}
+
+extern "C" void llmmm_profile_stamps8()
+{
+  unsigned long long t[4][16];
+  cudaMemcpyFromSymbol(t, llmmm::g_stamp8, sizeof(t));
+  for (int b = 0; b < 4; ++b) {
+    printf("CTA %d warp 4 (ns from start of its role): chunk done %lld, published %lld, all work done %lld, arrival counted %lld, "
+           "chunks summed %lld, epilogue done %lld\n", b, (long long)(t[b][1] - t[b][0]), (long long)(t[b][2] - t[b][0]),
+           (long long)(t[b][3] - t[b][0]), (long long)(t[b][4] - t[b][0]), (long long)(t[b][5] - t[b][0]),
+           (long long)(t[b][6] - t[b][0]));
   }
 }
 

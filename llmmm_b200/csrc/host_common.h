@@ -15,6 +15,8 @@ namespace llmmm {
 
 // Kernels launched by this library in this process (llmmm_launch_count()).
 extern std::atomic<uint64_t> g_launches;
+// ... and how many of them cut the tiles of their last wave along K (llmmm_split_launch_count()).
+extern std::atomic<uint64_t> g_split_launches;
 
 // Records a message for llmmm_last_error() and returns `code`.
 int set_error(int code, const char* fmt, ...);
@@ -57,6 +59,22 @@ int launch_decode(bool         out_f32,
                   int          N,
                   int          K,
                   cudaStream_t stream);
+
+// Caller-owned scratch registered with llmmm_set_workspace() for a device.  Layout: arrival counters of
+// the decode kernel, arrival counters of the split tiles of the general FP8 kernel (both zero between
+// launches), then the partial tiles of whichever kernel runs.
+constexpr size_t WS_DECODE_COUNTER_BYTES = 16384;
+constexpr size_t WS_SK_COUNTER_BYTES     = 16384;
+constexpr size_t WS_HEADER_BYTES         = WS_DECODE_COUNTER_BYTES + WS_SK_COUNTER_BYTES;
+
+struct Workspace {
+  void*  ptr   = nullptr;
+  size_t bytes = 0;
+};
+Workspace registered_workspace(int device);
+
+// Scratch the pair kernels want for splitting the tiles of their last wave (pair_walk.cuh).
+size_t split_workspace_bytes();
 
 #define LLMMM_CUDA_TRY(call)                                                                                           \
   do {                                                                                                                 \

@@ -15,7 +15,13 @@ pytestmark = pytest.mark.gpu
 REL_TOL = 1e-3
 
 
-def run_case(capi, oracle, cuda, M, N, K, dtype, seed, rows=None):
+def run_case(capi, oracle, cuda, M, N, K, dtype, seed, rows=None, scratch=None):
+    """scratch: None = whatever is registered, False = none (whole tiles only), True = registered (the
+    tiles of a partly filled last wave are cut along K)."""
+    if scratch is True:
+        capi.ensure_workspace(M, max(N, 128), max(K, 128))
+    elif scratch is False:
+        capi.clear_workspace()
     A, B = fp16_inputs(seed, M, N, K)
     if dtype == torch.float16:
         Ar, Br = oracle.from_f16_bits(oracle.to_f16_bits(A)), oracle.from_f16_bits(oracle.to_f16_bits(B))
@@ -67,10 +73,47 @@ def test_edge_and_ragged_shapes(capi, oracle, cuda, shape):
     run_case(capi, oracle, cuda, M, N, K, torch.float16, seed=1)
 
 
+# Shapes whose last wave of 256x256 tiles is cut along K when scratch is registered: few tiles with a long
+# K, ragged M / N, a K that is not a multiple of the 64-wide K-step, full waves followed by a partial one.
+SPLIT_SHAPES = [(256, 512, 4096), (384, 640, 4096), (300, 1288, 3592), (2304, 4352, 4096)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", SPLIT_SHAPES)
+def test_split_last_wave(capi, oracle, cuda, shape, dtype):
+    M, N, K = shape
+    rows = None if M <= 512 else [(M - 300, 300)]
+    n0 = capi.split_launch_count()
+    run_case(capi, oracle, cuda, M, N, K, dtype, seed=5, rows=rows, scratch=False)
+    assert capi.split_launch_count() == n0
+    run_case(capi, oracle, cuda, M, N, K, dtype, seed=5, rows=rows, scratch=True)
+    assert capi.split_launch_count() == n0 + 1
+
+
+def test_split_is_bitwise_stable(capi, cuda):
+    # arrival counters reset themselves and the chunks are added in a fixed order
+    M, N, K = 384, 640, 4096
+    g = torch.Generator(device=cuda).manual_seed(6)
+    A = torch.randn(M, K, device=cuda, generator=g).half()
+    B = torch.randn(K, N, device=cuda, generator=g).half()
+    capi.ensure_workspace(M, N, K)
+    outs = []
+    n0 = capi.split_launch_count()
+    for _ in range(5):
+        C = torch.empty(M, N, dtype=torch.float16, device=cuda)
+        capi.fp16_mm(A, B, C, M, N, K)
+        outs.append(C)
+    torch.cuda.synchronize()
+    capi.check_status()
+    assert capi.split_launch_count() == n0 + 5
+    for C in outs[1:]:
+        assert torch.equal(C, outs[0])
+
+
 def test_config1_4096_cubed_sampled(capi, oracle, cuda):
     # full size; 64 whole rows spread over the tiles plus the last row are checked on the CPU
     rows = [(r, 8) for r in (0, 120, 127 + 1, 1000, 2048 + 64, 3333, 4000, 4088)]
-    run_case(capi, oracle, cuda, 4096, 4096, 4096, torch.float16, seed=2, rows=rows)
+    run_case(capi, oracle, cuda, 4096, 4096, 4096, torch.float16, seed=2, rows=rows, scratch=True)
 
 
 def test_full_size_linearity_and_identity(capi, cuda):

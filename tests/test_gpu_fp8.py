@@ -103,8 +103,7 @@ def test_qwen3_4b_decode_shapes(capi, oracle, cuda, M, NK):
 def test_decode_without_workspace_uses_general_kernel(capi, oracle, cuda):
     # no scratch registered -> the library must still compute (general kernel), never fail or fall back to a CPU
     case = make_case(oracle, 42, 16, 512, 1024)
-    assert capi.lib().llmmm_set_workspace(None, 0) == 0
-    capi._workspaces.clear()
+    capi.clear_workspace()
     gq, gs, gf = gpu_mm(capi, cuda, *case, workspace=False)
     check_against_oracle(oracle, *case, gq, gs, gf)
     gq2, gs2, gf2 = gpu_mm(capi, cuda, *case, workspace=True)
@@ -129,6 +128,33 @@ def test_decode_repeated_calls_are_bitwise_stable(capi, oracle, cuda):
     for Cq, Cs in outs[1:]:
         assert torch.equal(Cq, outs[0][0]) and torch.equal(Cs, outs[0][1])
     capi.check_status()
+
+
+# Shapes whose last wave of 256x256 tiles is shared out K-block by K-block when scratch is registered:
+# few tiles with a long K (every tile has many contributors), ragged M and N, and several full waves
+# followed by a partial one.
+SPLIT_SHAPES = [(256, 512, 4096), (384, 640, 4096), (300, 1280, 3584), (1024, 2048, 4096), (2304, 4352, 4096)]
+
+
+@pytest.mark.parametrize("shape", SPLIT_SHAPES)
+def test_split_last_wave(capi, oracle, cuda, shape):
+    M, N, K = shape
+    case = make_case(oracle, 44, M, N, K)
+    rows = None if M <= 1024 else (M - 700, 700)
+    capi.clear_workspace()
+    n0 = capi.split_launch_count()
+    gq, gs, gf = gpu_mm(capi, cuda, *case, workspace=False)
+    assert capi.split_launch_count() == n0
+    check_against_oracle(oracle, *case, gq, gs, gf, rows=rows)
+    gq2, gs2, gf2 = gpu_mm(capi, cuda, *case, workspace=True)
+    # the split does take place for these shapes (both entry points), otherwise this test checks nothing
+    assert capi.split_launch_count() == n0 + 2
+    check_against_oracle(oracle, *case, gq2, gs2, gf2, rows=rows)
+    # splitting changes only the order of the fp32 promotion sums
+    assert np.abs(gf - gf2).max() <= 4e-6 * np.abs(gf).max()
+    # bitwise stable from call to call: counters reset themselves, pieces are added in a fixed order
+    gq3, gs3, gf3 = gpu_mm(capi, cuda, *case, workspace=True)
+    assert np.array_equal(gq2, gq3) and np.array_equal(gs2.view(np.uint32), gs3.view(np.uint32)) and np.array_equal(gf2, gf3)
 
 
 def gpu_c_quant(acc):
@@ -160,6 +186,7 @@ def full_size_case(capi, cuda, M, N, K, seed, w_std):
 def test_full_size_properties_and_sampled_rows(capi, oracle, cuda, shape):
     M, N, K, w_std = shape
     A_q, A_s, B_q, B_s = full_size_case(capi, cuda, M, N, K, 60, w_std)
+    capi.ensure_workspace(M, N, K)
     Cq = torch.full((M, N), 0xAA, dtype=torch.uint8, device=cuda)
     Cs = torch.full((N // 128, M), float("nan"), device=cuda)
     Cf = torch.full((M, N), float("nan"), device=cuda)
