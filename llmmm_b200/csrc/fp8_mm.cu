@@ -65,30 +65,12 @@ struct Fp8Bars {
   uint32_t abort_flag;
 };
 
-// acc{0,1} = fma(v{0,1}, sc, acc{0,1}) as one packed instruction (fma.rn.f32x2): the same flop rate as two
-// scalar FMAs but half the issue slots, which the TMA and MMA warps sharing the scheduler need.
-__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi)
+// acc{0,1} = fma(v{0,1}, sc, acc{0,1}).  Two scalar FMAs: the packed fma.rn.f32x2 has the same flop rate
+// and was measured slower here (aligned register pairs cost registers in a loop that has none to spare).
+__device__ __forceinline__ void ffma2(float& d0, float& d1, uint32_t a0, uint32_t a1, float sc)
 {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-
-__device__ __forceinline__ void ffma2(float& d0, float& d1, uint32_t a0, uint32_t a1, uint64_t sc2)
-{
-#ifndef LLMMM_FP8_PACKED_FMA
-  // scalar form (default): measured faster here, the packed form costs registers (aligned pairs)
-  float sc;
-  asm("{\n\t.reg .b32 hi;\n\tmov.b64 {%0, hi}, %1;\n\t}" : "=f"(sc) : "l"(sc2));
   d0 = __fmaf_rn(__uint_as_float(a0), sc, d0);
   d1 = __fmaf_rn(__uint_as_float(a1), sc, d1);
-  return;
-#endif
-  uint64_t d, a;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(d0), "f"(d1));
-  asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "r"(a0), "r"(a1));
-  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(sc2));
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
 }
 
 template<int REGS>
@@ -252,7 +234,7 @@ __global__ void __launch_bounds__(fp8cfg::THREADS, 1) fp8_blockwise_gemm_kernel(
         asm volatile("" : "+f"(a_cur), "+f"(b_cur));
         // one fp32 rounding of the scale product, as in the reference
         const float    sc  = __fmul_rn(a_cur, b_cur);
-        const uint64_t sc2 = pack_f32x2(sc, sc);
+        const float    sc2 = sc;
         if (kb + PREFETCH < k_blocks) {
           a_pf[j] = __ldg(a_s + (size_t)(kb + PREFETCH) * M);
           b_pf[j] = __ldg(b_s + kb + PREFETCH);
@@ -596,7 +578,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
           asm volatile("" : "+f"(a_cur), "+f"(b_cur));
           // one fp32 rounding of the scale product, as in the reference
           const float    sc  = __fmul_rn(a_cur, b_cur);
-        const uint64_t sc2 = pack_f32x2(sc, sc);
+        const float    sc2 = sc;
           if (kb + PREFETCH < kb_hi) {
             a_pf[j] = __ldg(a_s + (size_t)(kb + PREFETCH) * M);
             b_pf[j] = __ldg(b_s + kb + PREFETCH);
@@ -648,8 +630,8 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
           // The arithmetic on the last two loads must stay behind the hand-back above: the compiler may
           // move plain FMAs across asm statements, but not asm volatile statements across one another, so
           // the scale is passed through an empty one.
-          uint64_t sc2_late = sc2;
-          asm volatile("" : "+l"(sc2_late));
+          float sc2_late = sc2;
+          asm volatile("" : "+f"(sc2_late));
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             ffma2(acc[64 + i], acc[64 + i + 1], v0[i], v0[i + 1], sc2_late);
