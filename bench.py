@@ -308,8 +308,8 @@ def main() -> int:
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
         # dram__bytes_read.sum + dram__bytes_write.sum of this kernel on this workload, one ncu capture
-        # (profiles/fp8_blockwise_gemm_4096.md): 34.13 MB + 0.27 MB
-        "traffic": 34.4e6,
+        # (profiles/fp8_blockwise_gemm_4096.md): 34.17 MB + 2.56 MB
+        "traffic": 36.7e6,
         "peak_source": f"2 x bf16_tflops ({peak_kind}; the file has no fp8 figure; burst, kernel timed alone)",
         "frac_of_nominal_4500": achieved / 4500.0,
         "kernel": "fp8_blockwise_gemm_pair_kernel<false>",

@@ -21,6 +21,22 @@ FLAGS = [
 ]
 
 
+# Kernels whose hot loop has no register to spare: the build fails if ptxas reports spills for them.
+NO_SPILL = ("fp8_blockwise_gemm",)
+
+
+def spilling_kernels(ptxas_log: str, patterns: tuple[str, ...]) -> list[str]:
+    """Entry functions matching `patterns` for which `-Xptxas -v` reports spill stores or loads."""
+    bad, current = [], None
+    for line in ptxas_log.splitlines():
+        if "Compiling entry function" in line or "Function properties for" in line:
+            current = line.split("'")[1] if "'" in line else line.rsplit(" ", 1)[-1]
+        elif "bytes spill stores" in line and current and any(p in current for p in patterns):
+            if "0 bytes spill stores, 0 bytes spill loads" not in line:
+                bad.append(current)
+    return sorted(set(bad))
+
+
 def _newer(target: Path, deps: list[Path]) -> bool:
     if not target.exists():
         return False
@@ -41,6 +57,11 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stdout}\n{r.stderr}")
+        spilled = spilling_kernels(r.stderr, NO_SPILL)
+        if spilled:
+            obj.unlink(missing_ok=True)
+            raise RuntimeError(f"{src.name}: ptxas spilled registers in {spilled}; these kernels lose a third of their "
+                               "speed to a few spilled bytes (change the setmaxnreg split until -Xptxas -v shows 0)")
         return obj, r.stderr
 
     with cf.ThreadPoolExecutor(max_workers=min(8, len(sources))) as ex:

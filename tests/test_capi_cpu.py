@@ -74,3 +74,20 @@ def test_compute_fails_loudly_without_gpu(capi):
 def test_python_wrapper_rejects_unsupported_dtype(capi):
     with pytest.raises(RuntimeError, match="T is not supported"):
         capi.fp16_mm(torch.zeros(8, 8), torch.zeros(8, 8), torch.zeros(8, 8), 8, 8, 8)
+
+
+def test_build_refuses_spilling_gemm_kernels():
+    # a few spilled bytes in the FP8 promotion loop cost a third of the speed: the build parses ptxas -v
+    from llmmm_b200.build import spilling_kernels
+    log = "\n".join([
+        "ptxas info    : Compiling entry function '_ZN5llmmm30fp8_blockwise_gemm_pair_kernelILb0EEEv' for 'sm_100a'",
+        "ptxas info    : Function properties for _ZN5llmmm30fp8_blockwise_gemm_pair_kernelILb0EEEv",
+        "    16 bytes stack frame, 12 bytes spill stores, 52 bytes spill loads",
+        "ptxas info    : Compiling entry function '_ZN5llmmm25fp8_blockwise_gemm_kernelILb1EEEv' for 'sm_100a'",
+        "ptxas info    : Function properties for _ZN5llmmm25fp8_blockwise_gemm_kernelILb1EEEv",
+        "    8 bytes stack frame, 0 bytes spill stores, 0 bytes spill loads",
+        "ptxas info    : Compiling entry function '_ZN5llmmm18quant_1x128_kernelEPKfPhPfii' for 'sm_100a'",
+        "ptxas info    : Function properties for _ZN5llmmm18quant_1x128_kernelEPKfPhPfii",
+        "    16 bytes stack frame, 12 bytes spill stores, 52 bytes spill loads",
+    ])
+    assert spilling_kernels(log, ("fp8_blockwise_gemm",)) == ["_ZN5llmmm30fp8_blockwise_gemm_pair_kernelILb0EEEv"]
