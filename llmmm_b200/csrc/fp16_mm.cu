@@ -119,6 +119,9 @@ __global__ void __launch_bounds__(fp16cfg::THREADS, 1) fp16_gemm_kernel(const __
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
+  // no global memory touched so far: this may overlap the tail of the previous kernel on the stream
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer --
@@ -352,6 +355,9 @@ __global__ void __launch_bounds__(fp16pair::THREADS, 1)
   cluster_sync_all();  // the pair's barriers exist before any cross-CTA signal
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
+  // no global memory touched so far: this may overlap the tail of the previous kernel on the stream
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer --
@@ -632,21 +638,9 @@ static int launch_fp16_pair(const void* A, const void* B, void* C, int M, int N,
   // estimated cost of a split, in K-steps of 64 (one takes about 0.33 us): publishing a chunk and counting
   // the arrival about 3 us, reading a chunk back about 1.5 us
   const SplitPlan plan = plan_split(info, tiles, (K + BK - 1) / BK, /*fixed*/ 10, /*per_way_x2*/ 9, /*min_gain*/ 6);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim            = dim3(2 * plan.pairs);
-  cfg.blockDim           = dim3(THREADS);
-  cfg.dynamicSmemBytes   = SMEM_BYTES;
-  cfg.stream             = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id               = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs                = attr;
-  cfg.numAttrs             = 1;
-  LLMMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, fp16_gemm_pair_kernel<T>, tm_a, tm_b, tm_c, M, N, K, plan.dp_tiles,
-                                    plan.split_pairs, plan.split_s, plan.split_chunk, plan.partials, plan.counters,
-                                    info->status));
+  LLMMM_CUDA_TRY(launch_pdl(fp16_gemm_pair_kernel<T>, dim3(2 * plan.pairs), dim3(THREADS), SMEM_BYTES, stream, 2, tm_a, tm_b,
+                            tm_c, M, N, K, plan.dp_tiles, plan.split_pairs, plan.split_s, plan.split_chunk, plan.partials,
+                            plan.counters, info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
 }
@@ -689,9 +683,9 @@ static int launch_fp16(const void* A, const void* B, void* C, int M, int N, int 
   const int n_tiles = (N + BN - 1) / BN;
   const int tiles   = m_tiles * n_tiles;
   const int grid    = tiles < info->sm_count ? tiles : info->sm_count;
-  fp16_gemm_kernel<T><<<grid, THREADS, SMEM_BYTES, stream>>>(tm_a, tm_b, tm_c, M, N, K, info->status);
+  LLMMM_CUDA_TRY(launch_pdl(fp16_gemm_kernel<T>, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, 1, tm_a, tm_b, tm_c, M, N, K,
+                            info->status));
   g_launches.fetch_add(1);
-  LLMMM_CUDA_TRY(cudaGetLastError());
   return LLMMM_OK;
 }
 

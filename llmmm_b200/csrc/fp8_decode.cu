@@ -167,6 +167,10 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
+  // Set-up (barriers, tensor memory, descriptor prefetch) touched no global memory: it may overlap the tail
+  // of the previous kernel on the stream, and the next kernel may begin its own set-up from here on.
+  pdl_launch_dependents();
+  pdl_wait();
   if (threadIdx.x == 0) {
     PROFD(1);
   }
@@ -561,10 +565,9 @@ static int launch_decode_t(const void*       A,
   if ((long long)G > U) {
     G = (int)U;
   }
-  fp8_decode_kernel<MP, OUT_F32, false><<<G, THREADS, L::SMEM_BYTES, stream>>>(
-    tm_w, tm_x, A_s, B_s, C, C_s, M, N, K, partials, counters, info->status);
+  LLMMM_CUDA_TRY(launch_pdl(fp8_decode_kernel<MP, OUT_F32, false>, dim3((unsigned)G), dim3(THREADS), L::SMEM_BYTES, stream,
+                            1, tm_w, tm_x, A_s, B_s, C, C_s, M, N, K, partials, counters, info->status));
   g_launches.fetch_add(1);
-  LLMMM_CUDA_TRY(cudaGetLastError());
   return LLMMM_OK;
 }
 
@@ -595,22 +598,11 @@ static int launch_decode_cluster_t(const void*       A,
       fp8_decode_kernel<MP, OUT_F32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM_BYTES));
     attr_set[info->device] = true;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim            = dim3((unsigned)((N / 128) * cluster));
-  cfg.blockDim           = dim3(THREADS);
-  cfg.dynamicSmemBytes   = L::SMEM_BYTES;
-  cfg.stream             = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id               = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)cluster;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs                = attr;
-  cfg.numAttrs             = 1;
   float*    no_partials = nullptr;
   uint32_t* no_counters = nullptr;
-  LLMMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, fp8_decode_kernel<MP, OUT_F32, true>, tm_w, tm_x, A_s, B_s, C, C_s, M, N, K,
-                                    no_partials, no_counters, info->status));
+  LLMMM_CUDA_TRY(launch_pdl(fp8_decode_kernel<MP, OUT_F32, true>, dim3((unsigned)((N / 128) * cluster)), dim3(THREADS),
+                            L::SMEM_BYTES, stream, (unsigned)cluster, tm_w, tm_x, A_s, B_s, C, C_s, M, N, K, no_partials,
+                            no_counters, info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
 }

@@ -141,6 +141,9 @@ __global__ void __launch_bounds__(fp8cfg::THREADS, 1) fp8_blockwise_gemm_kernel(
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
+  // no global memory touched so far: this may overlap the tail of the previous kernel on the stream
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp < 4) {
     setmaxnreg_dec<REGS_CTRL>();
@@ -435,6 +438,9 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
   cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
+  // no global memory touched so far: this may overlap the tail of the previous kernel on the stream
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp < 4) {
     setmaxnreg_dec<REGS_CTRL>();
@@ -801,21 +807,9 @@ static int launch_fp8_pair(const void*       A,
   // estimated cost of a split, in K-blocks (one takes about 0.58 us): publishing a chunk and counting the
   // arrival about 3 us, reading a chunk back about 1.5 us
   const SplitPlan plan = plan_split(info, tiles, k_blocks, /*fixed*/ 4, /*per_way_x2*/ 5, /*min_gain*/ 3);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim            = dim3(2 * plan.pairs);
-  cfg.blockDim           = dim3(THREADS);
-  cfg.dynamicSmemBytes   = SMEM_BYTES;
-  cfg.stream             = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id               = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs                = attr;
-  cfg.numAttrs             = 1;
-  LLMMM_CUDA_TRY(cudaLaunchKernelEx(
-    &cfg, fp8_blockwise_gemm_pair_kernel<OUT_F32>, tm_a, tm_b, A_s, B_s, C, C_s, M, N, K, plan.dp_tiles,
-    plan.split_pairs, plan.split_s, plan.split_chunk, plan.partials, plan.counters, info->status));
+  LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<OUT_F32>, dim3(2 * plan.pairs), dim3(THREADS), SMEM_BYTES, stream,
+                            2, tm_a, tm_b, A_s, B_s, C, C_s, M, N, K, plan.dp_tiles, plan.split_pairs, plan.split_s,
+                            plan.split_chunk, plan.partials, plan.counters, info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
 }
@@ -857,10 +851,9 @@ static int launch_fp8(const void*  A,
   const int n_tiles = (N + BN - 1) / BN;
   const int tiles   = m_tiles * n_tiles;
   const int grid    = tiles < info->sm_count ? tiles : info->sm_count;
-  fp8_blockwise_gemm_kernel<OUT_F32>
-    <<<grid, THREADS, SMEM_BYTES, stream>>>(tm_a, tm_b, A_s, B_s, C, C_s, M, N, K, info->status);
+  LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_kernel<OUT_F32>, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, 1, tm_a, tm_b,
+                            A_s, B_s, C, C_s, M, N, K, info->status));
   g_launches.fetch_add(1);
-  LLMMM_CUDA_TRY(cudaGetLastError());
   return LLMMM_OK;
 }
 

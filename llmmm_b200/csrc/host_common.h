@@ -76,6 +76,34 @@ Workspace registered_workspace(int device);
 // Scratch the pair kernels want for splitting the tiles of their last wave (pair_walk.cuh).
 size_t split_workspace_bytes();
 
+// Launches `kernel` with programmatic stream serialisation allowed (the kernel must execute pdl_wait()
+// before its first access to global memory, see sm100.cuh) and, if cluster > 1, as clusters of that size.
+template<typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, unsigned cluster,
+                       Args&&... args)
+{
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim            = grid;
+  cfg.blockDim           = block;
+  cfg.dynamicSmemBytes   = smem;
+  cfg.stream             = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned            n                              = 0;
+  attr[n].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[n].val.programmaticStreamSerializationAllowed = 1;
+  ++n;
+  if (cluster > 1) {
+    attr[n].id               = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs    = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 #define LLMMM_CUDA_TRY(call)                                                                                           \
   do {                                                                                                                 \
     cudaError_t e__ = (call);                                                                                          \

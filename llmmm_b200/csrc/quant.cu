@@ -12,6 +12,7 @@
 #include <cuda_fp8.h>
 
 #include "host_common.h"
+#include "sm100.cuh"
 
 namespace llmmm {
 
@@ -50,6 +51,8 @@ constexpr int Q1_WARPS = 8;
 __global__ void __launch_bounds__(Q1_WARPS * 32)
   quant_1x128_kernel(const float* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale, int M, int K)
 {
+  pdl_launch_dependents();  // see sm100.cuh: the next kernel may start its set-up, this one waits for its predecessor
+  pdl_wait();
   const int lane    = threadIdx.x & 31;
   const int warp    = threadIdx.x >> 5;
   const int groups  = K / 128;
@@ -99,6 +102,8 @@ __global__ void __launch_bounds__(256)
   quant_128x128_kernel(const float* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale, int rows, int cols)
 {
   __shared__ float warp_amax[8];
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int cb   = blockIdx.x;
@@ -154,10 +159,9 @@ int llmmm_fp8_quant_1x128(const float* x, void* q, float* scale, int M, int K, l
   }
   const long long warps  = (long long)((M + Q1_ROWS - 1) / Q1_ROWS) * (K / 128);
   const long long blocks = (warps + Q1_WARPS - 1) / Q1_WARPS;
-  quant_1x128_kernel<<<(unsigned)blocks, Q1_WARPS * 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-    x, static_cast<uint8_t*>(q), scale, M, K);
+  LLMMM_CUDA_TRY(launch_pdl(quant_1x128_kernel, dim3((unsigned)blocks), dim3(Q1_WARPS * 32), 0,
+                            reinterpret_cast<cudaStream_t>(stream), 1, x, static_cast<uint8_t*>(q), scale, M, K));
   g_launches.fetch_add(1);
-  LLMMM_CUDA_TRY(cudaGetLastError());
   return LLMMM_OK;
 }
 
@@ -177,10 +181,9 @@ int llmmm_fp8_quant_128x128(const float* x, void* q, float* scale, int rows, int
     return LLMMM_ERR_UNSUPPORTED;
   }
   dim3 grid(cols / 128, rows / 128);
-  quant_128x128_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-    x, static_cast<uint8_t*>(q), scale, rows, cols);
+  LLMMM_CUDA_TRY(launch_pdl(quant_128x128_kernel, grid, dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 1, x,
+                            static_cast<uint8_t*>(q), scale, rows, cols));
   g_launches.fetch_add(1);
-  LLMMM_CUDA_TRY(cudaGetLastError());
   return LLMMM_OK;
 }
 

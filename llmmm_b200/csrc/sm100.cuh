@@ -126,6 +126,23 @@ mbar_wait(uint64_t* bar, uint32_t parity, uint32_t code, volatile uint32_t* abor
   mbar_wait_limit(bar, parity, code, abort_flag, status, WAIT_LIMIT_NS);
 }
 
+// ------------------------------------------- programmatic dependent launch ---
+//
+// A kernel launched with cudaLaunchAttributeProgrammaticStreamSerialization may start while its
+// predecessor on the stream is still running; pdl_wait() then blocks until that predecessor has
+// completed and its memory is visible.  Everything a kernel does before pdl_wait() must touch no global
+// memory.  pdl_launch_dependents() lets the NEXT kernel on the stream start its own set-up as soon as
+// every CTA of this grid has executed it (or has exited).  Both are no-ops without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents()
+{
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ void pdl_wait()
+{
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ------------------------------------------------------------------ TMA ---
 
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m)

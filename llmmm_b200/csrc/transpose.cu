@@ -10,12 +10,15 @@
 //     that shared memory is only touched with whole words, stored under an XOR swizzle that keeps both
 //     the transposed writes and the row reads free of bank conflicts.
 #include "host_common.h"
+#include "sm100.cuh"
 
 namespace llmmm {
 
 __global__ void __launch_bounds__(256) transpose_b32_kernel(uint32_t* __restrict__ dst, const uint32_t* __restrict__ src, int M, int N)
 {
   __shared__ uint32_t tile[32][33];
+  pdl_launch_dependents();  // see sm100.cuh: the next kernel may start its set-up, this one waits for its predecessor
+  pdl_wait();
   const int tx = threadIdx.x & 31;
   const int ty = threadIdx.x >> 5;
   const int m0 = blockIdx.y * 32;
@@ -37,6 +40,8 @@ __global__ void __launch_bounds__(256) transpose_b8_kernel(uint8_t* __restrict__
 {
   // T[out_row][word]: out_row = input column (0..127), word w holds input rows 4w..4w+3; physical word = w ^ (out_row >> 2)
   __shared__ uint32_t T[128][32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int tx = threadIdx.x & 31;  // 4-column block of the input tile
   const int ty = threadIdx.x >> 5;
   const int m0 = blockIdx.y * 128;
@@ -94,12 +99,13 @@ extern "C" int llmmm_transpose_aligned_128(void* dst, const void* src, int M, in
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (elem_bytes == 4) {
-    transpose_b32_kernel<<<dim3(N / 32, M / 32), 256, 0, s>>>(static_cast<uint32_t*>(dst), static_cast<const uint32_t*>(src), M, N);
+    LLMMM_CUDA_TRY(launch_pdl(transpose_b32_kernel, dim3(N / 32, M / 32), dim3(256), 0, s, 1, static_cast<uint32_t*>(dst),
+                              static_cast<const uint32_t*>(src), M, N));
   }
   else {
-    transpose_b8_kernel<<<dim3(N / 128, M / 128), 256, 0, s>>>(static_cast<uint8_t*>(dst), static_cast<const uint8_t*>(src), M, N);
+    LLMMM_CUDA_TRY(launch_pdl(transpose_b8_kernel, dim3(N / 128, M / 128), dim3(256), 0, s, 1, static_cast<uint8_t*>(dst),
+                              static_cast<const uint8_t*>(src), M, N));
   }
   g_launches.fetch_add(1);
-  LLMMM_CUDA_TRY(cudaGetLastError());
   return LLMMM_OK;
 }
