@@ -129,6 +129,14 @@ int llmmm_transpose_aligned_128(void* dst, const void* src, int M, int N, int el
 size_t llmmm_fp8_workspace_bytes(int M, int N, int K);
 int    llmmm_set_workspace(void* device_ptr, size_t bytes);
 
+/* A promise about the B_t / B_scale_t operands of later FP8 GEMM calls from this process: they are model
+ * weights, never written by the kernel that runs immediately before the GEMM on the same stream.  With it
+ * (enabled != 0) a decode-sized call (M <= 64) requests its first weight tiles while the preceding kernel of
+ * the stream is still finishing (programmatic dependent launch; activations, scales and outputs still wait
+ * for that kernel).  Off by default: then nothing is read before the preceding kernel has completed.  No
+ * counterpart in the reference. */
+int llmmm_set_static_weights(int enabled);
+
 /* Decode-sized FP8 blockwise GEMM for callers that cannot provide scratch memory.
  * This one has no counterpart in the reference (which has neither split-K nor
  * any scratch).  It exists for hosts where device allocation is off the table:

@@ -56,7 +56,8 @@ EXPORTED_SYMBOLS = (
     "llmmm_last_error", "llmmm_version", "llmmm_fp16_mm_f16", "llmmm_fp16_mm_bf16",
     "llmmm_fp8_blockwise_mm_e4m3out", "llmmm_fp8_blockwise_mm_f32out", "llmmm_fp8_quant_1x128",
     "llmmm_fp8_quant_128x128", "llmmm_fp8_workspace_bytes", "llmmm_set_workspace", "llmmm_check_status",
-    "llmmm_launch_count", "llmmm_split_launch_count", "llmmm_fp8_blockwise_mm_e4m3out_noalloc",
+    "llmmm_launch_count", "llmmm_split_launch_count", "llmmm_set_static_weights",
+    "llmmm_fp8_blockwise_mm_e4m3out_noalloc",
     "llmmm_transpose_aligned_128", "llmmm_selftest_wait_expiry",
 )
 
@@ -159,6 +160,13 @@ def fp8_workspace_bytes(M: int, N: int, K: int) -> int:
 
 
 _workspaces: dict[int, torch.Tensor] = {}
+
+
+def set_static_weights(enabled: bool) -> None:
+    """Promise (or withdraw the promise) that the B operands of later FP8 GEMMs are weights that the kernel
+    running just before the GEMM on the same stream never writes; decode-sized calls then prefetch them while
+    that kernel is still finishing."""
+    _check(lib().llmmm_set_static_weights(1 if enabled else 0))
 
 
 def clear_workspace() -> None:

@@ -34,30 +34,39 @@ namespace llmmm {
 namespace deccfg {
 constexpr int      BK            = 128;
 constexpr int      UMMA_K        = 32;
-constexpr int      STAGES        = 8;
+constexpr int      MAX_STAGES    = 6;    // the ring depth depends on the activation tile, see DecodeSmem
 constexpr int      THREADS       = 192;
 constexpr uint32_t W_BYTES       = 128 * BK;
 constexpr int      MAX_CTAS      = 256;
 constexpr int      MAX_GROUPS    = 4096;                 // counters: N <= 524288
 constexpr size_t   COUNTER_BYTES = MAX_GROUPS * sizeof(uint32_t);
-constexpr int      PARTS         = 8;    // TMEM partial stages of 64 columns each
-constexpr uint32_t TMEM_COLS     = 512;
+constexpr uint32_t TMEM_COLS     = 256;  // one partial stage per ring stage (see DecodeSmem), two CTAs per SM
 }  // namespace deccfg
 
 template<int MP>
 struct DecodeSmem {
   static constexpr uint32_t X_BYTES    = MP * deccfg::BK;
+  // As deep a ring as lets two CTAs share an SM (113 KB each; tensor memory: 256 columns each): the next
+  // kernel of a launch chain then sets up, and requests static weights, beside the running one.
+  static constexpr int      STAGES     = MP <= 16 ? 6 : (MP <= 32 ? 5 : 4);
+  // K-block `it` uses ring stage it % STAGES and the tensor-memory partial stage of the same index, so ONE
+  // tcgen05.commit per K-block tells both the promotion warps (partial ready) and the producer (operands
+  // consumed); a second commit would cost the single issuing thread another ~150 clk per K-block.
+  static constexpr uint32_t PART_COLS  = MP < 32 ? 32 : MP;
+  static_assert(STAGES * PART_COLS <= deccfg::TMEM_COLS, "partial stages exceed the tensor memory allocation");
   static constexpr uint32_t OFF_W      = 0;
-  static constexpr uint32_t OFF_X      = deccfg::STAGES * deccfg::W_BYTES;
-  static constexpr uint32_t OFF_BAR    = OFF_X + deccfg::STAGES * X_BYTES;
-  static constexpr uint32_t SMEM_BYTES = OFF_BAR + 2048 + 1024;
+  static constexpr uint32_t OFF_X      = STAGES * deccfg::W_BYTES;
+  static constexpr uint32_t OFF_BAR    = OFF_X + STAGES * X_BYTES;
+  // at least 80 KB, so that never more than two CTAs share an SM: a third one would sit in tcgen05.alloc until
+  // tensor memory is freed
+  static constexpr uint32_t USED_BYTES = OFF_BAR + 2048 + 1024;
+  static constexpr uint32_t SMEM_BYTES = USED_BYTES > 80 * 1024 ? USED_BYTES : 80 * 1024;
 };
 
 struct DecodeBars {
-  uint64_t full[deccfg::STAGES];
-  uint64_t empty[deccfg::STAGES];
-  uint64_t part_full[deccfg::PARTS];
-  uint64_t part_empty[deccfg::PARTS];
+  uint64_t full[deccfg::MAX_STAGES];        // operands of the stage have landed
+  uint64_t part_full[deccfg::MAX_STAGES];   // the K-block's MMAs are done: partial ready, operands consumed
+  uint64_t part_empty[deccfg::MAX_STAGES];  // the 4 promotion warps have copied the partial out
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t last_flag;
@@ -71,6 +80,8 @@ struct DecodeBars {
 __device__ unsigned long long g_prof_dec[16];
 __device__ unsigned long long g_prof_cta[256][4];  // per CTA: entry, promotion loop done, fix-up done, exit
 __device__ unsigned long long g_prof_fin[256][6];  // last segment: published, counted, reduced, amax, stored
+__device__ unsigned long long g_prof_pdl[256][2];  // producer thread: before / after waiting for the previous kernel
+__device__ unsigned long long g_prof_set[256][4];  // set-up: barriers initialised, before / after tcgen05.alloc, after the CTA barrier
 #define PROFF(i) if (et == 0) g_prof_fin[blockIdx.x][i] = global_timer_ns()
 #else
 #define PROFF(i)
@@ -100,7 +111,7 @@ __device__ __forceinline__ int cta_of_unit(uint32_t u, uint32_t G, uint32_t U)
 //   ring, a second barrier, and the leader adds them in rank order and runs the epilogue.  No scratch, no
 //   atomics, no global round trips; used when the groups times a cluster size of 2-7 fill the GPU.
 template<int MP, bool OUT_F32, bool CLUSTER>
-__global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __grid_constant__ CUtensorMap tm_w,
+__global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __grid_constant__ CUtensorMap tm_w,
                                                                         const __grid_constant__ CUtensorMap tm_x,
                                                                         const float* __restrict__ A_s,
                                                                         const float* __restrict__ B_s,
@@ -111,6 +122,7 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
                                                                         int       K,
                                                                         float*    partials,
                                                                         uint32_t* counters,
+                                                                        int       early_weights,
                                                                         uint32_t* status)
 {
   using namespace deccfg;
@@ -147,52 +159,89 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
   }
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < L::STAGES; ++s) {
       mbar_init(&bars->full[s], 1);
-      mbar_init(&bars->empty[s], 1);
-    }
-    for (int p = 0; p < PARTS; ++p) {
-      mbar_init(&bars->part_full[p], 1);
-      mbar_init(&bars->part_empty[p], 4);
+      mbar_init(&bars->part_full[s], 1);
+      mbar_init(&bars->part_empty[s], 4);
     }
     bars->abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tm_w);
     prefetch_tmap(&tm_x);
+#ifdef LLMMM_PROFILE
+    g_prof_set[blockIdx.x][0] = global_timer_ns();
+#endif
   }
   if (warp == 1) {
+#ifdef LLMMM_PROFILE
+    if (lane == 0) g_prof_set[blockIdx.x][1] = global_timer_ns();
+#endif
     tmem_alloc<TMEM_COLS>(&bars->tmem_base);
+#ifdef LLMMM_PROFILE
+    if (lane == 0) g_prof_set[blockIdx.x][2] = global_timer_ns();
+#endif
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+#ifdef LLMMM_PROFILE
+  if (threadIdx.x == 0) g_prof_set[blockIdx.x][3] = global_timer_ns();
+#endif
   const uint32_t tmem_base = bars->tmem_base;
   // Set-up (barriers, tensor memory, descriptor prefetch) touched no global memory: it may overlap the tail
   // of the previous kernel on the stream, and the next kernel may begin its own set-up from here on.
   pdl_launch_dependents();
-  pdl_wait();
+  if (warp != 0) {
+    pdl_wait();  // warp 0 waits below, as a whole: a waiting lane holds up the other lanes of its warp
+  }
   if (threadIdx.x == 0) {
     PROFD(1);
   }
 
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer --
+    const uint64_t pol_w = policy_evict_first();  // weights are read once
+    const uint64_t pol_x = policy_evict_last();   // activations are re-read by every CTA
+    const int      nb0   = (int)(u_begin / (uint32_t)KB);
+    const int      kb0   = (int)(u_begin % (uint32_t)KB);
+    // Weights the caller declared static (llmmm_set_static_weights) do not depend on the previous kernel
+    // of the stream: the first ring of weight tiles is requested before waiting for that kernel, the
+    // activation tiles of the same stages after it.
+    uint32_t early = 0;
+    if (lane == 0 && early_weights) {
+      int nb = nb0, kb = kb0;
+      for (uint32_t u = u_begin; u < u_end && early < (uint32_t)L::STAGES; ++u, ++early, ++kb) {
+        if (kb == KB) {
+          kb = 0;
+          ++nb;
+        }
+        mbar_arrive_expect_tx(&bars->full[early], W_BYTES + L::X_BYTES);
+        tma_load_2d_hint(smem + L::OFF_W + early * W_BYTES, &tm_w, &bars->full[early], kb * BK, nb * 128, pol_w);
+      }
+    }
+    __syncwarp();
+#ifdef LLMMM_PROFILE
+    if (lane == 0) g_prof_pdl[blockIdx.x][0] = global_timer_ns();
+#endif
+    pdl_wait();
+#ifdef LLMMM_PROFILE
+    if (lane == 0) g_prof_pdl[blockIdx.x][1] = global_timer_ns();
+#endif
     if (lane == 0) {
-      const uint64_t pol_w = policy_evict_first();  // weights are read once
-      const uint64_t pol_x = policy_evict_last();   // activations are re-read by every CTA
-      uint32_t       it    = 0;
-      int nb = (int)(u_begin / (uint32_t)KB);
-      int kb = (int)(u_begin % (uint32_t)KB);
+      uint32_t it = 0;
+      int      nb = nb0, kb = kb0;
       for (uint32_t u = u_begin; u < u_end; ++u, ++it, ++kb) {
         if (kb == KB) {
           kb = 0;
           ++nb;
         }
-        const uint32_t s  = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
-        mbar_wait(&bars->empty[s], ph ^ 1, DEV_WAIT_SMEM_EMPTY, abort_flag, status);
-        mbar_arrive_expect_tx(&bars->full[s], W_BYTES + L::X_BYTES);
-        tma_load_2d_hint(smem + L::OFF_W + s * W_BYTES, &tm_w, &bars->full[s], kb * BK, nb * 128, pol_w);
+        const uint32_t s  = it % L::STAGES;
+        const uint32_t ph = (it / L::STAGES) & 1;
+        if (it >= early) {
+          mbar_wait(&bars->part_full[s], ph ^ 1, DEV_WAIT_SMEM_EMPTY, abort_flag, status);
+          mbar_arrive_expect_tx(&bars->full[s], W_BYTES + L::X_BYTES);
+          tma_load_2d_hint(smem + L::OFF_W + s * W_BYTES, &tm_w, &bars->full[s], kb * BK, nb * 128, pol_w);
+        }
         tma_load_2d_hint(smem + L::OFF_X + s * L::X_BYTES, &tm_x, &bars->full[s], kb * BK, 0, pol_x);
       }
     }
@@ -208,10 +257,10 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
       constexpr uint32_t idesc = make_idesc(/*e4m3*/ 0, 0, 0, 0, 128, MP);
       uint32_t           it    = 0;
       for (uint32_t u = u_begin; u < u_end; ++u, ++it) {
-        const uint32_t s  = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
-        const uint32_t p  = it % PARTS;
-        const uint32_t pp = (it / PARTS) & 1;
+        const uint32_t s  = it % L::STAGES;
+        const uint32_t ph = (it / L::STAGES) & 1;
+        const uint32_t p  = s;
+        const uint32_t pp = ph;
         mbar_wait(&bars->part_empty[p], pp ^ 1, DEV_WAIT_TMEM_EMPTY, abort_flag, status);
         mbar_wait(&bars->full[s], ph, DEV_WAIT_SMEM_FULL, abort_flag, status);
         if (it == 0) {
@@ -222,9 +271,8 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
         const uint64_t dx = make_smem_desc_sw128(smem_u32(smem + L::OFF_X + s * L::X_BYTES), 0, 1024);
 #pragma unroll
         for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-          tc_mma_f8(tmem_base + p * 64, dw + (uint64_t)((kk * UMMA_K) >> 4), dx + (uint64_t)((kk * UMMA_K) >> 4), idesc, kk != 0);
+          tc_mma_f8(tmem_base + p * L::PART_COLS, dw + (uint64_t)((kk * UMMA_K) >> 4), dx + (uint64_t)((kk * UMMA_K) >> 4), idesc, kk != 0);
         }
-        tc_commit(&bars->empty[s]);
         tc_commit(&bars->part_full[p]);
       }
       PROFD(3);
@@ -265,8 +313,8 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
       float a_hi = (MP > 32 && lane + 32 < M) ? __ldg(A_s + (size_t)kb0 * M + 32 + lane) : 0.0f;
       float b_nx = __ldg(B_s + (size_t)nb * KB + kb0);
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
-        const uint32_t p  = it % PARTS;
-        const uint32_t pp = (it / PARTS) & 1;
+        const uint32_t p  = it % L::STAGES;
+        const uint32_t pp = (it / L::STAGES) & 1;
         // one fp32 rounding of each scale product, as in the reference
         const float sc_lo = __fmul_rn(a_lo, b_nx);
         const float sc_hi = __fmul_rn(a_hi, b_nx);
@@ -280,7 +328,7 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
         uint32_t v[MP];
 #pragma unroll
         for (int c = 0; c < MP / 16; ++c) {
-          tmem_ld_32x32b_x16(tmem_base + p * 64 + t_lane + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&v[c * 16]));
+          tmem_ld_32x32b_x16(tmem_base + p * L::PART_COLS + t_lane + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&v[c * 16]));
         }
         tmem_ld_wait();
         // the partial is in registers: hand the stage back before any arithmetic
@@ -476,6 +524,33 @@ __global__ void __launch_bounds__(deccfg::THREADS, 1) fp8_decode_kernel(const __
 }
 
 #ifdef LLMMM_PROFILE
+extern "C" void llmmm_profile_dump_pdl()
+{
+  unsigned long long c[256][4], w[256][2];
+  cudaMemcpyFromSymbol(c, g_prof_cta, sizeof(c));
+  cudaMemcpyFromSymbol(w, g_prof_pdl, sizeof(w));
+  double held = 0, setup = 0; unsigned long long first_entry = ~0ull, last_entry = 0, last_exit = 0, first_go = ~0ull; int n = 0;
+  for (int i = 0; i < 256; ++i) {
+    if (c[i][0] == 0 || w[i][1] == 0) continue;
+    held += (double)(w[i][1] - w[i][0]); setup += (double)(w[i][0] - c[i][0]); ++n;
+    if (c[i][0] < first_entry) first_entry = c[i][0];
+    if (c[i][0] > last_entry) last_entry = c[i][0];
+    if (c[i][3] > last_exit) last_exit = c[i][3];
+    if (w[i][1] < first_go) first_go = w[i][1];
+  }
+  unsigned long long st[256][4];
+  cudaMemcpyFromSymbol(st, g_prof_set, sizeof(st));
+  printf("CTA 5: entry +0, barriers initialised +%llu, tcgen05.alloc from +%llu to +%llu, CTA barrier passed +%llu, at the dependency wait +%llu, released +%llu, exit +%llu ns\n",
+         st[5][0] - c[5][0], st[5][1] - c[5][0], st[5][2] - c[5][0], st[5][3] - c[5][0], w[5][0] - c[5][0], w[5][1] - c[5][0], c[5][3] - c[5][0]);
+  unsigned long long h[16];
+  cudaMemcpyFromSymbol(h, g_prof_dec, sizeof(h));
+  printf("CTA 0 after its release (ns): first operands +%lld, MMAs issued +%lld, promotion done +%lld, all roles done +%lld, TMEM freed +%lld\n",
+         (long long)(h[2] - w[0][1]), (long long)(h[3] - w[0][1]), (long long)(h[4] - w[0][1]), (long long)(h[7] - w[0][1]), (long long)(h[8] - w[0][1]));
+  printf("last launch, %d CTAs: entries spread over %llu ns, set-up %.0f ns, held at the dependency wait %.0f ns (avg), "
+         "first entry -> first release %llu ns, first entry -> last exit %llu ns\n", n, last_entry - first_entry, setup / n,
+         held / n, first_go - first_entry, last_exit - first_entry);
+}
+
 extern "C" void llmmm_profile_dump_decode()
 {
   unsigned long long h[16];
@@ -509,6 +584,8 @@ extern "C" void llmmm_profile_dump_decode()
 #endif
 
 // ------------------------------------------------------------ host side ---
+
+std::atomic<int> g_static_weights{0};  // llmmm_set_static_weights()
 
 namespace {
 static_assert(deccfg::COUNTER_BYTES == WS_DECODE_COUNTER_BYTES, "layout of the registered scratch");
@@ -566,7 +643,8 @@ static int launch_decode_t(const void*       A,
     G = (int)U;
   }
   LLMMM_CUDA_TRY(launch_pdl(fp8_decode_kernel<MP, OUT_F32, false>, dim3((unsigned)G), dim3(THREADS), L::SMEM_BYTES, stream,
-                            1, tm_w, tm_x, A_s, B_s, C, C_s, M, N, K, partials, counters, info->status));
+                            1, tm_w, tm_x, A_s, B_s, C, C_s, M, N, K, partials, counters, g_static_weights.load(),
+                            info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
 }
@@ -602,7 +680,7 @@ static int launch_decode_cluster_t(const void*       A,
   uint32_t* no_counters = nullptr;
   LLMMM_CUDA_TRY(launch_pdl(fp8_decode_kernel<MP, OUT_F32, true>, dim3((unsigned)((N / 128) * cluster)), dim3(THREADS),
                             L::SMEM_BYTES, stream, (unsigned)cluster, tm_w, tm_x, A_s, B_s, C, C_s, M, N, K, no_partials,
-                            no_counters, info->status));
+                            no_counters, g_static_weights.load(), info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
 }
@@ -733,6 +811,12 @@ size_t llmmm_fp8_workspace_bytes(int M, int N, int K)
     return 0;
   }
   return llmmm::decode_workspace_bytes(M);
+}
+
+int llmmm_set_static_weights(int enabled)
+{
+  llmmm::g_static_weights.store(enabled ? 1 : 0);
+  return LLMMM_OK;
 }
 
 int llmmm_set_workspace(void* device_ptr, size_t bytes)

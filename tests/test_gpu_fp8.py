@@ -157,6 +157,47 @@ def test_split_last_wave(capi, oracle, cuda, shape):
     assert np.array_equal(gq2, gq3) and np.array_equal(gs2.view(np.uint32), gs3.view(np.uint32)) and np.array_equal(gf2, gf3)
 
 
+@pytest.mark.parametrize("M", [1, 16, 64])
+def test_decode_launch_chain_with_static_weights(capi, oracle, cuda, M):
+    # Back-to-back launches without synchronisation, each using the previous one's stream position: with the
+    # static-weights promise a launch prefetches its weights while the one before it is finishing; results
+    # must be what the un-promised chain gives, bit for bit, and right.
+    N, K = 2560, 4096
+    cases = [make_case(oracle, 80 + i, M, N, K) for i in range(3)]
+    dev = [to_dev(cuda, *c) for c in cases]
+    capi.ensure_workspace(M, N, K)
+
+    def chain():
+        outs = []
+        for rep in range(4):
+            for dA, dAs, dB, dBs in dev:
+                Cq = torch.full((M, N), 0xAA, dtype=torch.uint8, device=cuda)
+                Cs = torch.full((N // 128, M), float("nan"), device=cuda)
+                outs.append((Cq, Cs))
+        i = 0
+        for rep in range(4):
+            for dA, dAs, dB, dBs in dev:
+                capi.fp8_blockwise_mm(dA, dAs, dB, dBs, outs[i][0], outs[i][1], M, N, K)
+                i += 1
+        torch.cuda.synchronize()
+        capi.check_status()
+        return outs
+
+    plain = chain()
+    capi.set_static_weights(True)
+    try:
+        promised = chain()
+    finally:
+        capi.set_static_weights(False)
+    for (q0, s0), (q1, s1) in zip(plain, promised):
+        assert torch.equal(q0, q1) and torch.equal(s0, s1)
+    for i, case in enumerate(cases):
+        Cf = torch.empty(M, N, device=cuda)
+        capi.fp8_blockwise_mm_f32(*dev[i], Cf, M, N, K)
+        torch.cuda.synchronize()
+        check_against_oracle(oracle, *case, promised[i][0].cpu().numpy(), promised[i][1].cpu().numpy(), Cf.cpu().numpy())
+
+
 def gpu_c_quant(acc):
     """The output quantisation rule in torch fp32 on the GPU (for full-size property checks)."""
     M, N = acc.shape
