@@ -174,6 +174,24 @@ int llmmm_check_status(llmmm_stream_t stream);
  * no counterpart (its kernels contain no waits on other agents). */
 int llmmm_selftest_wait_expiry(unsigned int limit_us, llmmm_stream_t stream);
 
+/* Problem kinds for the two calls below. */
+#define LLMMM_KIND_FP16 0
+#define LLMMM_KIND_BF16 1
+#define LLMMM_KIND_FP8_E4M3OUT 2
+#define LLMMM_KIND_FP8_F32OUT 3
+
+/* Which kernel, tiling, wave count, split-K or cluster choice a call with these sizes would get on the current
+ * device with the scratch registered right now, as one line of text (NUL-terminated, truncated to len).
+ * Nothing is launched.  The reference has no heuristics (one fixed tile, src/mm/fp16/mm.cu:9-14; README.md:22
+ * lists auto-tuning as to do). */
+int llmmm_describe_plan(int kind, int M, int N, int K, char* buf, size_t len);
+
+/* The tune(N, K) member of the reference's planned functor (MM_IMPL<T>::tune, src/mm/fp32/impl.h:20, a stub
+ * there).  Here the per-shape choices are closed-form, so tuning is the one-time per-device set-up: function
+ * attributes of every kernel of the family and the cluster occupancy queries, so that the first real call
+ * (possibly inside a latency-critical loop or a stream capture) pays none of it. */
+int llmmm_tune(int kind, int N, int K);
+
 /* Number of kernels launched by this library in the calling process. */
 uint64_t llmmm_launch_count(void);
 

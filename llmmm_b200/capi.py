@@ -56,7 +56,7 @@ EXPORTED_SYMBOLS = (
     "llmmm_last_error", "llmmm_version", "llmmm_fp16_mm_f16", "llmmm_fp16_mm_bf16",
     "llmmm_fp8_blockwise_mm_e4m3out", "llmmm_fp8_blockwise_mm_f32out", "llmmm_fp8_quant_1x128",
     "llmmm_fp8_quant_128x128", "llmmm_fp8_workspace_bytes", "llmmm_set_workspace", "llmmm_check_status",
-    "llmmm_launch_count", "llmmm_split_launch_count", "llmmm_set_static_weights",
+    "llmmm_launch_count", "llmmm_split_launch_count", "llmmm_set_static_weights", "llmmm_describe_plan", "llmmm_tune",
     "llmmm_fp8_blockwise_mm_e4m3out_noalloc",
     "llmmm_transpose_aligned_128", "llmmm_selftest_wait_expiry",
 )
@@ -160,6 +160,21 @@ def fp8_workspace_bytes(M: int, N: int, K: int) -> int:
 
 
 _workspaces: dict[int, torch.Tensor] = {}
+
+
+KINDS = {"fp16": 0, "bf16": 1, "fp8": 2, "fp8_f32out": 3}
+
+
+def describe_plan(kind: str, M: int, N: int, K: int) -> str:
+    """Kernel, tiling, waves and split-K / cluster choice a call with these sizes would get right now."""
+    buf = ctypes.create_string_buffer(512)
+    _check(lib().llmmm_describe_plan(KINDS[kind], M, N, K, buf, ctypes.c_size_t(len(buf))))
+    return buf.value.decode()
+
+
+def tune(kind: str, N: int, K: int) -> None:
+    """One-time per-device set-up of a kernel family (MM_IMPL<T>::tune of the reference's planned functor)."""
+    _check(lib().llmmm_tune(KINDS[kind], N, K))
 
 
 def set_static_weights(enabled: bool) -> None:

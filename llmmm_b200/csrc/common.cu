@@ -215,7 +215,7 @@ __global__ void wait_expiry_selftest_kernel(uint32_t* status, unsigned long long
   }
 }
 
-SplitPlan plan_split(const DeviceInfo* info, int tiles, int k_steps, int fixed, int per_way_x2, int min_gain)
+SplitPlan plan_split(const DeviceInfo* info, int tiles, int k_steps, int fixed, int per_way_x2, int min_gain, bool count)
 {
   const int P = info->max_pairs;
   SplitPlan plan{};
@@ -245,7 +245,9 @@ SplitPlan plan_split(const DeviceInfo* info, int tiles, int k_steps, int fixed, 
     }
   }
   if (ways >= 2) {
-    g_split_launches.fetch_add(1);
+    if (count) {
+      g_split_launches.fetch_add(1);
+    }
     plan.dp_tiles    = tiles - tail_tiles;
     plan.split_s     = ways;
     plan.split_chunk = chunk;

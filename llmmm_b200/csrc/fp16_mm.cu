@@ -645,6 +645,41 @@ static int launch_fp16_pair(const void* A, const void* B, void* C, int M, int N,
   return LLMMM_OK;
 }
 
+void describe_fp16_plan(const DeviceInfo* info, bool bf16, int M, int N, int K, char* buf, size_t len)
+{
+  const char* t = bf16 ? "__nv_bfloat16" : "__half";
+  if (M > 128 && info->max_pairs > 0) {
+    using namespace fp16pair;
+    const int       tiles   = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int       k_steps = (K + BK - 1) / BK;
+    const SplitPlan plan    = plan_split(info, tiles, k_steps, 10, 9, 6, false);
+    if (plan.split_pairs > 0) {
+      snprintf(buf, len, "fp16_gemm_pair_kernel<%s>: %d tiles of 256x256 on %d CTA pairs; %d whole tiles round-robin, then %d "
+               "tiles cut %d-way along K (chunks of %d k-steps of 64), one chunk per pair", t, tiles, plan.pairs, plan.dp_tiles,
+               tiles - plan.dp_tiles, plan.split_s, plan.split_chunk);
+    }
+    else {
+      snprintf(buf, len, "fp16_gemm_pair_kernel<%s>: %d tiles of 256x256 on %d CTA pairs (%.2f waves), %d k-steps of 64 each, "
+               "no split", t, tiles, plan.pairs, (double)tiles / plan.pairs, k_steps);
+    }
+    return;
+  }
+  using namespace fp16cfg;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid  = tiles < info->sm_count ? tiles : info->sm_count;
+  snprintf(buf, len, "fp16_gemm_kernel<%s>: %d tiles of %dx%d on %d CTAs (%.2f waves)", t, tiles, BM, BN, grid, (double)tiles / grid);
+}
+
+int warm_fp16_kernels(const DeviceInfo* info)
+{
+  (void)info;
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp16_gemm_pair_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp16pair::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp16_gemm_pair_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp16pair::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp16_gemm_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp16cfg::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp16_gemm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp16cfg::SMEM_BYTES));
+  return LLMMM_OK;
+}
+
 template<typename T>
 static int launch_fp16(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream)
 {

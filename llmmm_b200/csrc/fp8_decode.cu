@@ -742,6 +742,45 @@ int choose_cluster(const DeviceInfo* info, int M, int N, int K)
 }
 }  // namespace
 
+bool describe_decode_plan(const DeviceInfo* info, int M, int N, int K, char* buf, size_t len)
+{
+  if (M > 64 || N / 128 > deccfg::MAX_GROUPS || (long long)(N / 128) * (K / 128) * 256 >= (1ll << 31)) {
+    return false;
+  }
+  const int mp = padded_m(M);
+  if (const int cluster = choose_cluster(info, M, N, K)) {
+    snprintf(buf, len, "fp8_decode_kernel<%d, cluster>: %d output groups x clusters of %d CTAs, each CTA streams %d or %d of the "
+             "%d K-blocks; reduction through distributed shared memory, no scratch", mp, N / 128, cluster, (K / 128) / cluster,
+             (K / 128 + cluster - 1) / cluster, K / 128);
+    return true;
+  }
+  const Workspace ws = registered_workspace(info->device);
+  if (ws.ptr == nullptr || ws.bytes < decode_workspace_bytes(M)) {
+    return false;  // no scratch: the general kernel runs
+  }
+  const long long U = (long long)(N / 128) * (K / 128);
+  long long       G = info->sm_count < deccfg::MAX_CTAS ? info->sm_count : deccfg::MAX_CTAS;
+  G                 = G < U ? G : U;
+  snprintf(buf, len, "fp8_decode_kernel<%d, stream-K>: %lld weight blocks of 128x128 over %lld CTAs (%.1f each), partial tiles "
+           "through the registered scratch, last-arriving CTA reduces", mp, U, G, (double)U / (double)G);
+  return true;
+}
+
+int warm_decode_kernels(const DeviceInfo* info)
+{
+#define LLMMM_WARM_DECODE(MPV, F32, CL)                                                                                \
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_decode_kernel<MPV, F32, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                      (int)DecodeSmem<MPV>::SMEM_BYTES));
+  LLMMM_WARM_DECODE(16, false, false) LLMMM_WARM_DECODE(16, true, false) LLMMM_WARM_DECODE(16, false, true) LLMMM_WARM_DECODE(16, true, true)
+  LLMMM_WARM_DECODE(32, false, false) LLMMM_WARM_DECODE(32, true, false) LLMMM_WARM_DECODE(32, false, true) LLMMM_WARM_DECODE(32, true, true)
+  LLMMM_WARM_DECODE(64, false, false) LLMMM_WARM_DECODE(64, true, false) LLMMM_WARM_DECODE(64, false, true) LLMMM_WARM_DECODE(64, true, true)
+#undef LLMMM_WARM_DECODE
+  for (int size = 2; size <= 7; ++size) {
+    cluster_capacity(info, size);  // occupancy queries, cached
+  }
+  return LLMMM_OK;
+}
+
 // Returns -1 when the decode path does not apply (M > 64, too many groups, or
 // no scratch buffer large enough is registered): the caller then uses the
 // general kernel, which needs no scratch.

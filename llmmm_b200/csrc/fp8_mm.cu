@@ -857,6 +857,44 @@ static int launch_fp8(const void*  A,
   return LLMMM_OK;
 }
 
+void describe_fp8_plan(const DeviceInfo* info, bool out_f32, int M, int N, int K, char* buf, size_t len)
+{
+  const char* o = out_f32 ? "true" : "false";
+  if (describe_decode_plan(info, M, N, K, buf, len)) {
+    return;
+  }
+  if (M > 128 && info->max_pairs > 0) {
+    using namespace fp8pair;
+    const int       tiles    = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int       k_blocks = K / BK;
+    const SplitPlan plan     = plan_split(info, tiles, k_blocks, 4, 5, 3, false);
+    if (plan.split_pairs > 0) {
+      snprintf(buf, len, "fp8_blockwise_gemm_pair_kernel<%s>: %d tiles of 256x256 on %d CTA pairs; %d whole tiles round-robin, then "
+               "%d tiles cut %d-way along K (chunks of %d K-blocks), one chunk per pair", o, tiles, plan.pairs, plan.dp_tiles,
+               tiles - plan.dp_tiles, plan.split_s, plan.split_chunk);
+    }
+    else {
+      snprintf(buf, len, "fp8_blockwise_gemm_pair_kernel<%s>: %d tiles of 256x256 on %d CTA pairs (%.2f waves), %d K-blocks each, "
+               "no split", o, tiles, plan.pairs, (double)tiles / plan.pairs, k_blocks);
+    }
+    return;
+  }
+  using namespace fp8cfg;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid  = tiles < info->sm_count ? tiles : info->sm_count;
+  snprintf(buf, len, "fp8_blockwise_gemm_kernel<%s>: %d tiles of %dx%d on %d CTAs (%.2f waves)", o, tiles, BM, BN, grid, (double)tiles / grid);
+}
+
+int warm_fp8_kernels(const DeviceInfo* info)
+{
+  (void)info;
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8cfg::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8cfg::SMEM_BYTES));
+  return warm_decode_kernels(info);
+}
+
 static int check_fp8_args(const void* A, const void* A_s, const void* B, const void* B_s, const void* C, int M, int N, int K)
 {
   if (A == nullptr || A_s == nullptr || B == nullptr || B_s == nullptr || C == nullptr) {

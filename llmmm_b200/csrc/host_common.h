@@ -76,6 +76,15 @@ Workspace registered_workspace(int device);
 // Scratch the pair kernels want for splitting the tiles of their last wave (pair_walk.cuh).
 size_t split_workspace_bytes();
 
+// What the launch heuristics choose for a problem, as text (llmmm_describe_plan), and the one-time set-up of
+// every kernel of a family on the current device (llmmm_tune): function attributes, occupancy queries.
+void describe_fp16_plan(const DeviceInfo* info, bool bf16, int M, int N, int K, char* buf, size_t len);
+void describe_fp8_plan(const DeviceInfo* info, bool out_f32, int M, int N, int K, char* buf, size_t len);
+bool describe_decode_plan(const DeviceInfo* info, int M, int N, int K, char* buf, size_t len);  // false: not a decode shape
+int  warm_fp16_kernels(const DeviceInfo* info);
+int  warm_fp8_kernels(const DeviceInfo* info);
+int  warm_decode_kernels(const DeviceInfo* info);
+
 // Launches `kernel` with programmatic stream serialisation allowed (the kernel must execute pdl_wait()
 // before its first access to global memory, see sm100.cuh) and, if cluster > 1, as clusters of that size.
 template<typename... KArgs, typename... Args>

@@ -80,6 +80,7 @@ struct SplitPlan {
 // `k_steps` per tile; the cost of a split is estimated as fixed + per_way_x2 * ways / 2 K-steps, and a
 // split is planned only if it is expected to save at least `min_gain` K-steps over running the last wave
 // with idle pairs.  Without registered scratch (or with nothing to gain) the plan is whole tiles only.
-SplitPlan plan_split(const DeviceInfo* info, int tiles, int k_steps, int fixed, int per_way_x2, int min_gain);
+// `count` = false leaves llmmm_split_launch_count() alone (a query, not a launch).
+SplitPlan plan_split(const DeviceInfo* info, int tiles, int k_steps, int fixed, int per_way_x2, int min_gain, bool count = true);
 
 }  // namespace llmmm

@@ -14,6 +14,7 @@
 #include <vector>
 
 #include "mm/fp16/mm.h"
+#include "mm/mm_impl.h"
 #include "../../oracle/oracle.h"
 
 #define CHECK(call)                                                                                                    \
@@ -95,10 +96,36 @@ int main(int argc, char** argv)
       }
     }
   }
+  // the functor the reference plans (src/mm/fp32/impl.h): tune, run, verify against the result just checked
+  LLMMM::MM_IMPL<half> impl;
+  bool                 functor_ok = true;
+  try {
+    impl.tune(N, K);
+    printf("plan: %s\n", impl.plan(M, N, K).c_str());
+    impl.verify(dA, dB, dC, M, N, K);  // dC holds the product computed above
+    std::vector<uint16_t> bad(Ch);
+    bad[bad.size() / 2] ^= 0x4000;  // one corrupted element must be reported
+    half* dBad;
+    CHECK(cudaMalloc(&dBad, bad.size() * 2));
+    CHECK(cudaMemcpy(dBad, bad.data(), bad.size() * 2, cudaMemcpyDefault));
+    bool caught = false;
+    try {
+      impl.verify(dA, dB, dBad, M, N, K);
+    }
+    catch (const std::runtime_error&) {
+      caught = true;
+    }
+    CHECK(cudaFree(dBad));
+    functor_ok = caught;
+  }
+  catch (const std::runtime_error& e) {
+    fprintf(stderr, "MM_IMPL: %s\n", e.what());
+    functor_ok = false;
+  }
   const double tflops = 2.0 * M * N * K / (ms / reps * 1e-3) / 1e12;
   printf("fp16_mm M=%d N=%d K=%d: %.1f us/launch, %.1f TFLOPS, max_abs_error = %.6f, max_relative_error = %.6f (%d rows vs Kahan)\n",
          M, N, K, ms / reps * 1e3, tflops, max_abs, max_rel, rows_checked);
-  const bool ok = max_rel <= 1e-3f && llmmm_check_status(nullptr) == LLMMM_OK;
+  const bool ok = max_rel <= 1e-3f && functor_ok && llmmm_check_status(nullptr) == LLMMM_OK;
   printf("%s\n", ok ? "PASS" : "FAIL");
   return ok ? 0 : 1;
 }

@@ -91,3 +91,17 @@ def test_build_refuses_spilling_gemm_kernels():
         "    16 bytes stack frame, 12 bytes spill stores, 52 bytes spill loads",
     ])
     assert spilling_kernels(log, ("fp8_blockwise_gemm",)) == ["_ZN5llmmm30fp8_blockwise_gemm_pair_kernelILb0EEEv"]
+
+
+def test_describe_plan_and_tune_validate_before_touching_a_device(capi):
+    L = capi.lib()
+    buf = ctypes.create_string_buffer(256)
+    n = ctypes.c_size_t(len(buf))
+    assert L.llmmm_describe_plan(7, 256, 256, 256, buf, n) == 2 and b"not supported" in L.llmmm_last_error()
+    assert L.llmmm_describe_plan(capi.KINDS["fp8"], 256, 100, 256, buf, n) == 1 and b"not aligned" in L.llmmm_last_error()
+    assert L.llmmm_describe_plan(capi.KINDS["fp16"], 256, 256, 12, buf, n) == 1
+    assert L.llmmm_describe_plan(capi.KINDS["fp16"], 256, 256, 256, None, n) == 1
+    # valid arguments, but this machine has no sm_100 device: unsupported, never a made-up answer
+    assert L.llmmm_describe_plan(capi.KINDS["fp8"], 4096, 4096, 4096, buf, n) == 2 and buf.value == b""
+    assert L.llmmm_tune(capi.KINDS["bf16"], 4096, 4096) == 2
+    assert L.llmmm_tune(9, 4096, 4096) == 2
