@@ -450,6 +450,26 @@ def extra_configs(torch, capi, dev, peaks):
         ms = time_graph(torch, fns * 6)
         helpers[name] = {"us": ms * 1e3, "gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (ms * 1e-3) / 1e9 / hbm}
     out["hbm_helpers_4096x4096"] = helpers
+    del x, q, xt, qt
+    # gate_up projection of the Qwen3-4B MLP at M = 4096 with the SwiGLU epilogue fused (H = silu(gate) * up,
+    # quantised 1x128 for the down projection), beside the plain GEMM of the same [2I, K] weight
+    m, i_, k = 4096, 9728, 2560
+    aq = torch.randint(0, 120, (m, k), dtype=torch.uint8, device=dev)
+    a_s = torch.rand(k // 128, m, device=dev)
+    wsets = [(torch.randint(0, 120, (2 * i_, k), dtype=torch.uint8, device=dev), torch.rand(2 * i_ // 128, k // 128, device=dev))
+             for _ in range(3)]
+    hq = torch.empty(m, i_, dtype=torch.uint8, device=dev)
+    hs = torch.empty(i_ // 128, m, device=dev)
+    cq = torch.empty(m, 2 * i_, dtype=torch.uint8, device=dev)
+    cs = torch.empty(2 * i_ // 128, m, device=dev)
+    capi.ensure_workspace(m, 2 * i_, k)
+    ms_f = time_graph(torch, [(lambda w=w: capi.fp8_blockwise_mm_swiglu(aq, a_s, w[0], w[1], hq, hs, m, i_, k)) for w in wsets] * 4)
+    ms_p = time_graph(torch, [(lambda w=w: capi.fp8_blockwise_mm(aq, a_s, w[0], w[1], cq, cs, m, 2 * i_, k)) for w in wsets] * 4)
+    flop = 2.0 * m * 2 * i_ * k
+    out["swiglu_gate_up_4096x19456x2560"] = {
+        "us_fused": ms_f * 1e3, "tflops_fused": flop / (ms_f * 1e-3) / 1e12,
+        "us_plain_gemm_same_weight": ms_p * 1e3, "tflops_plain": flop / (ms_p * 1e-3) / 1e12,
+        "frac_of_2x_measured_bf16_burst": flop / (ms_f * 1e-3) / 1e12 / (2.0 * float(peaks["bf16_tflops"]))}
     capi.check_status()
     return out
 

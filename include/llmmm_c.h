@@ -82,6 +82,26 @@ int llmmm_fp8_blockwise_mm_e4m3out(const void*    A,
                                    int            K,
                                    llmmm_stream_t stream);
 
+/* gate_up projection with the SwiGLU epilogue fused (the reference's README.md:16 plans this fusion; it has
+ * no implementation of it):
+ *   B_gate_up_t  [2I, K]  e4m3: rows 0..I-1 the gate projection, rows I..2I-1 the up projection
+ *   B_scale_t    [(2I/128), (K/128)] fp32
+ *   acc = the blockwise product of llmmm_fp8_blockwise_mm_e4m3out, [M, 2I], kept on chip
+ *   h[m, i] = silu(acc[m, i]) * acc[m, I + i],  silu(x) = x / (1 + exp(-x))   (fp32)
+ *   H [M, I] e4m3 and H_scale_t [(I/128), M]: h quantised in 1x128 groups along I by the same rule as C above,
+ *   which is the A / A_scale_t format of the down projection that consumes it.
+ * Requires I%128 == 0, K%128 == 0, any M >= 1 (meant for prefill-sized M: 256-row tiles). */
+int llmmm_fp8_blockwise_mm_swiglu_e4m3out(const void*    A,
+                                          const float*   A_scale_t,
+                                          const void*    B_gate_up_t,
+                                          const float*   B_scale_t,
+                                          void*          H,
+                                          float*         H_scale_t,
+                                          int            M,
+                                          int            I,
+                                          int            K,
+                                          llmmm_stream_t stream);
+
 /* Same product with the fp32 accumulator written out unquantised, C [M,N] fp32.
  * Replaces fp8_gemm_blockwise_quant_A_1x128__B_128x128__output_fp32
  * (examples/005.fp8.mm.cu:217-246). */

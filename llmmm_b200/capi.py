@@ -43,6 +43,7 @@ def lib() -> ctypes.CDLL:
             getattr(L, name).argtypes = [_vp, _vp, _vp, _i, _i, _i, _vp]
         L.llmmm_fp8_blockwise_mm_e4m3out.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
         L.llmmm_fp8_blockwise_mm_e4m3out_noalloc.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
+        L.llmmm_fp8_blockwise_mm_swiglu_e4m3out.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
         L.llmmm_fp8_blockwise_mm_f32out.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
         L.llmmm_fp8_quant_1x128.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
         L.llmmm_fp8_quant_128x128.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
@@ -57,7 +58,7 @@ EXPORTED_SYMBOLS = (
     "llmmm_fp8_blockwise_mm_e4m3out", "llmmm_fp8_blockwise_mm_f32out", "llmmm_fp8_quant_1x128",
     "llmmm_fp8_quant_128x128", "llmmm_fp8_workspace_bytes", "llmmm_set_workspace", "llmmm_check_status",
     "llmmm_launch_count", "llmmm_split_launch_count", "llmmm_set_static_weights", "llmmm_describe_plan", "llmmm_tune",
-    "llmmm_fp8_blockwise_mm_e4m3out_noalloc",
+    "llmmm_fp8_blockwise_mm_e4m3out_noalloc", "llmmm_fp8_blockwise_mm_swiglu_e4m3out",
     "llmmm_transpose_aligned_128", "llmmm_selftest_wait_expiry",
 )
 
@@ -122,6 +123,15 @@ def fp8_blockwise_mm_noalloc(A_q, A_s, B_q, B_s, C_q, C_s, M: int, N: int, K: in
         _check(lib().llmmm_fp8_blockwise_mm_e4m3out_noalloc(
             _dev(A_q), _dev(A_s, torch.float32), _dev(B_q), _dev(B_s, torch.float32), _dev(C_q),
             _dev(C_s, torch.float32), M, N, K, _stream(stream)))
+
+
+def fp8_blockwise_mm_swiglu(A_q, A_s, B_gate_up_q, B_s, H_q, H_s, M: int, I: int, K: int, stream=None) -> None:
+    """gate_up projection [2I, K] with the SwiGLU epilogue fused: H = silu(gate) * up, quantised 1x128 along I
+    into H_q [M, I] / H_s [I/128, M] (the A operand of the down projection)."""
+    with torch.cuda.device(A_q.device):
+        _check(lib().llmmm_fp8_blockwise_mm_swiglu_e4m3out(
+            _dev(A_q), _dev(A_s, torch.float32), _dev(B_gate_up_q), _dev(B_s, torch.float32), _dev(H_q),
+            _dev(H_s, torch.float32), M, I, K, _stream(stream)))
 
 
 def fp8_blockwise_mm_f32(A_q, A_s, B_q, B_s, C, M: int, N: int, K: int, stream=None) -> None:

@@ -365,7 +365,8 @@ constexpr uint32_t STAGE_TX   = 2 * (A_BYTES + B_BYTES);  // both CTAs' loads la
 constexpr uint32_t OFF_A      = 0;
 constexpr uint32_t OFF_B      = OFF_A + STAGES * A_BYTES;
 constexpr uint32_t OFF_BAR    = OFF_B + STAGES * B_BYTES;
-constexpr uint32_t SMEM_BYTES = OFF_BAR + 256 + 1024;
+constexpr uint32_t OFF_XCH    = OFF_BAR + 256;  // 2 x 256 floats: row maxima exchanged between the column halves (SWIGLU)
+constexpr uint32_t SMEM_BYTES = OFF_XCH + 2048 + 1024;
 constexpr uint32_t TMEM_COLS  = 512;  // two partial stages of 256 columns
 // split tiles (pair_walk.cuh): a slot holds 16 warp-sized units of 32 rows x 128 columns
 constexpr size_t   SK_UNIT_FLOATS = 32 * 128;
@@ -381,7 +382,19 @@ struct Fp8PairBars {
   uint32_t abort_flag;
 };
 
-template<bool OUT_F32>
+// What the pair kernel does with a finished tile:
+//   EPI_E4M3   C_q e4m3 + C_s (1x128 groups along N)
+//   EPI_F32    C fp32, no quantisation
+//   EPI_SWIGLU B_t holds a gate_up weight [2I, K] (gate rows first); a tile covers 128 output columns: CTA r
+//              loads gate rows n0 + 64r .. and up rows I + n0 + 64r .., so that a thread's 128 accumulators are
+//              64 gate values and the 64 up values of the SAME columns; H = silu(gate) * up is quantised
+//              1x128 along I into H_q [M, I] + H_s [I/128, M], the A-operand format of the next GEMM.
+//              The kernel's N parameter is I.
+constexpr int EPI_E4M3   = 0;
+constexpr int EPI_F32    = 1;
+constexpr int EPI_SWIGLU = 2;
+
+template<int EPI>
 __global__ void __launch_bounds__(fp8pair::THREADS, 1)
   fp8_blockwise_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
                                  const __grid_constant__ CUtensorMap tm_b,
@@ -401,6 +414,9 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
                                  uint32_t* status)
 {
   using namespace fp8pair;
+  constexpr bool OUT_F32 = (EPI == EPI_F32);
+  constexpr bool SWIGLU  = (EPI == EPI_SWIGLU);
+  constexpr int  TILE_N  = SWIGLU ? 128 : BN;  // output columns per tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Fp8PairBars*       bars       = reinterpret_cast<Fp8PairBars*>(smem + OFF_BAR);
@@ -452,7 +468,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
         int      tile, kb0, kb1;
         while (walk.next(tile, kb0, kb1)) {
           const int m0 = (tile % m_tiles) * BM + (int)rank * 128;
-          const int n0 = (tile / m_tiles) * BN + (int)rank * 128;
+          const int n0 = (tile / m_tiles) * TILE_N + (int)rank * (SWIGLU ? 64 : 128);
           for (int kb = kb0; kb < kb1; ++kb, ++it) {
             const uint32_t s  = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1;
@@ -462,7 +478,14 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
               mbar_arrive_expect_tx(&bars->full[s], STAGE_TX);
             }
             tma_load_2d_pair(smem + OFF_A + s * A_BYTES, &tm_a, full_leader, kb * BK, m0);
-            tma_load_2d_pair(smem + OFF_B + s * B_BYTES, &tm_b, full_leader, kb * BK, n0);
+            if constexpr (SWIGLU) {
+              // 64 gate rows, then the 64 up rows of the same output columns (the B descriptor's box is 64 rows)
+              tma_load_2d_pair(smem + OFF_B + s * B_BYTES, &tm_b, full_leader, kb * BK, n0);
+              tma_load_2d_pair(smem + OFF_B + s * B_BYTES + B_BYTES / 2, &tm_b, full_leader, kb * BK, N + n0);
+            }
+            else {
+              tma_load_2d_pair(smem + OFF_B + s * B_BYTES, &tm_b, full_leader, kb * BK, n0);
+            }
           }
         }
       }
@@ -544,14 +567,17 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
     uint32_t it = 0;
     PairWalk walk(pair, n_pairs, k_blocks, dp_tiles, split_pairs, split_s, split_chunk);
     int      tile, kb_lo, kb_hi;
+    uint32_t tile_count = 0;  // SWIGLU: which exchange buffer
     PROF8_STAMP(0);
     while (walk.next(tile, kb_lo, kb_hi)) {
       const int  m    = (tile % m_tiles) * BM + (int)rank * 128 + quarter * 32 + lane;
-      const int  ng   = (tile / m_tiles) * (BN / 128) + half;  // global 128-column group
+      // global 128-column group of the output (and, except for SWIGLU, of the weight scales)
+      const int  ng   = SWIGLU ? tile / m_tiles : (tile / m_tiles) * (BN / 128) + half;
       const bool m_ok = m < M;
       const bool g_ok = ng < n_groups;
       const float* a_s = A_s + (m_ok ? m : 0);
-      const float* b_s = B_s + (size_t)(g_ok ? ng : 0) * k_blocks;
+      const float* b_s = B_s + (size_t)(g_ok ? ng : 0) * k_blocks;               // SWIGLU: the gate rows' scales
+      const float* b_up = B_s + (size_t)(n_groups + (g_ok ? ng : 0)) * k_blocks;  // SWIGLU only: the up rows' scales
 
       float acc[128];
 #pragma unroll
@@ -565,11 +591,14 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
 #define LLMMM_FP8_PREFETCH 2
 #endif
       constexpr int PREFETCH = LLMMM_FP8_PREFETCH;
-      float         a_pf[PREFETCH], b_pf[PREFETCH];
+      float         a_pf[PREFETCH], b_pf[PREFETCH], b2_pf[PREFETCH];
 #pragma unroll
       for (int j = 0; j < PREFETCH; ++j) {
         a_pf[j] = (kb_lo + j < kb_hi) ? __ldg(a_s + (size_t)(kb_lo + j) * M) : 0.0f;
         b_pf[j] = (kb_lo + j < kb_hi) ? __ldg(b_s + kb_lo + j) : 0.0f;
+        if constexpr (SWIGLU) {
+          b2_pf[j] = (kb_lo + j < kb_hi) ? __ldg(b_up + kb_lo + j) : 0.0f;
+        }
       }
       for (int kb0 = kb_lo; kb0 < kb_hi; kb0 += PREFETCH) {
 #pragma unroll
@@ -583,11 +612,19 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
           float a_cur = a_pf[j], b_cur = b_pf[j];
           asm volatile("" : "+f"(a_cur), "+f"(b_cur));
           // one fp32 rounding of the scale product, as in the reference
-          const float    sc  = __fmul_rn(a_cur, b_cur);
-        const float    sc2 = sc;
+          const float sc2 = __fmul_rn(a_cur, b_cur);
+          float       sc2_late = sc2;  // the scale of the last 64 accumulators: the up rows' for SWIGLU
+          if constexpr (SWIGLU) {
+            float b2_cur = b2_pf[j];
+            asm volatile("" : "+f"(b2_cur));
+            sc2_late = __fmul_rn(a_cur, b2_cur);
+          }
           if (kb + PREFETCH < kb_hi) {
             a_pf[j] = __ldg(a_s + (size_t)(kb + PREFETCH) * M);
             b_pf[j] = __ldg(b_s + kb + PREFETCH);
+            if constexpr (SWIGLU) {
+              b2_pf[j] = __ldg(b_up + kb + PREFETCH);
+            }
           }
           PROF8_T(d0);
           mbar_wait(&bars->part_full[p], pp, DEV_WAIT_TMEM_FULL, abort_flag, status);
@@ -636,7 +673,6 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
           // The arithmetic on the last two loads must stay behind the hand-back above: the compiler may
           // move plain FMAs across asm statements, but not asm volatile statements across one another, so
           // the scale is passed through an empty one.
-          float sc2_late = sc2;
           asm volatile("" : "+f"(sc2_late));
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
@@ -651,7 +687,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
       }
 
       PROF8_T(e0);
-      if (kb_hi - kb_lo < k_blocks) {
+      if (!SWIGLU && kb_hi - kb_lo < k_blocks) {  // (SWIGLU tiles are never cut)
         // A chunk of a split tile, the last piece of work of this pair.  This warp's 32x128 piece is handled
         // independently of the other warps: publish the partial sum (four columns per lane side by side:
         // a warp writes 512 contiguous bytes per instruction), count the arrival, and if it is the last
@@ -722,7 +758,42 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
         }
         PROF8_STAMP(5);
       }
-      if (m_ok && g_ok) {
+      if constexpr (SWIGLU) {
+        // acc[0..63] = gate, acc[64..127] = up of this thread's 64 output columns
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const float g = acc[i];
+          const float h = __fdividef(g, 1.0f + __expf(-g)) * acc[64 + i];
+          acc[i]        = h;
+          amax          = fmaxf(amax, fabsf(h));
+        }
+        // the other 64 columns of the 1x128 group belong to the thread of the same row in the other half:
+        // exchange the two maxima through shared memory (two buffers, alternating from tile to tile)
+        float* xch = reinterpret_cast<float*>(smem + OFF_XCH) + (tile_count & 1) * 256;
+        ++tile_count;
+        xch[half * 128 + quarter * 32 + lane] = amax;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        amax = fmaxf(amax, xch[(half ^ 1) * 128 + quarter * 32 + lane]);
+        if (m_ok && g_ok) {
+          const float scale     = __fdiv_rn(amax, 448.0f);
+          const float scale_inv = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 0.0f;
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(C_out) + (size_t)m * N + (size_t)ng * 128 + half * 64);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 o;
+            o.x    = pack_e4m3x4(acc[16 * i + 0] * scale_inv, acc[16 * i + 1] * scale_inv, acc[16 * i + 2] * scale_inv, acc[16 * i + 3] * scale_inv);
+            o.y    = pack_e4m3x4(acc[16 * i + 4] * scale_inv, acc[16 * i + 5] * scale_inv, acc[16 * i + 6] * scale_inv, acc[16 * i + 7] * scale_inv);
+            o.z    = pack_e4m3x4(acc[16 * i + 8] * scale_inv, acc[16 * i + 9] * scale_inv, acc[16 * i + 10] * scale_inv, acc[16 * i + 11] * scale_inv);
+            o.w    = pack_e4m3x4(acc[16 * i + 12] * scale_inv, acc[16 * i + 13] * scale_inv, acc[16 * i + 14] * scale_inv, acc[16 * i + 15] * scale_inv);
+            dst[i] = o;
+          }
+          if (half == 0) {
+            C_s[(size_t)ng * M + m] = scale;
+          }
+        }
+      }
+      else if (m_ok && g_ok) {
         if constexpr (OUT_F32) {
           float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(C_out) + (size_t)m * N + (size_t)ng * 128);
 #pragma unroll
@@ -799,7 +870,7 @@ static int launch_fp8_pair(const void*       A,
   static thread_local bool attr_set[64] = {};
   if (!attr_set[info->device]) {
     LLMMM_CUDA_TRY(cudaFuncSetAttribute(
-      fp8_blockwise_gemm_pair_kernel<OUT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+      fp8_blockwise_gemm_pair_kernel<(OUT_F32 ? EPI_F32 : EPI_E4M3)>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
     attr_set[info->device] = true;
   }
   const int tiles    = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
@@ -807,9 +878,47 @@ static int launch_fp8_pair(const void*       A,
   // estimated cost of a split, in K-blocks (one takes about 0.58 us): publishing a chunk and counting the
   // arrival about 3 us, reading a chunk back about 1.5 us
   const SplitPlan plan = plan_split(info, tiles, k_blocks, /*fixed*/ 4, /*per_way_x2*/ 5, /*min_gain*/ 3);
-  LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<OUT_F32>, dim3(2 * plan.pairs), dim3(THREADS), SMEM_BYTES, stream,
+  LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<(OUT_F32 ? EPI_F32 : EPI_E4M3)>, dim3(2 * plan.pairs), dim3(THREADS), SMEM_BYTES, stream,
                             2, tm_a, tm_b, A_s, B_s, C, C_s, M, N, K, plan.dp_tiles, plan.split_pairs, plan.split_s,
                             plan.split_chunk, plan.partials, plan.counters, info->status));
+  g_launches.fetch_add(1);
+  return LLMMM_OK;
+}
+
+// gate_up GEMM with the SwiGLU epilogue: B [2I, K], B_s [2I/128, K/128], H_q [M, I], H_s [I/128, M].
+static int launch_fp8_swiglu(const void*       A,
+                             const float*      A_s,
+                             const void*       B,
+                             const float*      B_s,
+                             void*             H,
+                             float*            H_s,
+                             int               M,
+                             int               I,
+                             int               K,
+                             const DeviceInfo* info,
+                             cudaStream_t      stream)
+{
+  using namespace fp8pair;
+  CUtensorMap tm_a, tm_b;
+  if (!make_tmap_2d(&tm_a, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)M, (uint64_t)K, BK, 128, CU_TENSOR_MAP_SWIZZLE_128B)
+      || !make_tmap_2d(&tm_b, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)2 * I, (uint64_t)K, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B)) {
+    return LLMMM_ERR_CUDA;
+  }
+  static thread_local bool attr_set[64] = {};
+  if (!attr_set[info->device]) {
+    LLMMM_CUDA_TRY(cudaFuncSetAttribute(
+      fp8_blockwise_gemm_pair_kernel<EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+    attr_set[info->device] = true;
+  }
+  // a tile is 256 rows x 128 output columns (128 gate + 128 up weight rows); tiles are never cut along K here:
+  // the two threads that share a 1x128 output group would have to finish the same piece
+  const int tiles = ((M + BM - 1) / BM) * (I / 128);
+  const int pairs = tiles < info->max_pairs ? tiles : info->max_pairs;
+  float*    no_partials = nullptr;
+  uint32_t* no_counters = nullptr;
+  LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<EPI_SWIGLU>, dim3(2 * pairs), dim3(THREADS), SMEM_BYTES, stream, 2,
+                            tm_a, tm_b, A_s, B_s, H, H_s, M, I, K, tiles, 0, 1, K / BK, no_partials, no_counters,
+                            info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
 }
@@ -888,8 +997,9 @@ void describe_fp8_plan(const DeviceInfo* info, bool out_f32, int M, int N, int K
 int warm_fp8_kernels(const DeviceInfo* info)
 {
   (void)info;
-  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
-  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_E4M3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8cfg::SMEM_BYTES));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8cfg::SMEM_BYTES));
   return warm_decode_kernels(info);
@@ -973,6 +1083,39 @@ int llmmm_fp8_blockwise_mm_e4m3out(const void*    A,
     return rc;
   }
   return llmmm::launch_fp8<false>(A, A_scale_t, B_t, B_scale_t, C, C_scale_t, M, N, K, s);
+}
+
+int llmmm_fp8_blockwise_mm_swiglu_e4m3out(const void*    A,
+                                          const float*   A_scale_t,
+                                          const void*    B_gate_up_t,
+                                          const float*   B_scale_t,
+                                          void*          H,
+                                          float*         H_scale_t,
+                                          int            M,
+                                          int            I,
+                                          int            K,
+                                          llmmm_stream_t stream)
+{
+  using namespace llmmm;
+  if (A == nullptr || A_scale_t == nullptr || B_gate_up_t == nullptr || B_scale_t == nullptr || H == nullptr
+      || H_scale_t == nullptr) {
+    return set_error(LLMMM_ERR_SHAPE, "null pointer argument");
+  }
+  if (M < 1 || I < 128 || K < 128 || (I % 128) != 0 || (K % 128) != 0) {
+    return set_error(LLMMM_ERR_SHAPE, "M or I or K are not aligned. (need M>=1, I%%128==0, K%%128==0; got %d %d %d)", M, I, K);
+  }
+  if (((uintptr_t)A | (uintptr_t)B_gate_up_t | (uintptr_t)H) & 15) {
+    return set_error(LLMMM_ERR_SHAPE, "A, B and H must be 16-byte aligned");
+  }
+  const DeviceInfo* info = device_info();
+  if (info == nullptr) {
+    return LLMMM_ERR_UNSUPPORTED;
+  }
+  if (info->max_pairs < 1) {
+    return set_error(LLMMM_ERR_UNSUPPORTED, "this device cannot hold a cluster of two CTAs of the GEMM kernel");
+  }
+  return launch_fp8_swiglu(A, A_scale_t, B_gate_up_t, B_scale_t, H, H_scale_t, M, I, K, info,
+                           reinterpret_cast<cudaStream_t>(stream));
 }
 
 int llmmm_fp8_blockwise_mm_f32out(const void*    A,

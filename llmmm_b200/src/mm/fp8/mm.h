@@ -46,6 +46,24 @@ LLMMM_FP8_LAUNCHER(fp8_gemm_blockwise_quant_A_1x128__B_128x128__C_1x128__output_
 LLMMM_FP8_LAUNCHER(_fp8_gemm_blockwise_quant_A_1x128__B_128x128__C_1x128__output_fp8__opt_reg__quadra_buffer__inner_split)
 #undef LLMMM_FP8_LAUNCHER
 
+// The epilogue fusion the reference plans (README.md:16: SiLU * gate on the gate_up projection); named after
+// the launchers above.  B_transposed is the gate_up weight [2I, K] with the gate rows first; C [M, I] and
+// C_scale_transposed [(I/128), M] hold silu(gate) * up quantised 1x128 along I.
+inline void fp8_gemm_blockwise_quant_A_1x128__B_128x128__swiglu__C_1x128__output_fp8(const __nv_fp8_e4m3* A,
+                                                                                     const float*         A_scale_transposed,
+                                                                                     const __nv_fp8_e4m3* B_transposed,
+                                                                                     const float*         B_scale_transposed,
+                                                                                     __nv_fp8_e4m3*       C,
+                                                                                     float*               C_scale_transposed,
+                                                                                     int                  M,
+                                                                                     int                  I,
+                                                                                     int                  K,
+                                                                                     cudaStream_t         stream)
+{
+  LLMMM::throw_on_error(llmmm_fp8_blockwise_mm_swiglu_e4m3out(
+    A, A_scale_transposed, B_transposed, B_scale_transposed, C, C_scale_transposed, M, I, K, stream));
+}
+
 inline void fp8_gemm_blockwise_quant_A_1x128__B_128x128__output_fp32(const __nv_fp8_e4m3* A,
                                                                      const float*         A_scale_transposed,
                                                                      const __nv_fp8_e4m3* B_transposed,

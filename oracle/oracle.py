@@ -232,6 +232,26 @@ def fp8_blockwise_mm(A_q, A_s, B_q, B_s):
     return q, s, acc
 
 
+def swiglu(acc: np.ndarray) -> np.ndarray:
+    """h[m, i] = silu(acc[m, i]) * acc[m, I + i] for a gate_up accumulator [M, 2I] (gate columns first),
+    silu(x) = x / (1 + exp(-x)); computed in the dtype of `acc` (fp32: the kernel's arithmetic up to the
+    exponential's last bits; fp64: ground truth).  The reference only plans this fusion (README.md:16), so
+    the definition is the usual SwiGLU one."""
+    I = acc.shape[1] // 2
+    gate, up = acc[:, :I], acc[:, I:]
+    one = acc.dtype.type(1)
+    with np.errstate(over="ignore"):
+        return (gate / (one + np.exp(-gate)) * up).astype(acc.dtype)
+
+
+def fp8_blockwise_mm_swiglu(A_q, A_s, B_q, B_s, row0: int = 0, rows: int | None = None):
+    """gate_up GEMM + SwiGLU + 1x128 quantisation along I: (H_q, H_s, h_f32, h_f64_truth)."""
+    h32 = swiglu(fp8_blockwise_acc(A_q, A_s, B_q, B_s, row0=row0, rows=rows))
+    h64 = swiglu(fp8_blockwise_acc(A_q, A_s, B_q, B_s, exact=True, row0=row0, rows=rows))
+    q, s = c_quant_1x128(h32)
+    return q, s, h32, h64
+
+
 def transpose(x: np.ndarray) -> np.ndarray:
     """src/base/base.cu:125-152 for 1- and 4-byte elements."""
     x = np.ascontiguousarray(x)
