@@ -297,6 +297,7 @@ struct Fp16PairBars {
   uint64_t empty[fp16pair::STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t fix[4];  // one per epilogue warp: the other chunk of a split tile has landed in shared memory
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
@@ -340,6 +341,9 @@ __global__ void __launch_bounds__(fp16pair::THREADS, 1)
     for (int a = 0; a < 2; ++a) {
       mbar_init(&bars->tmem_full[a], 1);
       mbar_init(&bars->tmem_empty[a], 8);  // 4 epilogue warps of each CTA
+    }
+    for (int w = 0; w < 4; ++w) {
+      mbar_init(&bars->fix[w], 1);
     }
     bars->abort_flag = 0;
     fence_mbar_init();
@@ -530,8 +534,15 @@ __global__ void __launch_bounds__(fp16pair::THREADS, 1)
       // tensor memory) and write the tile.  Nothing here waits for another CTA.
       const int      tt   = tile - dp_tiles;
       const uint32_t unit = rank * 4 + (uint32_t)ew;
-      constexpr size_t UNIT_FLOAT4 = SPLIT_SLOT_FLOATS / 8 / 4;  // 8 units of 32 rows x 256 columns per slot
-      float4* mine = reinterpret_cast<float4*>(sk_partials + (size_t)pair * SPLIT_SLOT_FLOATS) + unit * UNIT_FLOAT4 + lane;
+      constexpr size_t   UNIT_FLOAT4 = SPLIT_SLOT_FLOATS / 8 / 4;  // 8 units of 32 rows x 256 columns per slot
+      constexpr uint32_t UNIT_BYTES  = (uint32_t)(UNIT_FLOAT4 * 16);
+      static_assert(4 * UNIT_BYTES <= OFF_C, "the four staging units must fit into the operand ring");
+      // The operand ring is idle (the last MMAs of this CTA pair are done): this warp's 32 KB of it stage
+      // the piece on its way out and, for the warp that sums, the other chunk on its way in.  Bulk copies
+      // move a piece about three times faster than the load/store units do (measured: 128 KB per CTA in
+      // 2.2 us with 16-byte stores).
+      float4* stage = reinterpret_cast<float4*>(smem + OFF_A + (uint32_t)ew * UNIT_BYTES) + lane;
+      float*  mine  = sk_partials + (size_t)pair * SPLIT_SLOT_FLOATS + unit * (UNIT_FLOAT4 * 4);
 #pragma unroll 1
       for (int c = 0; c < BN / 64; ++c) {
         uint32_t v0[32], v1[32];
@@ -540,60 +551,100 @@ __global__ void __launch_bounds__(fp16pair::THREADS, 1)
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          __stcg(mine + (c * 16 + j) * 32, make_float4(__uint_as_float(v0[4 * j]), __uint_as_float(v0[4 * j + 1]),
-                                                       __uint_as_float(v0[4 * j + 2]), __uint_as_float(v0[4 * j + 3])));
+          stage[(c * 16 + j) * 32] = make_float4(__uint_as_float(v0[4 * j]), __uint_as_float(v0[4 * j + 1]),
+                                                 __uint_as_float(v0[4 * j + 2]), __uint_as_float(v0[4 * j + 3]));
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          __stcg(mine + (c * 16 + 8 + j) * 32, make_float4(__uint_as_float(v1[4 * j]), __uint_as_float(v1[4 * j + 1]),
-                                                           __uint_as_float(v1[4 * j + 2]), __uint_as_float(v1[4 * j + 3])));
+          stage[(c * 16 + 8 + j) * 32] = make_float4(__uint_as_float(v1[4 * j]), __uint_as_float(v1[4 * j + 1]),
+                                                     __uint_as_float(v1[4 * j + 2]), __uint_as_float(v1[4 * j + 3]));
         }
       }
-      __threadfence();
+      fence_proxy_async_smem();
       __syncwarp();
       uint32_t arrived = 0;
       if (lane == 0) {
+        bulk_store(mine, stage, UNIT_BYTES);
+        tma_store_commit();
+        tma_store_wait_all<0>();  // written, not merely read out of shared memory
+        fence_proxy_async_all();
+        __threadfence();
         arrived = atomicAdd(&sk_counters[tt * 16 + unit], 1u);
       }
       arrived = __shfl_sync(0xffffffffu, arrived, 0);
       if (arrived == (uint32_t)(split_s - 1)) {
         __threadfence();
         const int my_chunk = pair % split_s;
+        if (split_s == 2) {
+          // two chunks: a + b == b + a bit for bit; this pair's chunk is still in tensor memory, the other
+          // one comes in with one bulk copy
+          if (lane == 0) {
+            fence_proxy_async_all();
+            mbar_arrive_expect_tx(&bars->fix[ew], UNIT_BYTES);
+            bulk_load(stage, sk_partials + (size_t)(pair ^ 1) * SPLIT_SLOT_FLOATS + unit * (UNIT_FLOAT4 * 4), UNIT_BYTES,
+                      &bars->fix[ew]);
+          }
+          mbar_wait(&bars->fix[ew], 0, DEV_WAIT_TMEM_FULL, abort_flag, status);
 #pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
-          uint32_t s0[32], s1[32];
-#pragma unroll 1
-          for (int w = 0; w < split_s; ++w) {
-            uint32_t v0[32], v1[32];
-            if (w == my_chunk) {
-              tmem_ld_32x32b_x32(t_addr + c * 64, v0);
-              tmem_ld_32x32b_x32(t_addr + c * 64 + 32, v1);
-              tmem_ld_wait();
-            }
-            else {
-              const float4* src = reinterpret_cast<const float4*>(sk_partials + (size_t)(tt * split_s + w) * SPLIT_SLOT_FLOATS)
-                                  + unit * UNIT_FLOAT4 + lane;
+          for (int c = 0; c < BN / 64; ++c) {
+            uint32_t s0[32], s1[32];
+            tmem_ld_32x32b_x32(t_addr + c * 64, s0);
+            tmem_ld_32x32b_x32(t_addr + c * 64 + 32, s1);
+            tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float4 a = __ldcg(src + (c * 16 + j) * 32);
-                const float4 b = __ldcg(src + (c * 16 + 8 + j) * 32);
-                v0[4 * j]     = __float_as_uint(a.x);
-                v0[4 * j + 1] = __float_as_uint(a.y);
-                v0[4 * j + 2] = __float_as_uint(a.z);
-                v0[4 * j + 3] = __float_as_uint(a.w);
-                v1[4 * j]     = __float_as_uint(b.x);
-                v1[4 * j + 1] = __float_as_uint(b.y);
-                v1[4 * j + 2] = __float_as_uint(b.z);
-                v1[4 * j + 3] = __float_as_uint(b.w);
+            for (int j = 0; j < 8; ++j) {
+              const float4 a = stage[(c * 16 + j) * 32];
+              const float4 b = stage[(c * 16 + 8 + j) * 32];
+              s0[4 * j]     = __float_as_uint(__uint_as_float(s0[4 * j]) + a.x);
+              s0[4 * j + 1] = __float_as_uint(__uint_as_float(s0[4 * j + 1]) + a.y);
+              s0[4 * j + 2] = __float_as_uint(__uint_as_float(s0[4 * j + 2]) + a.z);
+              s0[4 * j + 3] = __float_as_uint(__uint_as_float(s0[4 * j + 3]) + a.w);
+              s1[4 * j]     = __float_as_uint(__uint_as_float(s1[4 * j]) + b.x);
+              s1[4 * j + 1] = __float_as_uint(__uint_as_float(s1[4 * j + 1]) + b.y);
+              s1[4 * j + 2] = __float_as_uint(__uint_as_float(s1[4 * j + 2]) + b.z);
+              s1[4 * j + 3] = __float_as_uint(__uint_as_float(s1[4 * j + 3]) + b.w);
+            }
+            convert_and_store(s0, s1, m0, n0, c);
+          }
+        }
+        else {
+          // more chunks: added in the order of their K ranges, read with plain loads
+#pragma unroll 1
+          for (int c = 0; c < BN / 64; ++c) {
+            uint32_t s0[32], s1[32];
+#pragma unroll 1
+            for (int w = 0; w < split_s; ++w) {
+              uint32_t v0[32], v1[32];
+              if (w == my_chunk) {
+                tmem_ld_32x32b_x32(t_addr + c * 64, v0);
+                tmem_ld_32x32b_x32(t_addr + c * 64 + 32, v1);
+                tmem_ld_wait();
+              }
+              else {
+                const float4* src = reinterpret_cast<const float4*>(sk_partials + (size_t)(tt * split_s + w) * SPLIT_SLOT_FLOATS)
+                                    + unit * UNIT_FLOAT4 + lane;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float4 a = __ldcg(src + (c * 16 + j) * 32);
+                  const float4 b = __ldcg(src + (c * 16 + 8 + j) * 32);
+                  v0[4 * j]     = __float_as_uint(a.x);
+                  v0[4 * j + 1] = __float_as_uint(a.y);
+                  v0[4 * j + 2] = __float_as_uint(a.z);
+                  v0[4 * j + 3] = __float_as_uint(a.w);
+                  v1[4 * j]     = __float_as_uint(b.x);
+                  v1[4 * j + 1] = __float_as_uint(b.y);
+                  v1[4 * j + 2] = __float_as_uint(b.z);
+                  v1[4 * j + 3] = __float_as_uint(b.w);
+                }
+              }
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                s0[i] = (w == 0) ? v0[i] : __float_as_uint(__uint_as_float(s0[i]) + __uint_as_float(v0[i]));
+                s1[i] = (w == 0) ? v1[i] : __float_as_uint(__uint_as_float(s1[i]) + __uint_as_float(v1[i]));
               }
             }
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              s0[i] = (w == 0) ? v0[i] : __float_as_uint(__uint_as_float(s0[i]) + __uint_as_float(v0[i]));
-              s1[i] = (w == 0) ? v1[i] : __float_as_uint(__uint_as_float(s1[i]) + __uint_as_float(v1[i]));
-            }
+            convert_and_store(s0, s1, m0, n0, c);
           }
-          convert_and_store(s0, s1, m0, n0, c);
         }
         if (lane == 0) {
           sk_counters[tt * 16 + unit] = 0;  // every launch leaves the counters at zero

@@ -196,6 +196,31 @@ __device__ __forceinline__ void tma_store_wait_all()
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// Untiled bulk copies (both addresses 16-byte aligned, size a multiple of 16 bytes).
+// shared -> global, completion through the bulk async-group (tma_store_commit / tma_store_wait_all)
+__device__ __forceinline__ void bulk_store(void* gdst, const void* ssrc, uint32_t bytes)
+{
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               :
+               : "l"(reinterpret_cast<uint64_t>(gdst)), "r"(smem_u32(ssrc)), "r"(bytes)
+               : "memory");
+}
+
+// global -> this CTA's shared memory, completion on an mbarrier of this CTA (complete_tx of `bytes`)
+__device__ __forceinline__ void bulk_load(void* sdst, const void* gsrc, uint32_t bytes, uint64_t* bar)
+{
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :
+               : "r"(smem_u32(sdst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+// orders accesses of the generic and the async proxy to any state space (global data handed between them)
+__device__ __forceinline__ void fence_proxy_async_all()
+{
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+
 // L2 eviction policies for TMA loads.
 __device__ __forceinline__ uint64_t policy_evict_first()
 {
