@@ -513,9 +513,26 @@ def nsplit_config(torch, dist, capi, dev, rank, world):
     ms_gemm = timed(gemm, 10)
     ms_both = timed(lambda: (gemm(), shard.all_gather_c_n(C_q, C_s, Nn)), 5)
     flops = 2.0 * Mm * Nn * Kk
+    # the same gather done by the GEMM itself: every rank's epilogue stores its column shard into the full C of
+    # every rank (peer buffers mapped with CUDA IPC), checked against the NCCL-gathered result
+    try:
+        po = shard.PeerOutputs(Mm, Nn, dev)
+        dq, ds = po.dsts()
+        ms_fused = timed(lambda: capi.fp8_blockwise_mm_gather(A_q, A_s, B_q, B_s, dq, ds, Nn, n0, Mm, nr, Kk), 10)
+        po.wait_all()
+        gemm()
+        q_ref, s_ref = shard.all_gather_c_n(C_q, C_s, Nn)
+        same = bool(torch.equal(po.C_q, q_ref) and torch.equal(po.C_s, s_ref))
+        ok = torch.tensor([1 if same else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        fused = {"ms_gemm_with_fused_gather": ms_fused, "tflops_total_with_fused_gather": flops / (ms_fused * 1e-3) / 1e12,
+                 "fused_gather_equals_nccl_gather_on_all_ranks": bool(ok.item())}
+        po.close()
+    except Exception as e:  # a box without peer access between its GPUs: the NCCL figures above stand alone
+        fused = {"fused_gather_unavailable": repr(e)[:200]}
     return {"shape": "M=8192 N=37888 K=3584, N-split", "ranks": world, "ms_gemm": ms_gemm,
             "tflops_gemm_total": flops / (ms_gemm * 1e-3) / 1e12, "ms_gemm_plus_allgather": ms_both,
-            "gathered_bytes_per_rank": Mm * Nn + 4 * (Nn // 128) * Mm}
+            "gathered_bytes_per_rank": Mm * Nn + 4 * (Nn // 128) * Mm, **fused}
 
 
 if __name__ == "__main__":

@@ -82,6 +82,28 @@ int llmmm_fp8_blockwise_mm_e4m3out(const void*    A,
                                    int            K,
                                    llmmm_stream_t stream);
 
+/* N-split across GPUs with the all-gather of the outputs fused into the GEMM: this call computes the column
+ * shard [col_offset, col_offset + N) of a product that is N_total columns wide (B_t / B_scale_t are this
+ * rank's slabs: [N, K] and [(N/128), (K/128)]) and stores the shard into the FULL outputs
+ * C [M, N_total] e4m3 and C_scale_t [(N_total/128), M] of n_dsts (1..8) destinations: this GPU's own buffers
+ * and the other GPUs' buffers mapped into this process (CUDA IPC / peer access).  The peer stores are plain
+ * stores issued by the epilogue while other tiles are still being computed; when the kernel has completed on
+ * every rank (stream order + a barrier between the ranks) every destination holds the whole C.  The reference
+ * has no multi-GPU code.  Shapes as for llmmm_fp8_blockwise_mm_e4m3out; N_total, col_offset multiples of 128. */
+int llmmm_fp8_blockwise_mm_e4m3out_gather(const void*    A,
+                                          const float*   A_scale_t,
+                                          const void*    B_t,
+                                          const float*   B_scale_t,
+                                          void* const*   C_dsts,
+                                          float* const*  C_scale_dsts,
+                                          int            n_dsts,
+                                          int            N_total,
+                                          int            col_offset,
+                                          int            M,
+                                          int            N,
+                                          int            K,
+                                          llmmm_stream_t stream);
+
 /* gate_up projection with the SwiGLU epilogue fused (the reference's README.md:16 plans this fusion; it has
  * no implementation of it):
  *   B_gate_up_t  [2I, K]  e4m3: rows 0..I-1 the gate projection, rows I..2I-1 the up projection

@@ -44,6 +44,8 @@ def lib() -> ctypes.CDLL:
         L.llmmm_fp8_blockwise_mm_e4m3out.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
         L.llmmm_fp8_blockwise_mm_e4m3out_noalloc.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
         L.llmmm_fp8_blockwise_mm_swiglu_e4m3out.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
+        L.llmmm_fp8_blockwise_mm_e4m3out_gather.argtypes = [_vp, _vp, _vp, _vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp),
+                                                            _i, _i, _i, _i, _i, _i, _vp]
         L.llmmm_fp8_blockwise_mm_f32out.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
         L.llmmm_fp8_quant_1x128.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
         L.llmmm_fp8_quant_128x128.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
@@ -59,6 +61,7 @@ EXPORTED_SYMBOLS = (
     "llmmm_fp8_quant_128x128", "llmmm_fp8_workspace_bytes", "llmmm_set_workspace", "llmmm_check_status",
     "llmmm_launch_count", "llmmm_split_launch_count", "llmmm_set_static_weights", "llmmm_describe_plan", "llmmm_tune",
     "llmmm_fp8_blockwise_mm_e4m3out_noalloc", "llmmm_fp8_blockwise_mm_swiglu_e4m3out",
+    "llmmm_fp8_blockwise_mm_e4m3out_gather",
     "llmmm_transpose_aligned_128", "llmmm_selftest_wait_expiry",
 )
 
@@ -123,6 +126,26 @@ def fp8_blockwise_mm_noalloc(A_q, A_s, B_q, B_s, C_q, C_s, M: int, N: int, K: in
         _check(lib().llmmm_fp8_blockwise_mm_e4m3out_noalloc(
             _dev(A_q), _dev(A_s, torch.float32), _dev(B_q), _dev(B_s, torch.float32), _dev(C_q),
             _dev(C_s, torch.float32), M, N, K, _stream(stream)))
+
+
+def fp8_blockwise_mm_gather(A_q, A_s, B_q, B_s, C_dsts, Cs_dsts, N_total: int, col_offset: int, M: int, N: int, K: int,
+                            stream=None) -> None:
+    """Column shard [col_offset, col_offset + N) of an N_total-wide product, stored into the full C_q [M, N_total] /
+    C_s [N_total/128, M] of every destination (this GPU's and the peers' mapped buffers): the all-gather of an
+    N-split happens in the GEMM's epilogue.  Destinations are tensors or raw device addresses."""
+    n = len(C_dsts)
+    if n != len(Cs_dsts) or not 1 <= n <= 8:
+        raise RuntimeError("between 1 and 8 destinations are needed")
+
+    def addr(t, dtype):
+        return t if isinstance(t, int) else _dev(t, dtype)
+
+    c_arr = (ctypes.c_void_p * n)(*[addr(t, torch.uint8) for t in C_dsts])
+    s_arr = (ctypes.c_void_p * n)(*[addr(t, torch.float32) for t in Cs_dsts])
+    with torch.cuda.device(A_q.device):
+        _check(lib().llmmm_fp8_blockwise_mm_e4m3out_gather(
+            _dev(A_q), _dev(A_s, torch.float32), _dev(B_q), _dev(B_s, torch.float32), c_arr, s_arr, n, N_total,
+            col_offset, M, N, K, _stream(stream)))
 
 
 def fp8_blockwise_mm_swiglu(A_q, A_s, B_gate_up_q, B_s, H_q, H_s, M: int, I: int, K: int, stream=None) -> None:

@@ -390,9 +390,23 @@ struct Fp8PairBars {
 //              64 gate values and the 64 up values of the SAME columns; H = silu(gate) * up is quantised
 //              1x128 along I into H_q [M, I] + H_s [I/128, M], the A-operand format of the next GEMM.
 //              The kernel's N parameter is I.
+//   EPI_GATHER like EPI_E4M3, but this call computes a column shard [col0, col0 + N) of a wider C and stores it
+//              into the full C_q [M, ld] / C_s [ld/128, M] of up to 8 destinations at once -- the buffers of the
+//              other GPUs of an N-split, mapped into this process: the all-gather of the outputs happens as
+//              plain peer stores of the epilogue, overlapped with the tiles still being computed.
 constexpr int EPI_E4M3   = 0;
 constexpr int EPI_F32    = 1;
 constexpr int EPI_SWIGLU = 2;
+constexpr int EPI_GATHER = 3;
+
+struct GatherDst {
+  uint8_t* c[8];   // C_q base of every destination
+  float*   cs[8];  // C_s base of every destination
+  int      n;      // destinations in use
+  int      ld;     // columns of the full C
+  int      col0;   // first column of this call's shard in the full C
+  int      pad;
+};
 
 template<int EPI>
 __global__ void __launch_bounds__(fp8pair::THREADS, 1)
@@ -411,6 +425,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
                                  int       split_chunk,
                                  float* __restrict__ sk_partials,
                                  uint32_t* __restrict__ sk_counters,
+                                 const __grid_constant__ GatherDst gather,
                                  uint32_t* status)
 {
   using namespace fp8pair;
@@ -794,7 +809,32 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
         }
       }
       else if (m_ok && g_ok) {
-        if constexpr (OUT_F32) {
+        if constexpr (EPI == EPI_GATHER) {
+          float amax = 0.0f;
+#pragma unroll
+          for (int i = 0; i < 128; ++i) {
+            amax = fmaxf(amax, fabsf(acc[i]));
+          }
+          const float  scale     = __fdiv_rn(amax, 448.0f);
+          const float  scale_inv = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 0.0f;
+          const size_t q_off     = (size_t)m * gather.ld + (size_t)gather.col0 + (size_t)ng * 128;
+          const size_t s_off     = (size_t)(gather.col0 / 128 + ng) * M + m;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            uint4 o;
+            o.x = pack_e4m3x4(acc[16 * i + 0] * scale_inv, acc[16 * i + 1] * scale_inv, acc[16 * i + 2] * scale_inv, acc[16 * i + 3] * scale_inv);
+            o.y = pack_e4m3x4(acc[16 * i + 4] * scale_inv, acc[16 * i + 5] * scale_inv, acc[16 * i + 6] * scale_inv, acc[16 * i + 7] * scale_inv);
+            o.z = pack_e4m3x4(acc[16 * i + 8] * scale_inv, acc[16 * i + 9] * scale_inv, acc[16 * i + 10] * scale_inv, acc[16 * i + 11] * scale_inv);
+            o.w = pack_e4m3x4(acc[16 * i + 12] * scale_inv, acc[16 * i + 13] * scale_inv, acc[16 * i + 14] * scale_inv, acc[16 * i + 15] * scale_inv);
+            for (int d = 0; d < gather.n; ++d) {
+              reinterpret_cast<uint4*>(gather.c[d] + q_off)[i] = o;
+            }
+          }
+          for (int d = 0; d < gather.n; ++d) {
+            gather.cs[d][s_off] = scale;
+          }
+        }
+        else if constexpr (OUT_F32) {
           float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(C_out) + (size_t)m * N + (size_t)ng * 128);
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -880,7 +920,7 @@ static int launch_fp8_pair(const void*       A,
   const SplitPlan plan = plan_split(info, tiles, k_blocks, /*fixed*/ 4, /*per_way_x2*/ 5, /*min_gain*/ 3);
   LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<(OUT_F32 ? EPI_F32 : EPI_E4M3)>, dim3(2 * plan.pairs), dim3(THREADS), SMEM_BYTES, stream,
                             2, tm_a, tm_b, A_s, B_s, C, C_s, M, N, K, plan.dp_tiles, plan.split_pairs, plan.split_s,
-                            plan.split_chunk, plan.partials, plan.counters, info->status));
+                            plan.split_chunk, plan.partials, plan.counters, GatherDst{}, info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
 }
@@ -918,7 +958,41 @@ static int launch_fp8_swiglu(const void*       A,
   uint32_t* no_counters = nullptr;
   LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<EPI_SWIGLU>, dim3(2 * pairs), dim3(THREADS), SMEM_BYTES, stream, 2,
                             tm_a, tm_b, A_s, B_s, H, H_s, M, I, K, tiles, 0, 1, K / BK, no_partials, no_counters,
-                            info->status));
+                            GatherDst{}, info->status));
+  g_launches.fetch_add(1);
+  return LLMMM_OK;
+}
+
+// Column shard [col0, col0 + N) of a wider product, stored into every destination's full C (EPI_GATHER).
+static int launch_fp8_gather(const void*       A,
+                             const float*      A_s,
+                             const void*       B,
+                             const float*      B_s,
+                             const GatherDst&  dst,
+                             int               M,
+                             int               N,
+                             int               K,
+                             const DeviceInfo* info,
+                             cudaStream_t      stream)
+{
+  using namespace fp8pair;
+  CUtensorMap tm_a, tm_b;
+  if (!make_tmap_2d(&tm_a, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)M, (uint64_t)K, BK, 128, CU_TENSOR_MAP_SWIZZLE_128B)
+      || !make_tmap_2d(&tm_b, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, 128, CU_TENSOR_MAP_SWIZZLE_128B)) {
+    return LLMMM_ERR_CUDA;
+  }
+  static thread_local bool attr_set[64] = {};
+  if (!attr_set[info->device]) {
+    LLMMM_CUDA_TRY(cudaFuncSetAttribute(
+      fp8_blockwise_gemm_pair_kernel<EPI_GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+    attr_set[info->device] = true;
+  }
+  const int       tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const SplitPlan plan  = plan_split(info, tiles, K / BK, /*fixed*/ 4, /*per_way_x2*/ 5, /*min_gain*/ 3);
+  float*          none  = nullptr;
+  LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<EPI_GATHER>, dim3(2 * plan.pairs), dim3(THREADS), SMEM_BYTES, stream, 2,
+                            tm_a, tm_b, A_s, B_s, static_cast<void*>(nullptr), none, M, N, K, plan.dp_tiles, plan.split_pairs,
+                            plan.split_s, plan.split_chunk, plan.partials, plan.counters, dst, info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
 }
@@ -1000,6 +1074,7 @@ int warm_fp8_kernels(const DeviceInfo* info)
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_E4M3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8cfg::SMEM_BYTES));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8cfg::SMEM_BYTES));
   return warm_decode_kernels(info);
@@ -1083,6 +1158,53 @@ int llmmm_fp8_blockwise_mm_e4m3out(const void*    A,
     return rc;
   }
   return llmmm::launch_fp8<false>(A, A_scale_t, B_t, B_scale_t, C, C_scale_t, M, N, K, s);
+}
+
+int llmmm_fp8_blockwise_mm_e4m3out_gather(const void*    A,
+                                          const float*   A_scale_t,
+                                          const void*    B_t,
+                                          const float*   B_scale_t,
+                                          void* const*   C_dsts,
+                                          float* const*  C_scale_dsts,
+                                          int            n_dsts,
+                                          int            N_total,
+                                          int            col_offset,
+                                          int            M,
+                                          int            N,
+                                          int            K,
+                                          llmmm_stream_t stream)
+{
+  using namespace llmmm;
+  int rc = check_fp8_args(A, A_scale_t, B_t, B_scale_t, A, M, N, K);
+  if (rc != LLMMM_OK) {
+    return rc;
+  }
+  if (C_dsts == nullptr || C_scale_dsts == nullptr || n_dsts < 1 || n_dsts > 8) {
+    return set_error(LLMMM_ERR_SHAPE, "between 1 and 8 destinations are needed (got %d)", n_dsts);
+  }
+  if ((N_total % 128) != 0 || (col_offset % 128) != 0 || col_offset < 0 || col_offset + N > N_total) {
+    return set_error(LLMMM_ERR_SHAPE, "the shard [%d, %d) must lie on 128-column boundaries inside the %d columns of C",
+                     col_offset, col_offset + N, N_total);
+  }
+  GatherDst dst{};
+  for (int d = 0; d < n_dsts; ++d) {
+    if (C_dsts[d] == nullptr || C_scale_dsts[d] == nullptr || ((uintptr_t)C_dsts[d] & 15)) {
+      return set_error(LLMMM_ERR_SHAPE, "destination %d: null or not 16-byte aligned", d);
+    }
+    dst.c[d]  = static_cast<uint8_t*>(C_dsts[d]);
+    dst.cs[d] = C_scale_dsts[d];
+  }
+  dst.n    = n_dsts;
+  dst.ld   = N_total;
+  dst.col0 = col_offset;
+  const DeviceInfo* info = device_info();
+  if (info == nullptr) {
+    return LLMMM_ERR_UNSUPPORTED;
+  }
+  if (info->max_pairs < 1) {
+    return set_error(LLMMM_ERR_UNSUPPORTED, "this device cannot hold a cluster of two CTAs of the GEMM kernel");
+  }
+  return launch_fp8_gather(A, A_scale_t, B_t, B_scale_t, dst, M, N, K, info, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int llmmm_fp8_blockwise_mm_swiglu_e4m3out(const void*    A,

@@ -66,3 +66,28 @@ def test_m_split_is_bitwise_the_unsharded_result(capi, cuda, world):
         assert torch.equal(cq, full_q[m0:m1])
         assert torch.equal(cs, full_s[:, m0:m1])
     capi.check_status()
+
+
+@pytest.mark.parametrize("shape,world", [((384, 1536, 1024), 3), ((4096, 4096, 4096), 2)])
+def test_gather_epilogue_fills_every_destination(capi, cuda, shape, world):
+    """The fused all-gather, on one GPU: every shard's GEMM stores its columns into all `world` destinations (here
+    `world` local buffers standing in for the peers' mapped ones); afterwards each destination is the unsharded
+    result, bit for bit (no scratch registered, so no tile is cut along K)."""
+    M, N, K = shape
+    A_q, A_s, B_q, B_s = full_size_case(capi, cuda, M, N, K, 97, 0.02)
+    capi.clear_workspace()
+    full_q, full_s = run(capi, cuda, A_q, A_s, B_q, B_s)
+    dst_q = [torch.full((M, N), 0xAA, dtype=torch.uint8, device=cuda) for _ in range(world)]
+    dst_s = [torch.full((N // 128, M), float("nan"), device=cuda) for _ in range(world)]
+    for rank in range(world):
+        n0, n1 = shard.split_n(N, world, rank)
+        bq, bs = shard.shard_weights_n(B_q, B_s, world, rank)
+        capi.fp8_blockwise_mm_gather(A_q, A_s, bq.contiguous(), bs.contiguous(), dst_q, dst_s, N, n0, M, n1 - n0, K)
+    torch.cuda.synchronize()
+    capi.check_status()
+    for q, s in zip(dst_q, dst_s):
+        assert torch.equal(q, full_q) and torch.equal(s, full_s)
+    with pytest.raises(RuntimeError, match="128-column boundaries"):
+        capi.fp8_blockwise_mm_gather(A_q, A_s, B_q, B_s, dst_q, dst_s, N, 64, M, N, K)
+    with pytest.raises(RuntimeError, match="destinations"):
+        capi.fp8_blockwise_mm_gather(A_q, A_s, B_q, B_s, [], [], N, 0, M, N, K)
