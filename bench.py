@@ -514,7 +514,7 @@ def nsplit_config(torch, dist, capi, dev, rank, world):
     ms_both = timed(lambda: (gemm(), shard.all_gather_c_n(C_q, C_s, Nn)), 5)
     flops = 2.0 * Mm * Nn * Kk
     # the same gather done by the GEMM itself: every rank's epilogue stores its column shard into the full C of
-    # every rank (peer buffers mapped with CUDA IPC), checked against the NCCL-gathered result
+    # every rank (peer buffers from torch symmetric memory), checked against the NCCL-gathered result
     try:
         po = shard.PeerOutputs(Mm, Nn, dev)
         dq, ds = po.dsts()

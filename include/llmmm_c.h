@@ -86,7 +86,7 @@ int llmmm_fp8_blockwise_mm_e4m3out(const void*    A,
  * shard [col_offset, col_offset + N) of a product that is N_total columns wide (B_t / B_scale_t are this
  * rank's slabs: [N, K] and [(N/128), (K/128)]) and stores the shard into the FULL outputs
  * C [M, N_total] e4m3 and C_scale_t [(N_total/128), M] of n_dsts (1..8) destinations: this GPU's own buffers
- * and the other GPUs' buffers mapped into this process (CUDA IPC / peer access).  The peer stores are plain
+ * and the other GPUs' buffers mapped into this GPU's address space (virtual-memory API or peer access).  The peer stores are plain
  * stores issued by the epilogue while other tiles are still being computed; when the kernel has completed on
  * every rank (stream order + a barrier between the ranks) every destination holds the whole C.  The reference
  * has no multi-GPU code.  Shapes as for llmmm_fp8_blockwise_mm_e4m3out; N_total, col_offset multiples of 128. */

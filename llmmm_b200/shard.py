@@ -96,64 +96,40 @@ def all_gather_c_m(C_q: torch.Tensor, C_s: torch.Tensor, M: int, group=None):
 
 class PeerOutputs:
     """Full-size outputs C_q [M, N] / C_s [N/128, M] on every rank of an N-split, each rank's pair mapped into
-    every other rank's process (CUDA IPC through torch's storage sharing, peer access enabled), for
-    `capi.fp8_blockwise_mm_gather`: a rank's GEMM stores its column shard into all of them, so the all-gather
-    is done by the epilogue's peer stores.  One process per GPU, all GPUs of one box visible to every process.
+    every other rank's address space, for `capi.fp8_blockwise_mm_gather`: a rank's GEMM stores its column shard
+    into all of them, so the all-gather is done by the epilogue's peer stores.  The buffers come from torch's
+    symmetric memory (`torch.distributed._symmetric_memory`: device memory created with the virtual-memory API,
+    exported to the other processes of the group and mapped with access for this GPU); one process per GPU.
 
-    `dsts()` gives the destination lists (own buffers first); after the GEMM, `wait_all()` (stream
+    `dsts()` gives the destination address lists in rank order; after the GEMM, `wait_all()` (stream
     synchronisation + a barrier of the group) is the point from which every rank may read its whole C."""
 
     def __init__(self, M: int, N: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
         if N % 128:
             raise ValueError("N must be a multiple of 128")
-        self.group = group
-        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.group = dist.group.WORLD if group is None else group
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
         self.device = torch.device(device)
-        self.C_q = torch.empty(M, N, dtype=torch.uint8, device=self.device)
-        self.C_s = torch.empty(N // 128, M, dtype=torch.float32, device=self.device)
-        mine = (self.device.index, self.C_q.untyped_storage()._share_cuda_(), self.C_s.untyped_storage()._share_cuda_())
-        everyone = [None] * self.world
-        dist.all_gather_object(everyone, mine, group=group)
-        self.peer_q, self.peer_s, self._keep = [], [], []
-        for r, (dev_index, hq, hs) in enumerate(everyone):
-            if r == self.rank:
-                continue
-            _enable_peer_access(self.device.index, dev_index)
-            sq = torch.UntypedStorage._new_shared_cuda(*hq)
-            ss = torch.UntypedStorage._new_shared_cuda(*hs)
-            self._keep += [sq, ss]
-            self.peer_q.append(torch.empty(0, dtype=torch.uint8, device=f"cuda:{dev_index}").set_(sq, 0, (M, N)))
-            self.peer_s.append(torch.empty(0, dtype=torch.float32, device=f"cuda:{dev_index}").set_(ss, 0, (N // 128, M)))
-        dist.barrier(group=group)
+        with torch.cuda.device(self.device):
+            self._q = symm_mem.empty(M * N, dtype=torch.uint8, device=self.device)
+            self._s = symm_mem.empty((N // 128) * M, dtype=torch.float32, device=self.device)
+            self._hq = symm_mem.rendezvous(self._q, self.group)
+            self._hs = symm_mem.rendezvous(self._s, self.group)
+        self.C_q = self._q.view(M, N)
+        self.C_s = self._s.view(N // 128, M)
+        if len(self._hq.buffer_ptrs) != self.world or self._hq.buffer_ptrs[self.rank] != self._q.data_ptr():
+            raise RuntimeError("symmetric memory rendezvous returned an unexpected set of buffers")
+        dist.barrier(group=self.group)
 
     def dsts(self):
-        """(C_q destinations, C_s destinations) as raw device addresses, own buffers first."""
-        return ([self.C_q.data_ptr()] + [t.data_ptr() for t in self.peer_q],
-                [self.C_s.data_ptr()] + [t.data_ptr() for t in self.peer_s])
+        """(C_q destinations, C_s destinations) as raw device addresses valid on this GPU, in rank order."""
+        return list(self._hq.buffer_ptrs), list(self._hs.buffer_ptrs)
 
     def wait_all(self) -> None:
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
 
     def close(self) -> None:
-        """Unmaps the peers' buffers (every rank must call it, before the owners free theirs)."""
+        """Every rank calls it before the buffers go away: no rank may still be storing into a peer."""
         self.wait_all()
-        self.peer_q, self.peer_s, self._keep = [], [], []
-        torch.cuda.ipc_collect()
-        dist.barrier(group=self.group)
-
-
-def _enable_peer_access(device_index: int, peer_index: int) -> None:
-    """cudaDeviceEnablePeerAccess(peer) with `device_index` current (kernels, unlike copies, need it explicitly)."""
-    import ctypes
-    if device_index == peer_index:
-        return
-    if not torch.cuda.can_device_access_peer(device_index, peer_index):
-        raise RuntimeError(f"GPU {device_index} cannot access GPU {peer_index} directly")
-    rt = ctypes.CDLL("libcudart.so.12")
-    with torch.cuda.device(device_index):
-        torch.cuda.current_stream().synchronize()  # the context exists
-        rc = rt.cudaDeviceEnablePeerAccess(ctypes.c_int(peer_index), ctypes.c_uint(0))
-        if rc not in (0, 704):  # 704: peer access already enabled
-            raise RuntimeError(f"cudaDeviceEnablePeerAccess({peer_index}) failed with CUDA error {rc}")
-        rt.cudaGetLastError()
