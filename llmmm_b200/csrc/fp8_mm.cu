@@ -432,6 +432,9 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
   constexpr bool OUT_F32 = (EPI == EPI_F32);
   constexpr bool SWIGLU  = (EPI == EPI_SWIGLU);
   constexpr int  TILE_N  = SWIGLU ? 128 : BN;  // output columns per tile
+  // EPI_GATHER runs the ring one stage shorter: the sixth stage's two 16 KB slots stage the output tile so that
+  // the stores to the other GPUs leave as whole 128-byte rows
+  constexpr uint32_t NSTAGES = (EPI == EPI_GATHER) ? STAGES - 1 : STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Fp8PairBars*       bars       = reinterpret_cast<Fp8PairBars*>(smem + OFF_BAR);
@@ -485,8 +488,8 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
           const int m0 = (tile % m_tiles) * BM + (int)rank * 128;
           const int n0 = (tile / m_tiles) * TILE_N + (int)rank * (SWIGLU ? 64 : 128);
           for (int kb = kb0; kb < kb1; ++kb, ++it) {
-            const uint32_t s  = it % STAGES;
-            const uint32_t ph = (it / STAGES) & 1;
+            const uint32_t s  = it % NSTAGES;
+            const uint32_t ph = (it / NSTAGES) & 1;
             mbar_wait(&bars->empty[s], ph ^ 1, DEV_WAIT_SMEM_EMPTY, abort_flag, status);
             const uint32_t full_leader = mapa_shared(smem_u32(&bars->full[s]), 0);
             if (rank == 0) {
@@ -523,8 +526,8 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
         const uint32_t total = PairWalk(pair, n_pairs, k_blocks, dp_tiles, split_pairs, split_s, split_chunk).total_k_blocks();
         for (uint32_t it = p; it < total; it += 2) {
           {
-            const uint32_t s  = it % STAGES;
-            const uint32_t ph = (it / STAGES) & 1;
+            const uint32_t s  = it % NSTAGES;
+            const uint32_t ph = (it / NSTAGES) & 1;
             const uint32_t pp = (it >> 1) & 1;
             PROF8_T(c0);
             mbar_wait(&bars->part_empty[p], pp ^ 1, DEV_WAIT_TMEM_EMPTY, abort_flag, status);
@@ -808,17 +811,18 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
           }
         }
       }
-      else if (m_ok && g_ok) {
-        if constexpr (EPI == EPI_GATHER) {
+      else if constexpr (EPI == EPI_GATHER) {
+        // The whole warp takes part, also lanes of rows beyond M: the tile is transposed through shared memory.
+        uint8_t* stg = smem + (half == 0 ? OFF_A : OFF_B) + (STAGES - 1) * A_BYTES + quarter * 4096;
+        {
           float amax = 0.0f;
 #pragma unroll
           for (int i = 0; i < 128; ++i) {
             amax = fmaxf(amax, fabsf(acc[i]));
           }
-          const float  scale     = __fdiv_rn(amax, 448.0f);
-          const float  scale_inv = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 0.0f;
-          const size_t q_off     = (size_t)m * gather.ld + (size_t)gather.col0 + (size_t)ng * 128;
-          const size_t s_off     = (size_t)(gather.col0 / 128 + ng) * M + m;
+          const float scale     = __fdiv_rn(amax, 448.0f);
+          const float scale_inv = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 0.0f;
+          // this thread's 128 bytes go to its row of the warp's staging tile (16-byte chunks XOR-swizzled by row)
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             uint4 o;
@@ -826,15 +830,36 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
             o.y = pack_e4m3x4(acc[16 * i + 4] * scale_inv, acc[16 * i + 5] * scale_inv, acc[16 * i + 6] * scale_inv, acc[16 * i + 7] * scale_inv);
             o.z = pack_e4m3x4(acc[16 * i + 8] * scale_inv, acc[16 * i + 9] * scale_inv, acc[16 * i + 10] * scale_inv, acc[16 * i + 11] * scale_inv);
             o.w = pack_e4m3x4(acc[16 * i + 12] * scale_inv, acc[16 * i + 13] * scale_inv, acc[16 * i + 14] * scale_inv, acc[16 * i + 15] * scale_inv);
+            *reinterpret_cast<uint4*>(stg + lane * 128 + ((i ^ (lane & 7)) << 4)) = o;
+          }
+          if (m_ok && g_ok) {
+            const size_t s_off = (size_t)(gather.col0 / 128 + ng) * M + m;
             for (int d = 0; d < gather.n; ++d) {
-              reinterpret_cast<uint4*>(gather.c[d] + q_off)[i] = o;
+              gather.cs[d][s_off] = scale;  // 32 consecutive floats per warp
             }
           }
-          for (int d = 0; d < gather.n; ++d) {
-            gather.cs[d][s_off] = scale;
+        }
+        __syncwarp();
+        // one store instruction now covers four whole rows: lane l writes chunk l & 7 of row 4 i + (l >> 3), so
+        // that what crosses to the other GPUs are contiguous 128-byte rows, not 16-byte pieces
+        if (g_ok) {
+          const int    m_warp = m - lane;
+          const size_t col    = (size_t)gather.col0 + (size_t)ng * 128 + (size_t)((lane & 7) << 4);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int   rr = 4 * i + (lane >> 3);
+            const uint4 o  = *reinterpret_cast<const uint4*>(stg + rr * 128 + (((lane & 7) ^ (rr & 7)) << 4));
+            if (m_warp + rr < M) {
+              for (int d = 0; d < gather.n; ++d) {
+                *reinterpret_cast<uint4*>(gather.c[d] + (size_t)(m_warp + rr) * gather.ld + col) = o;
+              }
+            }
           }
         }
-        else if constexpr (OUT_F32) {
+        __syncwarp();
+      }
+      else if (m_ok && g_ok) {
+        if constexpr (OUT_F32) {
           float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(C_out) + (size_t)m * N + (size_t)ng * 128);
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
