@@ -439,9 +439,11 @@ def extra_configs(torch, capi, dev, peaks):
     s2 = torch.empty(32, 32, device=dev)
     xt = torch.empty(3, 4096, 4096, device=dev)
     qt = torch.empty(3, 4096, 4096, dtype=torch.uint8, device=dev)
+    wn = torch.rand(4096, device=dev, generator=gen) + 0.5
     cases = {
         "quant_1x128": ([lambda i=i: capi.fp8_quant_1x128(x[i], q[i], s1, 4096, 4096) for i in range(3)], 5 * 4096 * 4096 + 4 * 32 * 4096),
         "quant_128x128": ([lambda i=i: capi.fp8_quant_128x128(x[i], q[i], s2, 4096, 4096) for i in range(3)], 5 * 4096 * 4096 + 4 * 32 * 32),
+        "rmsnorm_quant_1x128": ([lambda i=i: capi.fp8_rmsnorm_quant_1x128(x[i], wn, 1e-6, q[i], s1, 4096, 4096) for i in range(3)], 5 * 4096 * 4096 + 4 * 32 * 4096 + 4 * 4096),
         "transpose_f32": ([lambda i=i: capi.transpose_aligned_128(xt[i], x[i], 4096, 4096) for i in range(3)], 8 * 4096 * 4096),
         "transpose_e4m3": ([lambda i=i: capi.transpose_aligned_128(qt[i], q[i], 4096, 4096) for i in range(3)], 2 * 4096 * 4096),
     }

@@ -143,6 +143,13 @@ int llmmm_fp8_blockwise_mm_f32out(const void*    A,
  * (examples/005.fp8.mm.cu:439-500, launcher :547-563).  Requires K%128 == 0. */
 int llmmm_fp8_quant_1x128(const float* x, void* q, float* scale, int M, int K, llmmm_stream_t stream);
 
+/* RMSNorm fused in front of the activation quantiser (the reference's README.md:16 plans RMSNorm hooks; it
+ * has no implementation): y[m,k] = x[m,k] * rsqrt(mean_k(x[m,:]^2) + eps) * weight[k] in fp32, then y is
+ * quantised exactly as llmmm_fp8_quant_1x128 quantises x: q [M,K] e4m3, scale [(K/128), M].  One pass over x
+ * from HBM instead of three (normalise, write, re-read to quantise).  Requires K%128 == 0, eps >= 0. */
+int llmmm_fp8_rmsnorm_quant_1x128(const float* x, const float* weight, float eps, void* q, float* scale, int M, int K,
+                                  llmmm_stream_t stream);
+
 /* Weight quantiser: x [rows,cols] fp32 -> q [rows,cols] e4m3,
  * scale [(rows/128),(cols/128)] fp32, one scale per 128x128 block.
  * Replaces fp8_blockwise_symmetric_quantization<128,128,false>

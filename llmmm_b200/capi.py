@@ -49,6 +49,7 @@ def lib() -> ctypes.CDLL:
         L.llmmm_fp8_blockwise_mm_f32out.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
         L.llmmm_fp8_quant_1x128.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
         L.llmmm_fp8_quant_128x128.argtypes = [_vp, _vp, _vp, _i, _i, _vp]
+        L.llmmm_fp8_rmsnorm_quant_1x128.argtypes = [_vp, _vp, ctypes.c_float, _vp, _vp, _i, _i, _vp]
         L.llmmm_transpose_aligned_128.argtypes = [_vp, _vp, _i, _i, _i, _vp]
         L.llmmm_selftest_wait_expiry.argtypes = [ctypes.c_uint, _vp]
         _lib = L
@@ -61,7 +62,7 @@ EXPORTED_SYMBOLS = (
     "llmmm_fp8_quant_128x128", "llmmm_fp8_workspace_bytes", "llmmm_set_workspace", "llmmm_check_status",
     "llmmm_launch_count", "llmmm_split_launch_count", "llmmm_set_static_weights", "llmmm_describe_plan", "llmmm_tune",
     "llmmm_fp8_blockwise_mm_e4m3out_noalloc", "llmmm_fp8_blockwise_mm_swiglu_e4m3out",
-    "llmmm_fp8_blockwise_mm_e4m3out_gather",
+    "llmmm_fp8_blockwise_mm_e4m3out_gather", "llmmm_fp8_rmsnorm_quant_1x128",
     "llmmm_transpose_aligned_128", "llmmm_selftest_wait_expiry",
 )
 
@@ -171,6 +172,13 @@ def fp8_quant_1x128(x, q, scale, M: int, K: int, stream=None) -> None:
     with torch.cuda.device(x.device):
         _check(lib().llmmm_fp8_quant_1x128(_dev(x, torch.float32), _dev(q), _dev(scale, torch.float32), M, K,
                                            _stream(stream)))
+
+
+def fp8_rmsnorm_quant_1x128(x, weight, eps: float, q, scale, M: int, K: int, stream=None) -> None:
+    """y = x * rsqrt(mean(x^2) + eps) * weight per row, then the 1x128 quantisation of y (one kernel)."""
+    with torch.cuda.device(x.device):
+        _check(lib().llmmm_fp8_rmsnorm_quant_1x128(_dev(x, torch.float32), _dev(weight, torch.float32), ctypes.c_float(eps),
+                                                   _dev(q), _dev(scale, torch.float32), M, K, _stream(stream)))
 
 
 def fp8_quant_128x128(x, q, scale, rows: int, cols: int, stream=None) -> None:

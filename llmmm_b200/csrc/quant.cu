@@ -160,9 +160,90 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// RMSNorm fused in front of the activation quantiser: y = x * rsqrt(mean(x^2) + eps) * weight, then the 1x128
+// quantisation of y.  One CTA per row: the first pass over the row sums the squares (the row comes from HBM),
+// the second pass re-reads it from L2, scales and quantises one 128-wide group per warp at a time.
+constexpr int RN_THREADS = 256;
+
+__global__ void __launch_bounds__(RN_THREADS)
+  rmsnorm_quant_1x128_kernel(const float* __restrict__ x, const float* __restrict__ weight, float eps, uint8_t* __restrict__ q,
+                             float* __restrict__ scale, int M, int K)
+{
+  __shared__ float warp_sum[RN_THREADS / 32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int     lane = threadIdx.x & 31;
+  const int     warp = threadIdx.x >> 5;
+  const int     m    = blockIdx.x;
+  const float4* row  = reinterpret_cast<const float4*>(x + (size_t)m * K);
+  float         ss   = 0.0f;
+  for (int i = threadIdx.x; i < K / 4; i += RN_THREADS) {
+    const float4 v = __ldg(row + i);
+    ss             = fmaf(v.x, v.x, ss);
+    ss             = fmaf(v.y, v.y, ss);
+    ss             = fmaf(v.z, v.z, ss);
+    ss             = fmaf(v.w, v.w, ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  }
+  if (lane == 0) {
+    warp_sum[warp] = ss;
+  }
+  __syncthreads();
+  float total = 0.0f;
+#pragma unroll
+  for (int i = 0; i < RN_THREADS / 32; ++i) {
+    total += warp_sum[i];  // the same order in every thread
+  }
+  const float inv = __frsqrt_rn(__fdiv_rn(total, (float)K) + eps);
+  const float4* wrow = reinterpret_cast<const float4*>(weight);
+  for (int g = warp; g < K / 128; g += RN_THREADS / 32) {
+    const float4 v = __ldg(row + g * 32 + lane);
+    const float4 w = __ldg(wrow + g * 32 + lane);
+    float4       y;
+    y.x = __fmul_rn(__fmul_rn(v.x, inv), w.x);
+    y.y = __fmul_rn(__fmul_rn(v.y, inv), w.y);
+    y.z = __fmul_rn(__fmul_rn(v.z, inv), w.z);
+    y.w = __fmul_rn(__fmul_rn(v.w, inv), w.w);
+    const float amax = warp_max(amax4(y));
+    const float s    = __fdiv_rn(amax, 448.0f);
+    reinterpret_cast<uint32_t*>(q + (size_t)m * K + (size_t)g * 128)[lane] = quant4(y, s);
+    if (lane == 0) {
+      scale[(size_t)g * M + m] = s;
+    }
+  }
+}
+
 }  // namespace llmmm
 
 extern "C" {
+
+int llmmm_fp8_rmsnorm_quant_1x128(const float* x, const float* weight, float eps, void* q, float* scale, int M, int K,
+                                  llmmm_stream_t stream)
+{
+  using namespace llmmm;
+  if (x == nullptr || weight == nullptr || q == nullptr || scale == nullptr) {
+    return set_error(LLMMM_ERR_SHAPE, "null pointer argument");
+  }
+  if (M < 1 || K < 128 || (K % 128) != 0) {
+    return set_error(LLMMM_ERR_SHAPE, "M or K are not aligned. (need M>=1, K%%128==0; got %d %d)", M, K);
+  }
+  if (((uintptr_t)x | (uintptr_t)q | (uintptr_t)weight) & 15) {
+    return set_error(LLMMM_ERR_SHAPE, "x, weight and q must be 16-byte aligned");
+  }
+  if (!(eps >= 0.0f)) {
+    return set_error(LLMMM_ERR_SHAPE, "eps must be non-negative");
+  }
+  if (device_info() == nullptr) {
+    return LLMMM_ERR_UNSUPPORTED;
+  }
+  LLMMM_CUDA_TRY(launch_pdl(rmsnorm_quant_1x128_kernel, dim3((unsigned)M), dim3(RN_THREADS), 0,
+                            reinterpret_cast<cudaStream_t>(stream), 1, x, weight, eps, static_cast<uint8_t*>(q), scale, M, K));
+  g_launches.fetch_add(1);
+  return LLMMM_OK;
+}
 
 int llmmm_fp8_quant_1x128(const float* x, void* q, float* scale, int M, int K, llmmm_stream_t stream)
 {

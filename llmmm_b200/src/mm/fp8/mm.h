@@ -78,6 +78,14 @@ inline void fp8_gemm_blockwise_quant_A_1x128__B_128x128__output_fp32(const __nv_
     llmmm_fp8_blockwise_mm_f32out(A, A_scale_transposed, B_transposed, B_scale_transposed, C, M, N, K, stream));
 }
 
+// RMSNorm fused in front of the activation quantiser (README.md:16 plans the hook): q / scale as produced by
+// fp8_blockwise_symmetric_quantization<1,128,true> for y = x * rsqrt(mean(x^2) + eps) * weight.
+inline void fp8_rmsnorm_blockwise_symmetric_quantization_1x128(
+  const float* x, const float* weight, float eps, __nv_fp8_e4m3* q, float* scale, int M, int K, cudaStream_t stream)
+{
+  LLMMM::throw_on_error(llmmm_fp8_rmsnorm_quant_1x128(x, weight, eps, q, scale, M, K, stream));
+}
+
 // Only the two instantiations the reference uses exist: <1,128,true>
 // (activations, :2686) and <128,128,false> (weights, :2739).
 template<int QUANT_M, int QUANT_N, bool SCALE_TRANPOSE>

@@ -232,6 +232,26 @@ def fp8_blockwise_mm(A_q, A_s, B_q, B_s):
     return q, s, acc
 
 
+def rmsnorm(x: np.ndarray, weight: np.ndarray, eps: float, exact: bool = False) -> np.ndarray:
+    """y = x * rsqrt(mean(x^2) + eps) * weight per row.  exact=False: fp32 with the kernel's operation order up to
+    the order of the sum of squares (x * inv first, then * weight); exact=True: fp64 ground truth.  The reference
+    only plans this hook (README.md:16); the definition is the usual RMSNorm."""
+    if exact:
+        x64, w64 = x.astype(np.float64), weight.astype(np.float64)
+        return x64 / np.sqrt((x64 * x64).mean(axis=1, keepdims=True) + eps) * w64
+    x = _c(x, np.float32)
+    ms = ((x.astype(np.float64) ** 2).sum(axis=1, keepdims=True)).astype(np.float32) / np.float32(x.shape[1])
+    inv = (np.float32(1) / np.sqrt(ms + np.float32(eps), dtype=np.float32)).astype(np.float32)
+    return ((x * inv).astype(np.float32) * _c(weight, np.float32)).astype(np.float32)
+
+
+def rmsnorm_quant_1x128(x: np.ndarray, weight: np.ndarray, eps: float):
+    """RMSNorm followed by the activation quantiser: (q, scale, y_f32, y_f64_truth)."""
+    y32 = rmsnorm(x, weight, eps)
+    q, s = quant_1x128(y32)
+    return q, s, y32, rmsnorm(x, weight, eps, exact=True)
+
+
 def swiglu(acc: np.ndarray) -> np.ndarray:
     """h[m, i] = silu(acc[m, i]) * acc[m, I + i] for a gate_up accumulator [M, 2I] (gate columns first),
     silu(x) = x / (1 + exp(-x)); computed in the dtype of `acc` (fp32: the kernel's arithmetic up to the
