@@ -312,7 +312,7 @@ def main() -> int:
         "traffic": 36.7e6,
         "peak_source": f"2 x bf16_tflops ({peak_kind}; the file has no fp8 figure; burst, kernel timed alone)",
         "frac_of_nominal_4500": achieved / 4500.0,
-        "kernel": "fp8_blockwise_gemm_pair_kernel<false>",
+        "kernel": "fp8_blockwise_gemm_pair_kernel<EPI_E4M3>",
     }
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
