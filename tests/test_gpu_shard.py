@@ -91,3 +91,23 @@ def test_gather_epilogue_fills_every_destination(capi, cuda, shape, world):
         capi.fp8_blockwise_mm_gather(A_q, A_s, B_q, B_s, dst_q, dst_s, N, 64, M, N, K)
     with pytest.raises(RuntimeError, match="destinations"):
         capi.fp8_blockwise_mm_gather(A_q, A_s, B_q, B_s, [], [], N, 0, M, N, K)
+
+
+def test_gather_epilogue_with_split_tiles(capi, cuda):
+    """With scratch registered a shard's last wave is cut along K; the gather epilogue must then store exactly what
+    the plain entry point stores for the same shard (same plan, same order of sums), at the shard's columns."""
+    M, N, K, world = 512, 2048, 4096, 2
+    A_q, A_s, B_q, B_s = full_size_case(capi, cuda, M, N, K, 98, 0.02)
+    dst_q = torch.full((M, N), 0xAA, dtype=torch.uint8, device=cuda)
+    dst_s = torch.full((N // 128, M), float("nan"), device=cuda)
+    n_split = capi.split_launch_count()
+    for rank in range(world):
+        n0, n1 = shard.split_n(N, world, rank)
+        bq, bs = shard.shard_weights_n(B_q, B_s, world, rank)
+        bq, bs = bq.contiguous(), bs.contiguous()
+        ref_q, ref_s = run(capi, cuda, A_q, A_s, bq, bs, scratch=True)
+        capi.fp8_blockwise_mm_gather(A_q, A_s, bq, bs, [dst_q], [dst_s], N, n0, M, n1 - n0, K)
+        torch.cuda.synchronize()
+        assert torch.equal(dst_q[:, n0:n1], ref_q) and torch.equal(dst_s[n0 // 128:n1 // 128], ref_s)
+    assert capi.split_launch_count() == n_split + 2 * world  # every one of these launches was split
+    capi.check_status()
