@@ -476,6 +476,20 @@ def extra_configs(torch, capi, dev, peaks):
         "us_fused": ms_f * 1e3, "tflops_fused": flop / (ms_f * 1e-3) / 1e12,
         "us_plain_gemm_same_weight": ms_p * 1e3, "tflops_plain": flop / (ms_p * 1e-3) / 1e12,
         "frac_of_2x_measured_bf16_burst": flop / (ms_f * 1e-3) / 1e12 / (2.0 * float(peaks["bf16_tflops"]))}
+    # the same MLP front half at decode size (M = 1, 16): decode GEMM into scratch + SwiGLU/quantise kernel
+    capi.set_static_weights(True)
+    dec_sw = []
+    for m_ in (1, 16):
+        xq = torch.randint(0, 120, (m_, k), dtype=torch.uint8, device=dev)
+        xs = torch.rand(k // 128, m_, device=dev)
+        hq_ = torch.empty(m_, i_, dtype=torch.uint8, device=dev)
+        hs_ = torch.empty(i_ // 128, m_, device=dev)
+        capi.ensure_swiglu_workspace(m_, i_, k)
+        ms_d = time_graph(torch, [(lambda w=w: capi.fp8_blockwise_mm_swiglu(xq, xs, w[0], w[1], hq_, hs_, m_, i_, k)) for w in wsets] * 4)
+        by = 2 * i_ * k + 4 * (2 * i_ // 128) * (k // 128) + m_ * k + 4 * m_ * k // 128 + m_ * i_ + 4 * m_ * i_ // 128
+        dec_sw.append({"M": m_, "us": ms_d * 1e3, "gbs": by / (ms_d * 1e-3) / 1e9, "frac_of_measured_hbm": by / (ms_d * 1e-3) / 1e9 / hbm})
+    capi.set_static_weights(False)
+    out["swiglu_gate_up_decode_19456x2560"] = dec_sw
     capi.check_status()
     return out
 

@@ -112,7 +112,10 @@ int llmmm_fp8_blockwise_mm_e4m3out_gather(const void*    A,
  *   h[m, i] = silu(acc[m, i]) * acc[m, I + i],  silu(x) = x / (1 + exp(-x))   (fp32)
  *   H [M, I] e4m3 and H_scale_t [(I/128), M]: h quantised in 1x128 groups along I by the same rule as C above,
  *   which is the A / A_scale_t format of the down projection that consumes it.
- * Requires I%128 == 0, K%128 == 0, any M >= 1 (meant for prefill-sized M: 256-row tiles). */
+ * Requires I%128 == 0, K%128 == 0, any M >= 1.  M > 64 runs one fused kernel (256-row tiles).  M <= 64 runs the
+ * weight-streaming decode kernel into scratch followed by a small SwiGLU + quantisation kernel, provided the
+ * registered scratch (llmmm_set_workspace) has llmmm_fp8_swiglu_workspace_bytes(M, I, K) bytes; otherwise the
+ * 256-row kernel runs for small M too (same results up to the order of fp32 sums, several times slower). */
 int llmmm_fp8_blockwise_mm_swiglu_e4m3out(const void*    A,
                                           const float*   A_scale_t,
                                           const void*    B_gate_up_t,
@@ -123,6 +126,8 @@ int llmmm_fp8_blockwise_mm_swiglu_e4m3out(const void*    A,
                                           int            I,
                                           int            K,
                                           llmmm_stream_t stream);
+
+size_t llmmm_fp8_swiglu_workspace_bytes(int M, int I, int K);
 
 /* Same product with the fp32 accumulator written out unquantised, C [M,N] fp32.
  * Replaces fp8_gemm_blockwise_quant_A_1x128__B_128x128__output_fp32

@@ -36,6 +36,8 @@ def lib() -> ctypes.CDLL:
         L.llmmm_launch_count.restype = ctypes.c_uint64
         L.llmmm_split_launch_count.restype = ctypes.c_uint64
         L.llmmm_fp8_workspace_bytes.restype = ctypes.c_size_t
+        L.llmmm_fp8_swiglu_workspace_bytes.restype = ctypes.c_size_t
+        L.llmmm_fp8_swiglu_workspace_bytes.argtypes = [_i, _i, _i]
         L.llmmm_fp8_workspace_bytes.argtypes = [_i, _i, _i]
         L.llmmm_set_workspace.argtypes = [_vp, ctypes.c_size_t]
         L.llmmm_check_status.argtypes = [_vp]
@@ -62,7 +64,7 @@ EXPORTED_SYMBOLS = (
     "llmmm_fp8_quant_128x128", "llmmm_fp8_workspace_bytes", "llmmm_set_workspace", "llmmm_check_status",
     "llmmm_launch_count", "llmmm_split_launch_count", "llmmm_set_static_weights", "llmmm_describe_plan", "llmmm_tune",
     "llmmm_fp8_blockwise_mm_e4m3out_noalloc", "llmmm_fp8_blockwise_mm_swiglu_e4m3out",
-    "llmmm_fp8_blockwise_mm_e4m3out_gather", "llmmm_fp8_rmsnorm_quant_1x128",
+    "llmmm_fp8_blockwise_mm_e4m3out_gather", "llmmm_fp8_rmsnorm_quant_1x128", "llmmm_fp8_swiglu_workspace_bytes",
     "llmmm_transpose_aligned_128", "llmmm_selftest_wait_expiry",
 )
 
@@ -232,10 +234,19 @@ def clear_workspace() -> None:
     _workspaces.pop(torch.cuda.current_device(), None)
 
 
+def ensure_swiglu_workspace(M: int, I: int, K: int, device=None) -> None:
+    """Scratch for the decode-sized (M <= 64) form of fp8_blockwise_mm_swiglu."""
+    ensure_workspace_bytes(int(lib().llmmm_fp8_swiglu_workspace_bytes(M, I, K)), device)
+
+
 def ensure_workspace(M: int, N: int, K: int, device=None) -> None:
     """Registers a split-K scratch buffer large enough for (M,N,K) on `device`.
     The buffer is owned here (the library never allocates)."""
-    need = fp8_workspace_bytes(M, N, K)
+    ensure_workspace_bytes(fp8_workspace_bytes(M, N, K), device)
+
+
+def ensure_workspace_bytes(need: int, device=None) -> None:
+    """Registers a scratch buffer of at least `need` bytes on `device` (kept if the current one is larger)."""
     if need == 0:
         return
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)

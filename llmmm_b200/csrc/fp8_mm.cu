@@ -1258,11 +1258,37 @@ int llmmm_fp8_blockwise_mm_swiglu_e4m3out(const void*    A,
   if (info == nullptr) {
     return LLMMM_ERR_UNSUPPORTED;
   }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (M <= 64) {
+    // Decode-sized: the weight-streaming decode kernel leaves the [M, 2I] accumulator in the registered scratch
+    // (behind its own partial tiles) and a second, tiny kernel applies SwiGLU and quantises.  Without enough
+    // scratch the 256-row kernel below runs (correct, but it reads the weights at a fraction of the rate).
+    const Workspace ws  = registered_workspace(info->device);
+    const size_t    off = (decode_workspace_bytes(M) + 255) & ~size_t(255);
+    if (ws.ptr != nullptr && ws.bytes >= off + (size_t)M * 2 * I * sizeof(float)) {
+      float*    acc = reinterpret_cast<float*>(static_cast<uint8_t*>(ws.ptr) + off);
+      const int rc  = launch_decode(true, A, A_scale_t, B_gate_up_t, B_scale_t, acc, nullptr, M, 2 * I, K, s);
+      if (rc == LLMMM_OK) {
+        return launch_swiglu_quant(acc, H, H_scale_t, M, I, s);
+      }
+      if (rc > 0) {
+        return rc;
+      }
+    }
+  }
   if (info->max_pairs < 1) {
     return set_error(LLMMM_ERR_UNSUPPORTED, "this device cannot hold a cluster of two CTAs of the GEMM kernel");
   }
-  return launch_fp8_swiglu(A, A_scale_t, B_gate_up_t, B_scale_t, H, H_scale_t, M, I, K, info,
-                           reinterpret_cast<cudaStream_t>(stream));
+  return launch_fp8_swiglu(A, A_scale_t, B_gate_up_t, B_scale_t, H, H_scale_t, M, I, K, info, s);
+}
+
+size_t llmmm_fp8_swiglu_workspace_bytes(int M, int I, int K)
+{
+  (void)K;
+  if (M < 1 || M > 64 || I < 128) {
+    return 0;  // larger M: the fused kernel needs no scratch
+  }
+  return ((llmmm::decode_workspace_bytes(M) + 255) & ~size_t(255)) + (size_t)M * 2 * I * sizeof(float);
 }
 
 int llmmm_fp8_blockwise_mm_f32out(const void*    A,

@@ -75,6 +75,11 @@ Workspace registered_workspace(int device);
 
 // Scratch the pair kernels want for splitting the tiles of their last wave (pair_walk.cuh).
 size_t split_workspace_bytes();
+// Scratch of the decode kernel for M rows (header + partial tiles), fp8_decode.cu.
+size_t decode_workspace_bytes(int M);
+// SwiGLU + 1x128 quantisation of a gate_up accumulator acc [M, 2I] fp32 (quant.cu): the second step of the
+// decode-sized form of llmmm_fp8_blockwise_mm_swiglu_e4m3out.
+int launch_swiglu_quant(const float* acc, void* H, float* H_s, int M, int I, cudaStream_t stream);
 
 // What the launch heuristics choose for a problem, as text (llmmm_describe_plan), and the one-time set-up of
 // every kernel of a family on the current device (llmmm_tune): function attributes, occupancy queries.

@@ -216,6 +216,49 @@ __global__ void __launch_bounds__(RN_THREADS)
   }
 }
 
+// h = silu(gate) * up for one row and one 128-wide group per warp, then the output quantisation rule of the
+// GEMM epilogue (scale = amax / 448, q = e4m3(h * (448 / amax))): the same arithmetic as the fused epilogue of
+// the prefill-sized kernel, applied to an accumulator that a decode-sized GEMM left in scratch.
+__global__ void __launch_bounds__(256)
+  swiglu_quant_1x128_kernel(const float* __restrict__ acc, uint8_t* __restrict__ H, float* __restrict__ H_s, int M, int I)
+{
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane   = threadIdx.x & 31;
+  const int groups = I / 128;
+  const int w      = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (w >= M * groups) {
+    return;
+  }
+  const int    m = w / groups, g = w % groups;
+  const float* row = acc + (size_t)m * 2 * I;
+  const float4 ga  = __ldcs(reinterpret_cast<const float4*>(row + (size_t)g * 128) + lane);
+  const float4 up  = __ldcs(reinterpret_cast<const float4*>(row + I + (size_t)g * 128) + lane);
+  float4       h;
+  h.x = __fdividef(ga.x, 1.0f + __expf(-ga.x)) * up.x;
+  h.y = __fdividef(ga.y, 1.0f + __expf(-ga.y)) * up.y;
+  h.z = __fdividef(ga.z, 1.0f + __expf(-ga.z)) * up.z;
+  h.w = __fdividef(ga.w, 1.0f + __expf(-ga.w)) * up.w;
+  const float amax  = warp_max(amax4(h));
+  const float scale = __fdiv_rn(amax, 448.0f);
+  const float inv   = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 0.0f;
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(h.x * inv, h.y * inv), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(h.z * inv, h.w * inv), __NV_SATFINITE, __NV_E4M3);
+  reinterpret_cast<uint32_t*>(H + (size_t)m * I + (size_t)g * 128)[lane] = lo | (hi << 16);
+  if (lane == 0) {
+    H_s[(size_t)g * M + m] = scale;
+  }
+}
+
+int launch_swiglu_quant(const float* acc, void* H, float* H_s, int M, int I, cudaStream_t stream)
+{
+  const int warps = M * (I / 128);
+  LLMMM_CUDA_TRY(launch_pdl(swiglu_quant_1x128_kernel, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, stream, 1, acc,
+                            static_cast<uint8_t*>(H), H_s, M, I));
+  g_launches.fetch_add(1);
+  return LLMMM_OK;
+}
+
 }  // namespace llmmm
 
 extern "C" {

@@ -24,7 +24,7 @@ def make_case(oracle, seed, M, I, K):
     return A_q, A_s, B_q, B_s
 
 
-def run(capi, cuda, case, M, I, K):
+def run(capi, cuda, case, M, I, K, launches=1):
     dA, dAs, dB, dBs = to_dev(cuda, *case)
     Hq = torch.full((M, I), 0xAA, dtype=torch.uint8, device=cuda)
     Hs = torch.full((I // 128, M), float("nan"), device=cuda)
@@ -32,7 +32,7 @@ def run(capi, cuda, case, M, I, K):
     capi.fp8_blockwise_mm_swiglu(dA, dAs, dB, dBs, Hq, Hs, M, I, K)
     torch.cuda.synchronize()
     capi.check_status()
-    assert capi.launch_count() == before + 1
+    assert capi.launch_count() == before + launches
     return Hq.cpu().numpy(), Hs.cpu().numpy()
 
 
@@ -100,6 +100,26 @@ def test_swiglu_qwen3_4b_prefill_and_down_projection(capi, oracle, cuda):
     # the two activations differ only where an e4m3 rounding flipped: a few bytes in a thousand
     assert float((Uq == Hq).float().mean()) > 0.995
     assert float((Y - Y2).abs().max()) <= 2e-3 * float(Y2.abs().max())
+
+
+@pytest.mark.parametrize("M", [1, 16, 33, 64])
+@pytest.mark.parametrize("IK", [(9728, 2560), (256, 1024)])
+def test_swiglu_decode_sized(capi, oracle, cuda, M, IK):
+    # M <= 64 with enough scratch: the weight-streaming decode kernel + a small SwiGLU/quantise kernel (2 launches);
+    # without scratch the 256-row kernel (1 launch).  Both against the oracle, and against each other.
+    I, K = IK
+    case = make_case(oracle, 93 + M, M, I, K)
+    capi.clear_workspace()
+    gq1, gs1 = run(capi, cuda, case, M, I, K, launches=1)
+    check(oracle, case, gq1, gs1)
+    capi.ensure_swiglu_workspace(M, I, K)
+    gq2, gs2 = run(capi, cuda, case, M, I, K, launches=2)
+    check(oracle, case, gq2, gs2)
+    ok = gs1 > 0
+    assert (np.abs(gs2[ok] / gs1[ok] - 1) <= 2e-5).all()
+    assert (gq1 == gq2).mean() > 0.99
+    gq3, gs3 = run(capi, cuda, case, M, I, K, launches=2)
+    assert np.array_equal(gq2, gq3) and np.array_equal(gs2.view(np.uint32), gs3.view(np.uint32))
 
 
 def test_swiglu_argument_errors(capi, cuda):
