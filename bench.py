@@ -488,8 +488,32 @@ def extra_configs(torch, capi, dev, peaks):
         ms_d = time_graph(torch, [(lambda w=w: capi.fp8_blockwise_mm_swiglu(xq, xs, w[0], w[1], hq_, hs_, m_, i_, k)) for w in wsets] * 4)
         by = 2 * i_ * k + 4 * (2 * i_ // 128) * (k // 128) + m_ * k + 4 * m_ * k // 128 + m_ * i_ + 4 * m_ * i_ // 128
         dec_sw.append({"M": m_, "us": ms_d * 1e3, "gbs": by / (ms_d * 1e-3) / 1e9, "frac_of_measured_hbm": by / (ms_d * 1e-3) / 1e9 / hbm})
-    capi.set_static_weights(False)
     out["swiglu_gate_up_decode_19456x2560"] = dec_sw
+    # the whole Qwen3-4B MLP block as three launches that hand each other 1x128-quantised activations:
+    # RMSNorm + quantise (hidden 2560) -> gate_up + SwiGLU + quantise (I = 9728) -> down projection (fp32 out)
+    mlp = []
+    wd = [(torch.randint(0, 120, (k, i_), dtype=torch.uint8, device=dev), torch.rand(k // 128, i_ // 128, device=dev)) for _ in range(3)]
+    gamma = torch.rand(k, device=dev) + 0.5
+    for m_ in (1, 16, 4096):
+        xin = torch.randn(m_, k, device=dev)
+        xq = torch.empty(m_, k, dtype=torch.uint8, device=dev)
+        xs = torch.empty(k // 128, m_, device=dev)
+        hq_ = torch.empty(m_, i_, dtype=torch.uint8, device=dev)
+        hs_ = torch.empty(i_ // 128, m_, device=dev)
+        y = torch.empty(m_, k, device=dev)
+        if m_ <= 64:
+            capi.ensure_swiglu_workspace(m_, i_, k)
+
+        def block(j):
+            capi.fp8_rmsnorm_quant_1x128(xin, gamma, 1e-6, xq, xs, m_, k)
+            capi.fp8_blockwise_mm_swiglu(xq, xs, wsets[j][0], wsets[j][1], hq_, hs_, m_, i_, k)
+            capi.fp8_blockwise_mm_f32(hq_, hs_, wd[j][0], wd[j][1], y, m_, k, i_)
+
+        ms_b = time_graph(torch, [(lambda j=j: block(j)) for j in range(3)] * 4)
+        mlp.append({"M": m_, "us_per_block": ms_b * 1e3, "launches_per_block": 3 if m_ > 64 else 4,
+                    "weight_bytes": 3 * i_ * k, "tflops": 2.0 * m_ * 3 * i_ * k / (ms_b * 1e-3) / 1e12})
+    capi.set_static_weights(False)
+    out["qwen3_4b_mlp_block"] = mlp
     capi.check_status()
     return out
 
