@@ -58,6 +58,7 @@ def check(oracle, case, gq, gs, rows=None):
 def test_swiglu_small_shapes(capi, oracle, cuda, shape):
     M, I, K = shape
     case = make_case(oracle, 90, M, I, K)
+    capi.clear_workspace()  # the fused 256-row kernel for every M (with scratch, M <= 64 takes the two-kernel path)
     gq, gs = run(capi, cuda, case, M, I, K)
     check(oracle, case, gq, gs)
 
