@@ -843,10 +843,10 @@ size_t llmmm_fp8_workspace_bytes(int M, int N, int K)
   if (M < 1 || N < 128) {
     return 0;
   }
-  if (M > 128) {
-    return llmmm::split_workspace_bytes();
+  if (M > 64) {
+    return llmmm::split_workspace_bytes();  // the pair kernel's split tiles (65..128 rows use it for few-tile shapes)
   }
-  if (M > 64 || N / 128 > llmmm::deccfg::MAX_GROUPS) {
+  if (N / 128 > llmmm::deccfg::MAX_GROUPS) {
     return 0;
   }
   return llmmm::decode_workspace_bytes(M);

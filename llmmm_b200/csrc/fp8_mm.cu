@@ -394,6 +394,23 @@ struct Fp8PairBars {
 //              into the full C_q [M, ld] / C_s [ld/128, M] of up to 8 destinations at once -- the buffers of the
 //              other GPUs of an N-split, mapped into this process: the all-gather of the outputs happens as
 //              plain peer stores of the epilogue, overlapped with the tiles still being computed.
+// Which general kernel a problem runs on.  More than 128 rows: the pair kernel.  65..128 rows: the single-CTA
+// kernel (128-row tiles waste nothing), unless its tiles would occupy at most half of the SMs and scratch is
+// registered: then the pair kernel, whose tiles can be cut along K, wins although half of each tile's rows are
+// empty (measured at M = 128: 2560x9728 45.6 -> 23.6 us, 4096x4096 21.5 -> 18.2 us; 19456x2560, 76 tiles,
+// would lose: 17.3 -> 29.3 us).
+static bool fp8_use_pair_kernel(const DeviceInfo* info, int M, int N)
+{
+  if (info->max_pairs < 1) {
+    return false;
+  }
+  if (M > 128) {
+    return true;
+  }
+  const int       tiles_1cta = ((M + fp8cfg::BM - 1) / fp8cfg::BM) * ((N + fp8cfg::BN - 1) / fp8cfg::BN);
+  const Workspace ws         = registered_workspace(info->device);
+  return M > 64 && ws.ptr != nullptr && ws.bytes >= split_workspace_bytes() && 2 * tiles_1cta <= info->sm_count;
+}
 constexpr int EPI_E4M3   = 0;
 constexpr int EPI_F32    = 1;
 constexpr int EPI_SWIGLU = 2;
@@ -1040,7 +1057,7 @@ static int launch_fp8(const void*  A,
     return LLMMM_ERR_UNSUPPORTED;
   }
 #ifndef LLMMM_FP8_NO_PAIR
-  if (M > 128 && info->max_pairs > 0) {
+  if (fp8_use_pair_kernel(info, M, N)) {
     return launch_fp8_pair<OUT_F32>(A, A_s, B, B_s, C, C_s, M, N, K, info, stream);
   }
 #endif
@@ -1071,7 +1088,7 @@ void describe_fp8_plan(const DeviceInfo* info, bool out_f32, int M, int N, int K
   if (describe_decode_plan(info, M, N, K, buf, len)) {
     return;
   }
-  if (M > 128 && info->max_pairs > 0) {
+  if (fp8_use_pair_kernel(info, M, N)) {
     using namespace fp8pair;
     const int       tiles    = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int       k_blocks = K / BK;

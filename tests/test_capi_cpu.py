@@ -52,11 +52,9 @@ def test_workspace_size_rule(capi):
     # decode-sized problems need scratch; larger M does not
     assert capi.fp8_workspace_bytes(1, 6144, 2560) == capi.fp8_workspace_bytes(16, 2560, 9728) > 0
     assert capi.fp8_workspace_bytes(64, 6144, 2560) > capi.fp8_workspace_bytes(32, 6144, 2560)
-    # 65..128 rows run on the single-CTA kernel, which never splits a tile
-    assert capi.fp8_workspace_bytes(65, 6144, 2560) == 0
-    assert capi.fp8_workspace_bytes(128, 6144, 2560) == 0
-    # larger problems: one size for all shapes (partial tiles of the split last wave)
-    assert capi.fp8_workspace_bytes(4096, 4096, 4096) == capi.fp8_workspace_bytes(129, 128, 128) > 0
+    # more than 64 rows: one size for all shapes (partial tiles of the pair kernel's split last wave)
+    assert capi.fp8_workspace_bytes(4096, 4096, 4096) == capi.fp8_workspace_bytes(65, 128, 128) > 0
+    assert capi.fp8_workspace_bytes(128, 6144, 2560) == capi.fp8_workspace_bytes(129, 128, 128)
 
 
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the behaviour on a machine without a GPU")

@@ -198,6 +198,23 @@ def test_decode_launch_chain_with_static_weights(capi, oracle, cuda, M):
         check_against_oracle(oracle, *case, promised[i][0].cpu().numpy(), promised[i][1].cpu().numpy(), Cf.cpu().numpy())
 
 
+@pytest.mark.parametrize("shape", [(128, 2560, 4096), (65, 512, 2048), (100, 4096, 1024)])
+def test_mid_m_few_tiles_take_the_pair_kernel_with_scratch(capi, oracle, cuda, shape):
+    # 65..128 rows, tiles on at most half of the SMs: single-CTA kernel without scratch, pair kernel (whose tiles
+    # are cut along K) with it; both against the oracle, and within the order of fp32 sums of each other
+    M, N, K = shape
+    case = make_case(oracle, 45, M, N, K)
+    capi.clear_workspace()
+    assert "fp8_blockwise_gemm_kernel" in capi.describe_plan("fp8", M, N, K)
+    gq, gs, gf = gpu_mm(capi, cuda, *case, workspace=False)
+    check_against_oracle(oracle, *case, gq, gs, gf)
+    capi.ensure_workspace(M, N, K)
+    assert "fp8_blockwise_gemm_pair_kernel" in capi.describe_plan("fp8", M, N, K)
+    gq2, gs2, gf2 = gpu_mm(capi, cuda, *case, workspace=True)
+    check_against_oracle(oracle, *case, gq2, gs2, gf2)
+    assert np.abs(gf - gf2).max() <= 4e-6 * np.abs(gf).max()
+
+
 def gpu_c_quant(acc):
     """The output quantisation rule in torch fp32 on the GPU (for full-size property checks)."""
     M, N = acc.shape
