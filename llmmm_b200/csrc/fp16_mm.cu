@@ -696,10 +696,26 @@ static int launch_fp16_pair(const void* A, const void* B, void* C, int M, int N,
   return LLMMM_OK;
 }
 
+// Which kernel a problem runs on: more than 128 rows (and columns) the pair kernel; 65..128 rows the single-CTA
+// kernel, unless its tiles would occupy at most half of the SMs and scratch is registered: then the pair
+// kernel, whose tiles can be cut along K (the same rule as for FP8).
+static bool fp16_use_pair_kernel(const DeviceInfo* info, int M, int N)
+{
+  if (info->max_pairs < 1 || N <= 128) {
+    return false;
+  }
+  if (M > 128) {
+    return true;
+  }
+  const int       tiles_1cta = ((M + fp16cfg::BM - 1) / fp16cfg::BM) * ((N + fp16cfg::BN - 1) / fp16cfg::BN);
+  const Workspace ws         = registered_workspace(info->device);
+  return M > 64 && ws.ptr != nullptr && ws.bytes >= split_workspace_bytes() && 2 * tiles_1cta <= info->sm_count;
+}
+
 void describe_fp16_plan(const DeviceInfo* info, bool bf16, int M, int N, int K, char* buf, size_t len)
 {
   const char* t = bf16 ? "__nv_bfloat16" : "__half";
-  if (M > 128 && info->max_pairs > 0) {
+  if (fp16_use_pair_kernel(info, M, N)) {
     using namespace fp16pair;
     const int       tiles   = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int       k_steps = (K + BK - 1) / BK;
@@ -756,7 +772,7 @@ static int launch_fp16(const void* A, const void* B, void* C, int M, int N, int 
       || !make_tmap_2d(&tm_c, C, dt, 2, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B)) {
     return LLMMM_ERR_CUDA;
   }
-  if (M > 128 && N > 128 && info->max_pairs > 0) {
+  if (fp16_use_pair_kernel(info, M, N)) {
     return launch_fp16_pair<T>(A, B, C, M, N, K, info, stream);
   }
   static thread_local bool attr_set[64] = {};

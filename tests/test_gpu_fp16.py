@@ -90,6 +90,21 @@ def test_split_last_wave(capi, oracle, cuda, shape, dtype):
     assert capi.split_launch_count() == n0 + 1
 
 
+@pytest.mark.parametrize("shape", [(128, 2560, 4096), (65, 512, 8192), (100, 4096, 4104)])
+def test_mid_m_few_tiles_take_the_pair_kernel_with_scratch(capi, oracle, cuda, shape):
+    # 65..128 rows whose tiles would occupy at most half of the SMs: the single-CTA kernel without scratch,
+    # the pair kernel (tiles cut along K) with it
+    M, N, K = shape
+    capi.clear_workspace()
+    assert "fp16_gemm_kernel" in capi.describe_plan("fp16", M, N, K)
+    run_case(capi, oracle, cuda, M, N, K, torch.float16, seed=8, scratch=False)
+    capi.ensure_workspace(M, N, K)
+    assert "fp16_gemm_pair_kernel" in capi.describe_plan("fp16", M, N, K)
+    n0 = capi.split_launch_count()
+    run_case(capi, oracle, cuda, M, N, K, torch.bfloat16, seed=8, scratch=True)
+    assert capi.split_launch_count() == n0 + 1
+
+
 def test_split_is_bitwise_stable(capi, cuda):
     # arrival counters reset themselves and the chunks are added in a fixed order
     M, N, K = 384, 640, 4096
