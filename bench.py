@@ -517,8 +517,30 @@ def extra_configs(torch, capi, dev, peaks):
         ms_b = time_graph(torch, [(lambda j=j: block(j)) for j in range(3)] * 4)
         mlp.append({"M": m_, "us_per_block": ms_b * 1e3, "launches_per_block": 3 if m_ > 64 else 4,
                     "weight_bytes": 3 * i_ * k, "tflops": 2.0 * m_ * 3 * i_ * k / (ms_b * 1e-3) / 1e12})
-    capi.set_static_weights(False)
     out["qwen3_4b_mlp_block"] = mlp
+    # qkv projection of Qwen3-4B (32 query + 8 key + 8 value heads of 128, hidden 2560) with the per-head q/k
+    # RMSNorm and the rotary embedding fused in front of the output quantisation, beside the plain GEMM
+    n_q, n_kv = 32, 8
+    nq = (n_q + 2 * n_kv) * 128
+    wq = [(torch.randint(0, 120, (nq, k), dtype=torch.uint8, device=dev), torch.rand(nq // 128, k // 128, device=dev)) for _ in range(3)]
+    ang = torch.arange(8192, device=dev, dtype=torch.float32)[:, None] / (1e6 ** (torch.arange(64, device=dev) / 64.0))[None, :]
+    cos_t, sin_t = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+    qw, kw = torch.rand(128, device=dev) + 0.5, torch.rand(128, device=dev) + 0.5
+    qkv = []
+    for m_ in (1, 16, 4096):
+        xq = torch.randint(0, 120, (m_, k), dtype=torch.uint8, device=dev)
+        xs = torch.rand(k // 128, m_, device=dev)
+        oq = torch.empty(m_, nq, dtype=torch.uint8, device=dev)
+        os_ = torch.empty(nq // 128, m_, device=dev)
+        pos = (torch.arange(m_, device=dev, dtype=torch.int32) + 17) % 8192
+        capi.ensure_qk_norm_rope_workspace(m_, nq, k)
+        ms_r = time_graph(torch, [(lambda w=w: capi.fp8_blockwise_mm_qk_norm_rope(xq, xs, w[0], w[1], oq, os_, pos, cos_t, sin_t, qw, kw,
+                                                                                  1e-6, n_q, n_kv, m_, nq, k)) for w in wq] * 4)
+        ms_g = time_graph(torch, [(lambda w=w: capi.fp8_blockwise_mm(xq, xs, w[0], w[1], oq, os_, m_, nq, k)) for w in wq] * 4)
+        qkv.append({"M": m_, "us_fused": ms_r * 1e3, "us_plain_gemm": ms_g * 1e3, "launches": 1 if m_ > 64 else 2,
+                    "tflops_fused": 2.0 * m_ * nq * k / (ms_r * 1e-3) / 1e12})
+    capi.set_static_weights(False)
+    out["qwen3_4b_qkv_norm_rope_6144x2560"] = qkv
     capi.check_status()
     return out
 

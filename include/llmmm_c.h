@@ -129,6 +129,43 @@ int llmmm_fp8_blockwise_mm_swiglu_e4m3out(const void*    A,
 
 size_t llmmm_fp8_swiglu_workspace_bytes(int M, int I, int K);
 
+/* qkv projection with the per-head q/k RMSNorm and the rotary position embedding fused in front of the output
+ * quantisation (the reference's README.md:16 plans "norm/rope fusion"; it has no implementation of it).  Heads
+ * are 128 columns wide, which is exactly one 1x128 quantisation group:
+ *   B_t [N, K] e4m3 with N = (n_q_heads + 2 n_kv_heads) * 128: query heads first, then key heads, then value heads
+ *   acc = the blockwise product of llmmm_fp8_blockwise_mm_e4m3out, [M, N], kept on chip
+ *   query / key head x (128 values of row m):
+ *     if the weight pointer of its kind is not NULL:  x[i] = x[i] * (1 / sqrt(mean(x^2) + eps)) * weight[i]
+ *     p = positions[m];  for i < 64:  y[i]      = x[i]      * cos_table[p, i] - x[i + 64] * sin_table[p, i]
+ *                                     y[i + 64] = x[i + 64] * cos_table[p, i] + x[i]      * sin_table[p, i]
+ *   value heads pass unchanged; every head is then quantised as one 1x128 group into C [M, N] e4m3 and
+ *   C_scale_t [(N/128), M] by the same rule as C above.
+ *   positions [M] int32 (rows of the angle tables), cos_table / sin_table [rows, 64] fp32, weights [128] fp32.
+ * Requires K%128 == 0, any M >= 1; tables, weights, A, B_t and C 16-byte aligned.  M > 64 runs one fused kernel
+ * (256-row tiles; a partly filled last wave is cut along K when scratch is registered).  M <= 64 runs the
+ * weight-streaming decode kernel into scratch followed by a small kernel, provided the registered scratch has
+ * llmmm_fp8_qk_norm_rope_workspace_bytes(M, N, K) bytes; otherwise the 256-row kernel runs for small M too. */
+int llmmm_fp8_blockwise_mm_qk_norm_rope_e4m3out(const void*    A,
+                                                const float*   A_scale_t,
+                                                const void*    B_t,
+                                                const float*   B_scale_t,
+                                                void*          C,
+                                                float*         C_scale_t,
+                                                const int*     positions,
+                                                const float*   cos_table,
+                                                const float*   sin_table,
+                                                const float*   q_norm_weight,
+                                                const float*   k_norm_weight,
+                                                float          eps,
+                                                int            n_q_heads,
+                                                int            n_kv_heads,
+                                                int            M,
+                                                int            N,
+                                                int            K,
+                                                llmmm_stream_t stream);
+
+size_t llmmm_fp8_qk_norm_rope_workspace_bytes(int M, int N, int K);
+
 /* Same product with the fp32 accumulator written out unquantised, C [M,N] fp32.
  * Replaces fp8_gemm_blockwise_quant_A_1x128__B_128x128__output_fp32
  * (examples/005.fp8.mm.cu:217-246). */

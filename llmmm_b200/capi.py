@@ -46,6 +46,9 @@ def lib() -> ctypes.CDLL:
         L.llmmm_fp8_blockwise_mm_e4m3out.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
         L.llmmm_fp8_blockwise_mm_e4m3out_noalloc.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
         L.llmmm_fp8_blockwise_mm_swiglu_e4m3out.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
+        L.llmmm_fp8_blockwise_mm_qk_norm_rope_e4m3out.argtypes = [_vp] * 11 + [ctypes.c_float, _i, _i, _i, _i, _i, _vp]
+        L.llmmm_fp8_qk_norm_rope_workspace_bytes.restype = ctypes.c_size_t
+        L.llmmm_fp8_qk_norm_rope_workspace_bytes.argtypes = [_i, _i, _i]
         L.llmmm_fp8_blockwise_mm_e4m3out_gather.argtypes = [_vp, _vp, _vp, _vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp),
                                                             _i, _i, _i, _i, _i, _i, _vp]
         L.llmmm_fp8_blockwise_mm_f32out.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
@@ -66,6 +69,7 @@ EXPORTED_SYMBOLS = (
     "llmmm_fp8_blockwise_mm_e4m3out_noalloc", "llmmm_fp8_blockwise_mm_swiglu_e4m3out",
     "llmmm_fp8_blockwise_mm_e4m3out_gather", "llmmm_fp8_rmsnorm_quant_1x128", "llmmm_fp8_swiglu_workspace_bytes",
     "llmmm_transpose_aligned_128", "llmmm_selftest_wait_expiry",
+    "llmmm_fp8_blockwise_mm_qk_norm_rope_e4m3out", "llmmm_fp8_qk_norm_rope_workspace_bytes",
 )
 
 
@@ -158,6 +162,25 @@ def fp8_blockwise_mm_swiglu(A_q, A_s, B_gate_up_q, B_s, H_q, H_s, M: int, I: int
         _check(lib().llmmm_fp8_blockwise_mm_swiglu_e4m3out(
             _dev(A_q), _dev(A_s, torch.float32), _dev(B_gate_up_q), _dev(B_s, torch.float32), _dev(H_q),
             _dev(H_s, torch.float32), M, I, K, _stream(stream)))
+
+
+def fp8_blockwise_mm_qk_norm_rope(A_q, A_s, B_q, B_s, C_q, C_s, positions, cos, sin, q_weight, k_weight, eps: float,
+                                  n_q_heads: int, n_kv_heads: int, M: int, N: int, K: int, stream=None) -> None:
+    """qkv projection [N, K], N = (n_q_heads + 2 n_kv_heads) * 128, with the per-head RMSNorm of query / key heads
+    (weights may be None) and the rotary embedding (pairs (i, i + 64), table row positions[m]) fused in front of
+    the 1x128 output quantisation."""
+    with torch.cuda.device(A_q.device):
+        _check(lib().llmmm_fp8_blockwise_mm_qk_norm_rope_e4m3out(
+            _dev(A_q), _dev(A_s, torch.float32), _dev(B_q), _dev(B_s, torch.float32), _dev(C_q),
+            _dev(C_s, torch.float32), _dev(positions, torch.int32), _dev(cos, torch.float32), _dev(sin, torch.float32),
+            None if q_weight is None else _dev(q_weight, torch.float32),
+            None if k_weight is None else _dev(k_weight, torch.float32),
+            float(eps), n_q_heads, n_kv_heads, M, N, K, _stream(stream)))
+
+
+def ensure_qk_norm_rope_workspace(M: int, N: int, K: int, device=None) -> None:
+    """Scratch for fp8_blockwise_mm_qk_norm_rope (decode-sized: accumulator; larger: the last-wave split)."""
+    ensure_workspace_bytes(int(lib().llmmm_fp8_qk_norm_rope_workspace_bytes(M, N, K)), device)
 
 
 def fp8_blockwise_mm_f32(A_q, A_s, B_q, B_s, C, M: int, N: int, K: int, stream=None) -> None:

@@ -394,6 +394,9 @@ struct Fp8PairBars {
 //              into the full C_q [M, ld] / C_s [ld/128, M] of up to 8 destinations at once -- the buffers of the
 //              other GPUs of an N-split, mapped into this process: the all-gather of the outputs happens as
 //              plain peer stores of the epilogue, overlapped with the tiles still being computed.
+//   EPI_ROPE   like EPI_E4M3 for a qkv projection with heads of 128 columns: a thread's 128 accumulators are one
+//              head of its row, so the per-head RMSNorm of query / key heads and the rotary embedding are
+//              thread-local arithmetic in front of the quantisation.
 // Which general kernel a problem runs on.  More than 128 rows: the pair kernel.  65..128 rows: the single-CTA
 // kernel (128-row tiles waste nothing), unless its tiles would occupy at most half of the SMs and scratch is
 // registered: then the pair kernel, whose tiles can be cut along K, wins although half of each tile's rows are
@@ -415,6 +418,7 @@ constexpr int EPI_E4M3   = 0;
 constexpr int EPI_F32    = 1;
 constexpr int EPI_SWIGLU = 2;
 constexpr int EPI_GATHER = 3;
+constexpr int EPI_ROPE   = 4;
 
 struct GatherDst {
   uint8_t* c[8];   // C_q base of every destination
@@ -424,6 +428,23 @@ struct GatherDst {
   int      col0;   // first column of this call's shard in the full C
   int      pad;
 };
+
+// A read-only 16-byte load the compiler may not move across other asm volatile statements (the epilogue of
+// EPI_ROPE limits its loads in flight with it: hoisted above one another they would need a second register file).
+__device__ __forceinline__ float4 ldg_pinned(const float4* p)
+{
+  float4 v;
+  asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+
+// EPI_ROPE without norm weights multiplies by these
+__device__ const float4 g_ones128_v[32] = {
+  {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1},
+  {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1},
+  {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1},
+  {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}};
+#define g_ones128 (reinterpret_cast<const float*>(g_ones128_v))
 
 template<int EPI>
 __global__ void __launch_bounds__(fp8pair::THREADS, 1)
@@ -443,6 +464,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
                                  float* __restrict__ sk_partials,
                                  uint32_t* __restrict__ sk_counters,
                                  const __grid_constant__ GatherDst gather,
+                                 const __grid_constant__ RopeHook rope,
                                  uint32_t* status)
 {
   using namespace fp8pair;
@@ -451,7 +473,8 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
   constexpr int  TILE_N  = SWIGLU ? 128 : BN;  // output columns per tile
   // EPI_GATHER runs the ring one stage shorter: the sixth stage's two 16 KB slots stage the output tile so that
   // the stores to the other GPUs leave as whole 128-byte rows
-  constexpr uint32_t NSTAGES = (EPI == EPI_GATHER) ? STAGES - 1 : STAGES;
+  // (EPI_ROPE stages its angle-table rows in the same slots)
+  constexpr uint32_t NSTAGES = (EPI == EPI_GATHER || EPI == EPI_ROPE) ? STAGES - 1 : STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Fp8PairBars*       bars       = reinterpret_cast<Fp8PairBars*>(smem + OFF_BAR);
@@ -722,7 +745,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
       }
 
       PROF8_T(e0);
-      if (!SWIGLU && kb_hi - kb_lo < k_blocks) {  // (SWIGLU tiles are never cut)
+      if (!SWIGLU && EPI != EPI_ROPE && kb_hi - kb_lo < k_blocks) {  // (SWIGLU and ROPE tiles are never cut)
         // A chunk of a split tile, the last piece of work of this pair.  This warp's 32x128 piece is handled
         // independently of the other warps: publish the partial sum (four columns per lane side by side:
         // a warp writes 512 contiguous bytes per instruction), count the arrival, and if it is the last
@@ -792,6 +815,82 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
           sk_counters[tt * 16 + unit] = 0;  // every launch leaves the counters at zero
         }
         PROF8_STAMP(5);
+      }
+      if constexpr (EPI == EPI_ROPE) {
+        // ng is the head: query heads first, then key heads, then value heads (which pass unchanged).  The whole
+        // warp takes part, also lanes of rows beyond M: the angle-table rows go through shared memory.
+        const int kind = ng < rope.n_q ? 0 : (ng < rope.n_q + rope.n_kv ? 1 : 2);
+        if (g_ok && kind < 2) {
+          // one straight line of arithmetic with and without weights (a branch around 128 accumulator updates
+          // costs registers at the join): without weights the factors are exactly 1
+          const float* wgt = kind == 0 ? rope.q_w : rope.k_w;
+          const bool   nrm = wgt != nullptr;
+          float        ss4[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // four chains: a single one is 128 dependent FMAs
+#pragma unroll
+          for (int i = 0; i < 128; ++i) {
+            ss4[i & 3] = fmaf(acc[i], acc[i], ss4[i & 3]);
+          }
+          const float ss = (ss4[0] + ss4[1]) + (ss4[2] + ss4[3]);
+          // (the approximate instruction, 2 ulp: the exact square root and reciprocal are subroutine calls, and a
+          // call here has to save accumulators on the stack)
+          const float   inv = nrm ? rsqrtf(fmaf(ss, 1.0f / 128.0f, rope.eps)) : 1.0f;
+          const float4* w4  = reinterpret_cast<const float4*>(nrm ? wgt : g_ones128);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if ((i & 3) == 0 && i > 0) {
+              asm volatile("" : "+f"(acc[4 * i - 1]));  // four loads in flight at most: the next group starts here
+            }
+            const float4 wv = ldg_pinned(w4 + i);  // the same address in every lane
+            acc[4 * i]      = acc[4 * i] * inv * wv.x;
+            acc[4 * i + 1]  = acc[4 * i + 1] * inv * wv.y;
+            acc[4 * i + 2]  = acc[4 * i + 2] * inv * wv.z;
+            acc[4 * i + 3]  = acc[4 * i + 3] * inv * wv.w;
+          }
+          // Rotation.  Lane l needs row pos[m_l] of both tables (2 x 256 bytes).  Read directly, every load
+          // instruction would touch 32 different cache lines; instead the warp fetches 16 columns of its 32 rows
+          // at a time with 64-byte pieces per row (8 lines per instruction) into a 4 KB staging tile
+          // (16-byte chunks XOR-swizzled by row) and every lane reads its own row from there.
+          uint8_t*  stg   = smem + (half == 0 ? OFF_A : OFF_B) + (STAGES - 1) * A_BYTES + quarter * 4096;
+          asm volatile("" : "+f"(acc[127]));  // (behind the normalisation)
+          const int p_own = __ldg(rope.pos + (m_ok ? m : 0));
+          const int part  = lane & 7;  // 0..3: cos chunk, 4..7: sin chunk
+          const float* tab = part < 4 ? rope.cos : rope.sin;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {  // four loads in flight: addresses and data of eight do not fit
+              float4 ld[4];
+#pragma unroll
+              for (int jj = 0; jj < 4; ++jj) {
+                const int rr = 4 * (4 * b + jj) + (lane >> 3);
+                const int pr = __shfl_sync(0xffffffffu, p_own, rr);
+                ld[jj] = ldg_pinned(reinterpret_cast<const float4*>(tab + (size_t)pr * 64 + 16 * c) + (part & 3));
+              }
+#pragma unroll
+              for (int jj = 0; jj < 4; ++jj) {
+                const int rr = 4 * (4 * b + jj) + (lane >> 3);
+                *reinterpret_cast<float4*>(stg + rr * 128 + ((part ^ (rr & 7)) << 4)) = ld[jj];
+              }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              const float4 cv = *reinterpret_cast<const float4*>(stg + lane * 128 + ((q4 ^ (lane & 7)) << 4));
+              const float4 sn = *reinterpret_cast<const float4*>(stg + lane * 128 + (((4 + q4) ^ (lane & 7)) << 4));
+              const float  cc[4] = {cv.x, cv.y, cv.z, cv.w};
+              const float  sv[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int   i0 = 16 * c + 4 * q4 + e;
+                const float x0 = acc[i0], x1 = acc[64 + i0];
+                acc[i0]      = __fmaf_rn(x0, cc[e], -__fmul_rn(x1, sv[e]));
+                acc[64 + i0] = __fmaf_rn(x1, cc[e], __fmul_rn(x0, sv[e]));
+              }
+            }
+            __syncwarp();
+            asm volatile("" : "+f"(acc[64 + 16 * c + 15]));  // the next chunk's loads start behind this chunk's arithmetic
+          }
+        }
       }
       if constexpr (SWIGLU) {
         // acc[0..63] = gate, acc[64..127] = up of this thread's 64 output columns
@@ -930,18 +1029,19 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
   }
 }
 
-template<bool OUT_F32>
-static int launch_fp8_pair(const void*       A,
-                           const float*      A_s,
-                           const void*       B,
-                           const float*      B_s,
-                           void*             C,
-                           float*            C_s,
-                           int               M,
-                           int               N,
-                           int               K,
-                           const DeviceInfo* info,
-                           cudaStream_t      stream)
+template<int EPI>
+static int launch_fp8_pair_epi(const void*       A,
+                               const float*      A_s,
+                               const void*       B,
+                               const float*      B_s,
+                               void*             C,
+                               float*            C_s,
+                               int               M,
+                               int               N,
+                               int               K,
+                               const RopeHook&   hook,
+                               const DeviceInfo* info,
+                               cudaStream_t      stream)
 {
   using namespace fp8pair;
   CUtensorMap tm_a, tm_b;
@@ -952,7 +1052,7 @@ static int launch_fp8_pair(const void*       A,
   static thread_local bool attr_set[64] = {};
   if (!attr_set[info->device]) {
     LLMMM_CUDA_TRY(cudaFuncSetAttribute(
-      fp8_blockwise_gemm_pair_kernel<(OUT_F32 ? EPI_F32 : EPI_E4M3)>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+      fp8_blockwise_gemm_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
     attr_set[info->device] = true;
   }
   const int tiles    = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
@@ -960,11 +1060,18 @@ static int launch_fp8_pair(const void*       A,
   // estimated cost of a split, in K-blocks (one takes about 0.58 us): publishing a chunk and counting the
   // arrival about 3 us, reading a chunk back about 1.5 us
   const SplitPlan plan = plan_split(info, tiles, k_blocks, /*fixed*/ 4, /*per_way_x2*/ 5, /*min_gain*/ 3);
-  LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<(OUT_F32 ? EPI_F32 : EPI_E4M3)>, dim3(2 * plan.pairs), dim3(THREADS), SMEM_BYTES, stream,
+  LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<EPI>, dim3(2 * plan.pairs), dim3(THREADS), SMEM_BYTES, stream,
                             2, tm_a, tm_b, A_s, B_s, C, C_s, M, N, K, plan.dp_tiles, plan.split_pairs, plan.split_s,
-                            plan.split_chunk, plan.partials, plan.counters, GatherDst{}, info->status));
+                            plan.split_chunk, plan.partials, plan.counters, GatherDst{}, hook, info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
+}
+
+template<bool OUT_F32>
+static int launch_fp8_pair(const void* A, const float* A_s, const void* B, const float* B_s, void* C, float* C_s, int M,
+                           int N, int K, const DeviceInfo* info, cudaStream_t stream)
+{
+  return launch_fp8_pair_epi<(OUT_F32 ? EPI_F32 : EPI_E4M3)>(A, A_s, B, B_s, C, C_s, M, N, K, RopeHook{}, info, stream);
 }
 
 // gate_up GEMM with the SwiGLU epilogue: B [2I, K], B_s [2I/128, K/128], H_q [M, I], H_s [I/128, M].
@@ -1000,7 +1107,7 @@ static int launch_fp8_swiglu(const void*       A,
   uint32_t* no_counters = nullptr;
   LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<EPI_SWIGLU>, dim3(2 * pairs), dim3(THREADS), SMEM_BYTES, stream, 2,
                             tm_a, tm_b, A_s, B_s, H, H_s, M, I, K, tiles, 0, 1, K / BK, no_partials, no_counters,
-                            GatherDst{}, info->status));
+                            GatherDst{}, RopeHook{}, info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
 }
@@ -1034,7 +1141,7 @@ static int launch_fp8_gather(const void*       A,
   float*          none  = nullptr;
   LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<EPI_GATHER>, dim3(2 * plan.pairs), dim3(THREADS), SMEM_BYTES, stream, 2,
                             tm_a, tm_b, A_s, B_s, static_cast<void*>(nullptr), none, M, N, K, plan.dp_tiles, plan.split_pairs,
-                            plan.split_s, plan.split_chunk, plan.partials, plan.counters, dst, info->status));
+                            plan.split_s, plan.split_chunk, plan.partials, plan.counters, dst, RopeHook{}, info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
 }
@@ -1117,6 +1224,7 @@ int warm_fp8_kernels(const DeviceInfo* info)
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8cfg::SMEM_BYTES));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8cfg::SMEM_BYTES));
   return warm_decode_kernels(info);
@@ -1297,6 +1405,85 @@ int llmmm_fp8_blockwise_mm_swiglu_e4m3out(const void*    A,
     return set_error(LLMMM_ERR_UNSUPPORTED, "this device cannot hold a cluster of two CTAs of the GEMM kernel");
   }
   return launch_fp8_swiglu(A, A_scale_t, B_gate_up_t, B_scale_t, H, H_scale_t, M, I, K, info, s);
+}
+
+int llmmm_fp8_blockwise_mm_qk_norm_rope_e4m3out(const void*    A,
+                                                const float*   A_scale_t,
+                                                const void*    B_t,
+                                                const float*   B_scale_t,
+                                                void*          C,
+                                                float*         C_scale_t,
+                                                const int*     positions,
+                                                const float*   cos_table,
+                                                const float*   sin_table,
+                                                const float*   q_norm_weight,
+                                                const float*   k_norm_weight,
+                                                float          eps,
+                                                int            n_q_heads,
+                                                int            n_kv_heads,
+                                                int            M,
+                                                int            N,
+                                                int            K,
+                                                llmmm_stream_t stream)
+{
+  using namespace llmmm;
+  if (A == nullptr || A_scale_t == nullptr || B_t == nullptr || B_scale_t == nullptr || C == nullptr || C_scale_t == nullptr
+      || positions == nullptr || cos_table == nullptr || sin_table == nullptr) {
+    return set_error(LLMMM_ERR_SHAPE, "null pointer argument");
+  }
+  if (M < 1 || N < 128 || K < 128 || (N % 128) != 0 || (K % 128) != 0) {
+    return set_error(LLMMM_ERR_SHAPE, "M or N or K are not aligned. (need M>=1, N%%128==0, K%%128==0; got %d %d %d)", M, N, K);
+  }
+  if (n_q_heads < 0 || n_kv_heads < 0 || (long long)(n_q_heads + 2LL * n_kv_heads) * 128 != N) {
+    return set_error(LLMMM_ERR_SHAPE, "N must be (n_q_heads + 2 n_kv_heads) * 128 (got N=%d, %d query and %d key/value heads)", N,
+                     n_q_heads, n_kv_heads);
+  }
+  if (((uintptr_t)A | (uintptr_t)B_t | (uintptr_t)C | (uintptr_t)cos_table | (uintptr_t)sin_table | (uintptr_t)q_norm_weight
+       | (uintptr_t)k_norm_weight)
+      & 15) {
+    return set_error(LLMMM_ERR_SHAPE, "A, B, C, the angle tables and the norm weights must be 16-byte aligned");
+  }
+  if (!(eps >= 0.0f)) {
+    return set_error(LLMMM_ERR_SHAPE, "eps must be non-negative");
+  }
+  const DeviceInfo* info = device_info();
+  if (info == nullptr) {
+    return LLMMM_ERR_UNSUPPORTED;
+  }
+  const RopeHook hook{cos_table, sin_table, positions, q_norm_weight, k_norm_weight, eps, n_q_heads, n_kv_heads, 0};
+  cudaStream_t   s = reinterpret_cast<cudaStream_t>(stream);
+  if (M <= 64) {
+    // Decode-sized: the weight-streaming decode kernel leaves the [M, N] accumulator in the registered scratch
+    // (behind its own partial tiles) and a second, tiny kernel applies the hook and quantises.  Without enough
+    // scratch the 256-row kernel below runs (correct, but it reads the weights at a fraction of the rate).
+    const Workspace ws  = registered_workspace(info->device);
+    const size_t    off = (decode_workspace_bytes(M) + 255) & ~size_t(255);
+    if (ws.ptr != nullptr && ws.bytes >= off + (size_t)M * N * sizeof(float)) {
+      float*    acc = reinterpret_cast<float*>(static_cast<uint8_t*>(ws.ptr) + off);
+      const int rc  = launch_decode(true, A, A_scale_t, B_t, B_scale_t, acc, nullptr, M, N, K, s);
+      if (rc == LLMMM_OK) {
+        return launch_rope_quant(acc, C, C_scale_t, hook, M, N, s);
+      }
+      if (rc > 0) {
+        return rc;
+      }
+    }
+  }
+  if (info->max_pairs < 1) {
+    return set_error(LLMMM_ERR_UNSUPPORTED, "this device cannot hold a cluster of two CTAs of the GEMM kernel");
+  }
+  return launch_fp8_pair_epi<EPI_ROPE>(A, A_scale_t, B_t, B_scale_t, C, C_scale_t, M, N, K, hook, info, s);
+}
+
+size_t llmmm_fp8_qk_norm_rope_workspace_bytes(int M, int N, int K)
+{
+  if (M < 1 || N < 128) {
+    return 0;
+  }
+  if (M > 64) {
+    return llmmm_fp8_workspace_bytes(M, N, K);  // the last-wave split of the 256-row kernel
+  }
+  return ((llmmm::decode_workspace_bytes(M) + 255) & ~size_t(255)) + (size_t)M * N * sizeof(float);
 }
 
 size_t llmmm_fp8_swiglu_workspace_bytes(int M, int I, int K)

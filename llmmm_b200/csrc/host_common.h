@@ -81,6 +81,23 @@ size_t decode_workspace_bytes(int M);
 // decode-sized form of llmmm_fp8_blockwise_mm_swiglu_e4m3out.
 int launch_swiglu_quant(const float* acc, void* H, float* H_s, int M, int I, cudaStream_t stream);
 
+// What the qkv projection's epilogue hook needs: heads of 128 columns, first n_q query heads, then n_kv key heads,
+// the rest value heads.  Query and key heads are RMS-normalised over their 128 values (weights q_w / k_w; a null
+// pointer skips the normalisation for that kind) and rotated (pairs (i, i + 64), angle table row pos[m]); value
+// heads pass unchanged.
+struct RopeHook {
+  const float* cos;  // [positions, 64]
+  const float* sin;  // [positions, 64]
+  const int*   pos;  // [M]
+  const float* q_w;  // [128] or null
+  const float* k_w;  // [128] or null
+  float        eps;
+  int          n_q;
+  int          n_kv;
+  int          pad;
+};
+int launch_rope_quant(const float* acc, void* C, float* C_s, const RopeHook& hook, int M, int N, cudaStream_t stream);
+
 // What the launch heuristics choose for a problem, as text (llmmm_describe_plan), and the one-time set-up of
 // every kernel of a family on the current device (llmmm_tune): function attributes, occupancy queries.
 void describe_fp16_plan(const DeviceInfo* info, bool bf16, int M, int N, int K, char* buf, size_t len);

@@ -259,6 +259,74 @@ int launch_swiglu_quant(const float* acc, void* H, float* H_s, int M, int I, cud
   return LLMMM_OK;
 }
 
+// The qkv hook (per-head RMSNorm of query / key heads, rotary embedding, 1x128 quantisation) applied to an fp32
+// accumulator [M, N] that a decode-sized GEMM left in scratch: one warp per (row, head); lane l holds columns
+// 2l, 2l+1 and 64+2l, 64+2l+1, i.e. two rotation pairs.  Same arithmetic as the fused epilogue of the
+// prefill-sized kernel up to the order of the sum of squares.
+__global__ void __launch_bounds__(256)
+  rope_quant_1x128_kernel(const float* __restrict__ acc, uint8_t* __restrict__ C, float* __restrict__ C_s,
+                          const __grid_constant__ RopeHook hook, int M, int N)
+{
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane  = threadIdx.x & 31;
+  const int heads = N / 128;
+  const int w     = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (w >= M * heads) {
+    return;
+  }
+  const int    m = w / heads, h = w % heads;
+  const float* row = acc + (size_t)m * N + (size_t)h * 128;
+  float2       lo  = __ldcs(reinterpret_cast<const float2*>(row) + lane);
+  float2       hi  = __ldcs(reinterpret_cast<const float2*>(row + 64) + lane);
+  const int    kind = h < hook.n_q ? 0 : (h < hook.n_q + hook.n_kv ? 1 : 2);
+  if (kind < 2) {
+    const float* wgt = kind == 0 ? hook.q_w : hook.k_w;
+    if (wgt != nullptr) {
+      float ss = fmaf(lo.x, lo.x, fmaf(lo.y, lo.y, fmaf(hi.x, hi.x, hi.y * hi.y)));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      }
+      const float  inv = __frcp_rn(__fsqrt_rn(fmaf(ss, 1.0f / 128.0f, hook.eps)));
+      const float2 wl  = __ldg(reinterpret_cast<const float2*>(wgt) + lane);
+      const float2 wh  = __ldg(reinterpret_cast<const float2*>(wgt + 64) + lane);
+      lo.x = lo.x * inv * wl.x;
+      lo.y = lo.y * inv * wl.y;
+      hi.x = hi.x * inv * wh.x;
+      hi.y = hi.y * inv * wh.y;
+    }
+    const size_t p = (size_t)__ldg(hook.pos + m) * 64;
+    const float2 c = __ldg(reinterpret_cast<const float2*>(hook.cos + p) + lane);
+    const float2 s = __ldg(reinterpret_cast<const float2*>(hook.sin + p) + lane);
+    const float2 l0 = lo, h0 = hi;
+    lo.x = __fmaf_rn(l0.x, c.x, -__fmul_rn(h0.x, s.x));
+    lo.y = __fmaf_rn(l0.y, c.y, -__fmul_rn(h0.y, s.y));
+    hi.x = __fmaf_rn(h0.x, c.x, __fmul_rn(l0.x, s.x));
+    hi.y = __fmaf_rn(h0.y, c.y, __fmul_rn(l0.y, s.y));
+  }
+  const float amax  = warp_max(fmaxf(fmaxf(fabsf(lo.x), fabsf(lo.y)), fmaxf(fabsf(hi.x), fabsf(hi.y))));
+  const float scale = __fdiv_rn(amax, 448.0f);
+  const float inv   = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 0.0f;
+  uint8_t*    dst   = C + (size_t)m * N + (size_t)h * 128;
+  reinterpret_cast<uint16_t*>(dst)[lane] =
+    (uint16_t)__nv_cvt_float2_to_fp8x2(make_float2(lo.x * inv, lo.y * inv), __NV_SATFINITE, __NV_E4M3);
+  reinterpret_cast<uint16_t*>(dst + 64)[lane] =
+    (uint16_t)__nv_cvt_float2_to_fp8x2(make_float2(hi.x * inv, hi.y * inv), __NV_SATFINITE, __NV_E4M3);
+  if (lane == 0) {
+    C_s[(size_t)h * M + m] = scale;
+  }
+}
+
+int launch_rope_quant(const float* acc, void* C, float* C_s, const RopeHook& hook, int M, int N, cudaStream_t stream)
+{
+  const int warps = M * (N / 128);
+  LLMMM_CUDA_TRY(launch_pdl(rope_quant_1x128_kernel, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, stream, 1, acc,
+                            static_cast<uint8_t*>(C), C_s, hook, M, N));
+  g_launches.fetch_add(1);
+  return LLMMM_OK;
+}
+
 }  // namespace llmmm
 
 extern "C" {

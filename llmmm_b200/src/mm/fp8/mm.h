@@ -64,6 +64,33 @@ inline void fp8_gemm_blockwise_quant_A_1x128__B_128x128__swiglu__C_1x128__output
     A, A_scale_transposed, B_transposed, B_scale_transposed, C, C_scale_transposed, M, I, K, stream));
 }
 
+// The other planned fusion (README.md:16: norm / rope): the qkv projection with heads of 128 columns (query heads,
+// then key heads, then value heads); query and key heads are RMS-normalised per head (a null weight skips it) and
+// rotated by the angle-table row positions[m] (pairs (i, i + 64)) before the 1x128 quantisation.
+inline void fp8_gemm_blockwise_quant_A_1x128__B_128x128__qk_norm_rope__C_1x128__output_fp8(const __nv_fp8_e4m3* A,
+                                                                                           const float*         A_scale_transposed,
+                                                                                           const __nv_fp8_e4m3* B_transposed,
+                                                                                           const float*         B_scale_transposed,
+                                                                                           __nv_fp8_e4m3*       C,
+                                                                                           float*               C_scale_transposed,
+                                                                                           const int*           positions,
+                                                                                           const float*         cos_table,
+                                                                                           const float*         sin_table,
+                                                                                           const float*         q_norm_weight,
+                                                                                           const float*         k_norm_weight,
+                                                                                           float                eps,
+                                                                                           int                  n_q_heads,
+                                                                                           int                  n_kv_heads,
+                                                                                           int                  M,
+                                                                                           int                  N,
+                                                                                           int                  K,
+                                                                                           cudaStream_t         stream)
+{
+  LLMMM::throw_on_error(llmmm_fp8_blockwise_mm_qk_norm_rope_e4m3out(
+    A, A_scale_transposed, B_transposed, B_scale_transposed, C, C_scale_transposed, positions, cos_table, sin_table,
+    q_norm_weight, k_norm_weight, eps, n_q_heads, n_kv_heads, M, N, K, stream));
+}
+
 inline void fp8_gemm_blockwise_quant_A_1x128__B_128x128__output_fp32(const __nv_fp8_e4m3* A,
                                                                      const float*         A_scale_transposed,
                                                                      const __nv_fp8_e4m3* B_transposed,

@@ -272,6 +272,43 @@ def fp8_blockwise_mm_swiglu(A_q, A_s, B_q, B_s, row0: int = 0, rows: int | None 
     return q, s, h32, h64
 
 
+def qk_norm_rope(acc: np.ndarray, positions, cos, sin, q_weight, k_weight, eps: float, n_q: int, n_kv: int) -> np.ndarray:
+    """The qkv hook on an accumulator [M, (n_q + 2 n_kv) * 128], heads of 128 columns (query, key, value):
+    query / key heads are RMS-normalised over their 128 values when the weight of their kind is given
+    (x * (1 / sqrt(mean(x^2) + eps)) * w) and rotated: y[i] = x[i] cos[p, i] - x[i+64] sin[p, i],
+    y[i+64] = x[i+64] cos[p, i] + x[i] sin[p, i], p = positions[m]; value heads pass unchanged.  Computed in the
+    dtype of `acc` (fp32: the kernel's arithmetic up to the sum of squares' order and the reciprocal square
+    root's last bits; fp64: ground truth).  The reference only plans "norm/rope fusion" (README.md:16); this is
+    the usual definition with the half-split pairing."""
+    t = acc.dtype.type
+    M, N = acc.shape
+    x = acc.reshape(M, N // 128, 128).copy()
+    c = np.asarray(cos)[np.asarray(positions)].astype(acc.dtype)[:, None, :]  # [M, 1, 64]
+    s = np.asarray(sin)[np.asarray(positions)].astype(acc.dtype)[:, None, :]
+    for lo, hi, w in ((0, n_q, q_weight), (n_q, n_q + n_kv, k_weight)):
+        h = x[:, lo:hi]
+        if w is not None:
+            ms = (h.astype(np.float64) ** 2).sum(axis=2, keepdims=True).astype(acc.dtype) / t(128)
+            inv = (t(1) / np.sqrt(ms + t(eps), dtype=acc.dtype)).astype(acc.dtype)
+            h = ((h * inv).astype(acc.dtype) * np.asarray(w).astype(acc.dtype)).astype(acc.dtype)
+        x0, x1 = h[..., :64], h[..., 64:]
+        x[:, lo:hi] = np.concatenate([x0 * c - x1 * s, x1 * c + x0 * s], axis=2).astype(acc.dtype)
+    return x.reshape(M, N)
+
+
+def fp8_blockwise_mm_qk_norm_rope(A_q, A_s, B_q, B_s, positions, cos, sin, q_weight, k_weight, eps, n_q, n_kv,
+                                  row0: int = 0, rows: int | None = None):
+    """qkv GEMM + hook + 1x128 quantisation: (C_q, C_s, y_f32, y_f64_truth) for rows [row0, row0 + rows)."""
+    n = A_q.shape[0] - row0 if rows is None else rows
+    pos = np.asarray(positions)[row0:row0 + n]
+    y32 = qk_norm_rope(fp8_blockwise_acc(A_q, A_s, B_q, B_s, row0=row0, rows=rows), pos, cos, sin, q_weight, k_weight,
+                       eps, n_q, n_kv)
+    y64 = qk_norm_rope(fp8_blockwise_acc(A_q, A_s, B_q, B_s, exact=True, row0=row0, rows=rows), pos, cos, sin,
+                       q_weight, k_weight, eps, n_q, n_kv)
+    q, s = c_quant_1x128(y32)
+    return q, s, y32, y64
+
+
 def transpose(x: np.ndarray) -> np.ndarray:
     """src/base/base.cu:125-152 for 1- and 4-byte elements."""
     x = np.ascontiguousarray(x)

@@ -140,3 +140,37 @@ def test_transpose(oracle):
     a = rng.integers(0, 255, (128, 256), dtype=np.uint8)
     f = rng.standard_normal((128, 256)).astype(np.float32)
     assert (oracle.transpose(a) == a.T).all() and (oracle.transpose(f) == f.T).all()
+
+
+def test_qk_norm_rope_against_torch(oracle):
+    # the hook's restatement against an independent torch formulation (rotate-half rotary embedding, RMSNorm
+    # over the head), in fp64; properties: value heads untouched, the rotation keeps each head's norm
+    import torch
+    rng = np.random.default_rng(3)
+    M, n_q, n_kv = 5, 3, 2
+    acc = rng.standard_normal((M, (n_q + 2 * n_kv) * 128))
+    pos = np.array([0, 7, 3, 100, 7], np.int32)
+    ang = np.arange(128, dtype=np.float64)[:, None] / (1e4 ** (np.arange(64) / 64))[None, :]
+    cos, sin = np.cos(ang), np.sin(ang)
+    q_w, k_w = 1 + 0.1 * rng.standard_normal(128), 1 + 0.1 * rng.standard_normal(128)
+    got = oracle.qk_norm_rope(acc, pos, cos, sin, q_w, k_w, 1e-6, n_q, n_kv)
+
+    x = torch.from_numpy(acc).view(M, n_q + 2 * n_kv, 128)
+    c = torch.from_numpy(np.concatenate([cos, cos], 1))[torch.from_numpy(pos).long()][:, None, :]
+    s = torch.from_numpy(np.concatenate([sin, sin], 1))[torch.from_numpy(pos).long()][:, None, :]
+
+    def hook(h, w):
+        h = h * torch.rsqrt((h * h).mean(-1, keepdim=True) + 1e-6) * torch.from_numpy(w)
+        rot = torch.cat([-h[..., 64:], h[..., :64]], -1)
+        return h * c + rot * s
+
+    want = torch.cat([hook(x[:, :n_q], q_w), hook(x[:, n_q:n_q + n_kv], k_w), x[:, n_q + n_kv:]], 1).reshape(M, -1).numpy()
+    assert np.abs(got - want).max() < 1e-12
+    assert (got[:, (n_q + n_kv) * 128:] == acc[:, (n_q + n_kv) * 128:]).all()
+    plain = oracle.qk_norm_rope(acc, pos, cos, sin, None, None, 1e-6, n_q, n_kv)
+    n0 = np.linalg.norm(acc.reshape(M, -1, 128), axis=2)
+    assert np.abs(np.linalg.norm(plain.reshape(M, -1, 128), axis=2) - n0).max() < 1e-12
+    # the fp32 form stays within fp32 rounding of the fp64 one
+    got32 = oracle.qk_norm_rope(acc.astype(np.float32), pos, cos.astype(np.float32), sin.astype(np.float32),
+                                q_w.astype(np.float32), k_w.astype(np.float32), 1e-6, n_q, n_kv)
+    assert got32.dtype == np.float32 and np.abs(got32 - got).max() < 5e-6
