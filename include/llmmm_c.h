@@ -142,7 +142,7 @@ size_t llmmm_fp8_swiglu_workspace_bytes(int M, int I, int K);
  *   C_scale_t [(N/128), M] by the same rule as C above.
  *   positions [M] int32 (rows of the angle tables), cos_table / sin_table [rows, 64] fp32, weights [128] fp32.
  * Requires K%128 == 0, any M >= 1; tables, weights, A, B_t and C 16-byte aligned.  M > 64 runs one fused kernel
- * (256-row tiles; a partly filled last wave is cut along K when scratch is registered).  M <= 64 runs the
+ * (256-row tiles, always whole: registered scratch is not used).  M <= 64 runs the
  * weight-streaming decode kernel into scratch followed by a small kernel, provided the registered scratch has
  * llmmm_fp8_qk_norm_rope_workspace_bytes(M, N, K) bytes; otherwise the 256-row kernel runs for small M too. */
 int llmmm_fp8_blockwise_mm_qk_norm_rope_e4m3out(const void*    A,

@@ -179,7 +179,7 @@ def fp8_blockwise_mm_qk_norm_rope(A_q, A_s, B_q, B_s, C_q, C_s, positions, cos, 
 
 
 def ensure_qk_norm_rope_workspace(M: int, N: int, K: int, device=None) -> None:
-    """Scratch for fp8_blockwise_mm_qk_norm_rope (decode-sized: accumulator; larger: the last-wave split)."""
+    """Scratch for the decode-sized (M <= 64) form of fp8_blockwise_mm_qk_norm_rope; larger M needs none."""
     ensure_workspace_bytes(int(lib().llmmm_fp8_qk_norm_rope_workspace_bytes(M, N, K)), device)
 
 

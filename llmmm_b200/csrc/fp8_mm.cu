@@ -1059,7 +1059,11 @@ static int launch_fp8_pair_epi(const void*       A,
   const int k_blocks = K / BK;
   // estimated cost of a split, in K-blocks (one takes about 0.58 us): publishing a chunk and counting the
   // arrival about 3 us, reading a chunk back about 1.5 us
-  const SplitPlan plan = plan_split(info, tiles, k_blocks, /*fixed*/ 4, /*per_way_x2*/ 5, /*min_gain*/ 3);
+  SplitPlan plan = plan_split(info, tiles, k_blocks, /*fixed*/ 4, /*per_way_x2*/ 5, /*min_gain*/ 3, /*count*/ EPI != EPI_ROPE);
+  if constexpr (EPI == EPI_ROPE) {
+    // whole tiles only: this instantiation has no code for the chunks of a cut tile (no register left for it)
+    plan = SplitPlan{tiles, 0, 1, k_blocks, tiles < info->max_pairs ? tiles : info->max_pairs, nullptr, nullptr};
+  }
   LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<EPI>, dim3(2 * plan.pairs), dim3(THREADS), SMEM_BYTES, stream,
                             2, tm_a, tm_b, A_s, B_s, C, C_s, M, N, K, plan.dp_tiles, plan.split_pairs, plan.split_s,
                             plan.split_chunk, plan.partials, plan.counters, GatherDst{}, hook, info->status));
@@ -1480,8 +1484,9 @@ size_t llmmm_fp8_qk_norm_rope_workspace_bytes(int M, int N, int K)
   if (M < 1 || N < 128) {
     return 0;
   }
+  (void)K;
   if (M > 64) {
-    return llmmm_fp8_workspace_bytes(M, N, K);  // the last-wave split of the 256-row kernel
+    return 0;  // the fused kernel runs whole tiles and needs no scratch
   }
   return ((llmmm::decode_workspace_bytes(M) + 255) & ~size_t(255)) + (size_t)M * N * sizeof(float);
 }

@@ -101,16 +101,33 @@ def test_identity_angles_without_weights_equal_the_plain_gemm(capi, oracle, cuda
     assert (gq == pq).all() and (gs == ps).all()
 
 
+def test_registered_scratch_does_not_cut_tiles(capi, oracle, cuda):
+    # few tiles with a long K: the plain GEMM cuts them along K when scratch is registered, the hooked kernel
+    # keeps whole tiles (it has no code for chunks) and gives the same bytes with and without scratch
+    c = make_case(oracle, 74, 300, 2, 1, 4096)
+    capi.clear_workspace()
+    gq, gs = run(capi, cuda, c)
+    check(oracle, c, gq, gs)
+    capi.ensure_workspace(c["M"], c["N"], c["K"])
+    n0 = capi.split_launch_count()
+    plain(capi, cuda, c)
+    assert capi.split_launch_count() == n0 + 1
+    gq2, gs2 = run(capi, cuda, c)
+    assert capi.split_launch_count() == n0 + 1
+    assert (gq2 == gq).all() and (gs2 == gs).all()
+
+
 def test_qwen3_4b_qkv_prefill(capi, oracle, cuda):
     # 32 query + 8 key + 8 value heads of 128 over hidden size 2560, with and without registered scratch
+    # (which this kernel does not use)
     c = make_case(oracle, 72, 1024, 32, 8, 2560)
     capi.clear_workspace()
     gq, gs = run(capi, cuda, c)
     check(oracle, c, gq, gs, rows=(1016, 8))
     check(oracle, c, gq, gs, rows=(301, 4))
-    capi.ensure_qk_norm_rope_workspace(c["M"], c["N"], c["K"])
+    capi.ensure_workspace(c["M"], c["N"], c["K"])
     gq2, gs2 = run(capi, cuda, c)
-    check(oracle, c, gq2, gs2, rows=(1016, 8))
+    assert (gq2 == gq).all() and (gs2 == gs).all()
     gq3, gs3 = run(capi, cuda, c)
     assert (gq2 == gq3).all() and (gs2 == gs3).all()  # bitwise stable from call to call
 
