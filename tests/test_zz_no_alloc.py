@@ -5,7 +5,11 @@ library instead of a caller-owned workspace.  Both entry points must therefore
 agree bit for bit (this path is integer/byte output with IEEE-derived scales;
 the other FP8 tests use no looser tolerance for kernel-vs-kernel comparisons),
 on two calls in a row, since the second call meets the scratch the first one
-left behind.  Collected last on purpose (file name), runs alone as well."""
+left behind.  The shapes are chosen so that most of them really take the
+stream-K kernel (the one that publishes partial tiles and counts arrivals in
+the built-in array) rather than the cluster kernel, which needs no scratch;
+the test asserts which one runs.  Collected last on purpose (file name), runs
+alone as well."""
 import numpy as np
 import pytest
 import torch
@@ -22,12 +26,28 @@ def make_inputs(oracle, cuda, seed, M, N, K):
     return [torch.from_numpy(a).to(cuda) for a in (A_q, A_s, B_q, B_s)]
 
 
-@pytest.mark.parametrize("shape", [(1, 2560, 4096), (16, 6144, 2560), (5, 384, 128)])
+# (M, N, K, kernel the launch heuristics must pick).  Order matters: the wide gate_up shape runs first and leaves
+# partial tiles and (zeroed) counters behind for the narrower ones that follow.
+SHAPES = [
+    (1, 19456, 2560, "stream-K"),   # 152 output groups: more than the SMs, no cluster size fits
+    (16, 1280, 4096, "stream-K"),   # 10 groups: clusters of 7 would leave half of the SMs idle
+    (4, 384, 4096, "stream-K"),     # 96 weight blocks on 96 CTAs: 32 contributors per output group
+    (13, 19456, 2560, "stream-K"),  # ragged M
+    (1, 2560, 4096, "cluster"),     # takes no scratch at all
+    (16, 6144, 2560, "cluster"),
+    (5, 384, 128, "stream-K"),      # one K-block: every segment is whole, nothing is published
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: f"{s[0]}x{s[1]}x{s[2]}")
 def test_noalloc_matches_workspace_entry_point_twice(capi, oracle, cuda, shape):
-    M, N, K = shape
+    M, N, K, kernel = shape
     first = make_inputs(oracle, cuda, 90, M, N, K)
     second = make_inputs(oracle, cuda, 91, M, N, K)
     capi.ensure_workspace(M, N, K)
+    # both entry points make the same choice between the cluster and the stream-K kernel; the plan text of the
+    # regular entry (with its workspace registered) names it
+    assert kernel in capi.describe_plan("fp8", M, N, K)
     for A_q, A_s, B_q, B_s in (first, second):
         ref_q = torch.full((M, N), 0xAA, dtype=torch.uint8, device=cuda)
         ref_s = torch.full((N // 128, M), float("nan"), device=cuda)
