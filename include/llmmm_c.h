@@ -214,9 +214,12 @@ int llmmm_transpose_aligned_128(void* dst, const void* src, int M, int N, int el
  * (results are bitwise stable from call to call, and differ from the unsplit
  * ones only by the association of fp32 sums).  llmmm_fp8_workspace_bytes gives
  * the size for an FP8 problem; for FP16/BF16 pass the same M (any N, K >= 128).
- * Without registered scratch every shape still runs, unsplit.  The buffer is
- * shared by all later calls on that device; calls that may overlap on the GPU
- * need separate streams AND separate buffers, or must be serialised. */
+ * Without registered scratch every shape still runs, unsplit.  llmmm_set_workspace
+ * clears the parts of the buffer that must be zero between launches (it
+ * synchronises; register once, outside the token loop); every launch leaves them
+ * zero again.  One buffer per device serves all later calls on that device, so
+ * calls that use the registered scratch must be serialised per device (one
+ * stream, or events between streams). */
 size_t llmmm_fp8_workspace_bytes(int M, int N, int K);
 int    llmmm_set_workspace(void* device_ptr, size_t bytes);
 
@@ -234,14 +237,15 @@ int llmmm_set_static_weights(int enabled);
  * servers whose own pool already holds all of device memory, and token loops
  * that must never reach cudaMalloc/cudaFree because those calls synchronise the
  * device.  Same arguments and results as llmmm_fp8_blockwise_mm_e4m3out, but the
- * split-K scratch is a fixed 4,210,688-byte array inside the library image (held
+ * split-K scratch is a fixed 2,621,440-byte array inside the library image (held
  * by every GPU that loads the library until the process exits), so:
  *   - 1 <= M <= 16 and N <= 524288 only; anything larger returns
  *     LLMMM_ERR_SHAPE with a message naming the limit;
  *   - no call allocates or frees anything; the first call on a device looks up
  *     the array's device address (make that first call outside stream capture);
- *   - all calls on a device share the one array: two calls whose kernels can
- *     overlap on the GPU (different streams) race; serialise them. */
+ *   - all calls on a device share the one array, which every completed call
+ *     leaves all zero again: two calls whose kernels can overlap on the GPU
+ *     (different streams) race; serialise them. */
 int llmmm_fp8_blockwise_mm_e4m3out_noalloc(const void*    A,
                                            const float*   A_scale_t,
                                            const void*    B_t,

@@ -1,6 +1,11 @@
 """Builds libllmmm_b200.so (the C-ABI library) in-tree with nvcc for sm_100a.
 
-Usage: python -m llmmm_b200.build [--force] [--verbose]
+Usage: python -m llmmm_b200.build [--force] [--verbose] [--profile]
+
+--profile builds a second library, libllmmm_b200_profile.so, from the same sources with -DLLMMM_PROFILE: the
+kernels then record %globaltimer / clock64 stamps at their hand-off points and the library exports
+llmmm_profile_dump_* functions that print them (load that library instead of the regular one, run the shape,
+call the dump function).  The regular library contains none of this.
 """
 from __future__ import annotations
 
@@ -14,6 +19,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OBJ = PKG / "build"
 LIB = PKG / "libllmmm_b200.so"
+PROFILE_LIB = PKG / "libllmmm_b200_profile.so"
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -49,20 +55,23 @@ def _newer(target: Path, deps: list[Path]) -> bool:
     return all(d.stat().st_mtime <= t for d in deps)
 
 
-def build_library(force: bool = False, verbose: bool = False) -> Path:
+def build_library(force: bool = False, verbose: bool = False, profile: bool = False) -> Path:
     sources = sorted(CSRC.glob("*.cu"))
     headers = sorted(CSRC.glob("*.h")) + sorted(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "llmmm_c.h"]
-    OBJ.mkdir(exist_ok=True)
+    obj_dir = OBJ / "profile" if profile else OBJ
+    lib = PROFILE_LIB if profile else LIB
+    flags = FLAGS + (["-DLLMMM_PROFILE"] if profile else [])
+    obj_dir.mkdir(parents=True, exist_ok=True)
 
     def compile_one(src: Path) -> tuple[Path, str]:
-        obj = OBJ / (src.stem + ".o")
+        obj = obj_dir / (src.stem + ".o")
         if not force and _newer(obj, [src] + headers):
             return obj, ""
-        cmd = [NVCC, *FLAGS, "-c", str(src), "-o", str(obj)]
+        cmd = [NVCC, *flags, "-c", str(src), "-o", str(obj)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stdout}\n{r.stderr}")
-        spilled = spilling_kernels(r.stderr, NO_SPILL)
+        spilled = [] if profile else spilling_kernels(r.stderr, NO_SPILL)
         if spilled:
             obj.unlink(missing_ok=True)
             raise RuntimeError(f"{src.name}: ptxas spilled registers in {spilled}; these kernels lose a third of their "
@@ -76,13 +85,13 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
         for _, log in results:
             if log:
                 sys.stderr.write(log)
-    if force or not _newer(LIB, objs):
-        cmd = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB), *map(str, objs), "-lcudart"]
+    if force or not _newer(lib, objs):
+        cmd = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(lib), *map(str, objs), "-lcudart"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
-    print(build_library(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_library(force="--force" in sys.argv, verbose="--verbose" in sys.argv, profile="--profile" in sys.argv))

@@ -10,6 +10,9 @@
 
 namespace llmmm {
 
+std::atomic<int> g_scratch_dirty[64];
+std::atomic<int> g_noalloc_dirty[64];
+
 namespace {
 
 thread_local char g_error[512] = "";
@@ -326,6 +329,8 @@ int llmmm_check_status(llmmm_stream_t stream)
   LLMMM_CUDA_TRY(cudaMemcpy(&word, info->status, sizeof(word), cudaMemcpyDeviceToHost));
   if (word != 0) {
     cudaMemset(info->status, 0, sizeof(word));
+    llmmm::g_scratch_dirty[info->device].store(1);
+    llmmm::g_noalloc_dirty[info->device].store(1);
     return llmmm::set_error(LLMMM_ERR_DEVICE_WAIT, "a device-side wait ran out, code 0x%x", word);
   }
   return LLMMM_OK;

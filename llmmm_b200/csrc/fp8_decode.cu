@@ -13,16 +13,25 @@
 //     contiguous run per CTA, so all SMs stream the same number of bytes
 //     whatever N is; a run crosses output groups, giving "segments";
 //   * warp 0 streams weight blocks (and the matching activation slab) through
-//     an 8-deep TMA ring, warp 1 issues four MMAs per K-block from zero into
-//     one of two TMEM partial stages, warps 2-5 promote with
-//     acc = fma(partial, A_s*B_s, acc) in registers;
+//     a 4-6-deep TMA ring; warps 1-3 take turns issuing the MMAs of a K-block
+//     (four per K-block, from zero, into the tensor-memory partial stage of the
+//     ring slot): a thread that issues four MMAs and a commit is held for about
+//     640 clk whatever their width, so one thread alone could not keep up with
+//     the ring; warps 4-7 promote
+//     with acc = fma(partial, A_s*B_s, acc) in registers, the scale products of
+//     a whole run staged through shared memory ahead of time (a load per
+//     K-block would put an L2 round trip into every iteration);
 //   * a segment that covers a group's whole K range is finished in place;
-//     otherwise its fp32 partial goes to the caller's scratch buffer and the
-//     last CTA to arrive at the group's counter (no CTA ever waits for another)
-//     adds the partials in fixed CTA order, so results do not depend on timing;
+//     otherwise its fp32 partial goes to the caller's scratch buffer as
+//     self-announcing words (zero = not there yet), and the rows of the output group are shared out
+//     among the contributors' warps (a reduce-scatter: one warp polls one
+//     row's words of every contributor, adds them in fixed CTA order, takes the
+//     absmax, quantises and stores the row), so results do not depend on timing,
+//     no single CTA reads every partial tile, and the exchange costs one store
+//     and one load latency instead of store + fence + atomic + poll + load;
 //   * the 1x128 output group runs across the 128 lanes in this orientation:
-//     the group absmax is a warp-shuffle reduction plus a 4-entry exchange in
-//     shared memory between the four warps.
+//     for a whole segment the group absmax is a warp-shuffle reduction plus a
+//     4-entry exchange in shared memory between the four warps.
 #include <cuda_fp8.h>
 #include <mutex>
 
@@ -35,11 +44,13 @@ namespace deccfg {
 constexpr int      BK            = 128;
 constexpr int      UMMA_K        = 32;
 constexpr int      MAX_STAGES    = 6;    // the ring depth depends on the activation tile, see DecodeSmem
-constexpr int      THREADS       = 192;
+constexpr int      THREADS       = 256;  // warps 0-3: producer, three MMA issuers; warps 4-7: promotion
+constexpr int      EPI_WARP0     = 4;    // first promotion warp (setmaxnreg acts on whole warpgroups of 4 warps)
+constexpr int      REGS_CTRL     = 56;   // the control warpgroup gives up 72 of its 128 registers per thread ...
+constexpr int      REGS_EPI      = 200;  // ... and the promotion warpgroup takes them
 constexpr uint32_t W_BYTES       = 128 * BK;
-constexpr int      MAX_CTAS      = 256;
-constexpr int      MAX_GROUPS    = 4096;                 // counters: N <= 524288
-constexpr size_t   COUNTER_BYTES = MAX_GROUPS * sizeof(uint32_t);
+constexpr int      MAX_CTAS      = 160;  // grid of the stream-K kernel: one CTA per SM, at most this many
+constexpr int      MAX_GROUPS    = 4096; // N <= 524288
 constexpr uint32_t TMEM_COLS     = 256;  // one partial stage per ring stage (see DecodeSmem), two CTAs per SM
 }  // namespace deccfg
 
@@ -57,9 +68,17 @@ struct DecodeSmem {
   static constexpr uint32_t OFF_W      = 0;
   static constexpr uint32_t OFF_X      = STAGES * deccfg::W_BYTES;
   static constexpr uint32_t OFF_BAR    = OFF_X + STAGES * X_BYTES;
+  // cluster kernel: a CTA owns every c-th row of its group and receives c partials of each in its idle weight
+  // ring, c * ceil(MP / c) rows of 512 bytes
+  static_assert((MP + 8) * 512 <= STAGES * deccfg::W_BYTES, "received partial rows must fit into the idle ring");
+  // scale products A_s[kb, m] * B_s[nb, kb] of CHUNK consecutive K-blocks of the CTA's run, [CHUNK][MP] fp32
+  static constexpr int      CHUNK      = MP <= 32 ? 32 : 16;
+  static constexpr uint32_t OFF_SC     = OFF_BAR + 1536;
+  static constexpr uint32_t SC_BYTES   = CHUNK * MP * 4;
   // at least 80 KB, so that never more than two CTAs share an SM: a third one would sit in tcgen05.alloc until
   // tensor memory is freed
-  static constexpr uint32_t USED_BYTES = OFF_BAR + 2048 + 1024;
+  static constexpr uint32_t USED_BYTES = OFF_SC + SC_BYTES + 1024;
+  static_assert(2 * (USED_BYTES + 1024) <= 228 * 1024, "two CTAs of consecutive launches must fit on one SM");
   static constexpr uint32_t SMEM_BYTES = USED_BYTES > 80 * 1024 ? USED_BYTES : 80 * 1024;
 };
 
@@ -69,27 +88,31 @@ struct DecodeBars {
   uint64_t part_empty[deccfg::MAX_STAGES];  // the 4 promotion warps have copied the partial out
   uint32_t tmem_base;
   uint32_t abort_flag;
-  uint32_t last_flag;
-  uint32_t pad;
+  uint32_t pad[2];
   float    amax[4][64];
   float    inv[64];
 };
+static_assert(sizeof(DecodeBars) <= 1536, "DecodeBars outgrew its slot in shared memory");
 
 #ifdef LLMMM_PROFILE
-// Debug build only: %globaltimer at the phases of CTA 0 (see llmmm_profile_dump_decode()).
-__device__ unsigned long long g_prof_dec[16];
-__device__ unsigned long long g_prof_cta[256][4];  // per CTA: entry, promotion loop done, fix-up done, exit
-__device__ unsigned long long g_prof_fin[256][6];  // last segment: published, counted, reduced, amax, stored
-__device__ unsigned long long g_prof_pdl[256][2];  // producer thread: before / after waiting for the previous kernel
-__device__ unsigned long long g_prof_set[256][4];  // set-up: barriers initialised, before / after tcgen05.alloc, after the CTA barrier
-#define PROFF(i) if (et == 0) g_prof_fin[blockIdx.x][i] = global_timer_ns()
+// Profiling build only: %globaltimer of every CTA at its phases (see llmmm_profile_dump_decode()).
+__device__ unsigned long long g_prof_cta[256][12];
+__device__ unsigned long long g_prof_kb[8][4];  // CTA 0, first promotion warp, K-blocks 0..7: waiting, partial seen, loaded, done
+#define PROF_KB(i)                                                                                                     \
+  do {                                                                                                                 \
+    if (blockIdx.x == 0 && threadIdx.x == deccfg::EPI_WARP0 * 32 && it < 8) {                                          \
+      g_prof_kb[it][i] = global_timer_ns();                                                                            \
+    }                                                                                                                  \
+  } while (0)
+#define PROF_CTA(i)                                                                                                    \
+  do {                                                                                                                 \
+    if ((threadIdx.x & 31) == 0) {                                                                                     \
+      g_prof_cta[blockIdx.x][i] = global_timer_ns();                                                                   \
+    }                                                                                                                  \
+  } while (0)
 #else
-#define PROFF(i)
-#endif
-#ifdef LLMMM_PROFILE
-#define PROFD(i) if (blockIdx.x == 0) g_prof_dec[i] = global_timer_ns()
-#else
-#define PROFD(i)
+#define PROF_CTA(i)
+#define PROF_KB(i)
 #endif
 
 __device__ __forceinline__ void epilogue_bar_sync()
@@ -104,12 +127,225 @@ __device__ __forceinline__ int cta_of_unit(uint32_t u, uint32_t G, uint32_t U)
   return (int)(((u + 1) * G - 1) / U);
 }
 
+// One output group that was cut among several CTAs, as seen by one promotion warp of a contributor.
+struct SplitGroup {
+  int  nb;     // output group
+  int  c_lo;   // first contributing CTA
+  int  cnt;    // contributors
+  int  gw;     // this warp's index among the 4 * cnt promotion warps of the contributors
+  bool mine;   // this warp owns at least one row of the group
+};
+
+// Partial tiles travel between CTAs as self-announcing 32-bit words: the scratch is all zero between launches,
+// a contributor stores its fp32 values in a code that is never zero, and a reader polls the words themselves
+// until none of those it needs is zero.  There is no separate "data is ready" signal and therefore no fence, no
+// atomic and no second round trip.  A reader puts the words it consumed back to zero.
+// Code: the value's bits with the sign flipped, so +0.0 (frequent) becomes 0x80000000; the one value that would
+// then be zero, -0.0 (a product that underflowed), takes the code of a NaN that arithmetic never produces.
+constexpr uint32_t PARTIAL_MINUS_ZERO = 0xffc00001u;
+
+__device__ __forceinline__ uint32_t encode_partial(float v)
+{
+  const uint32_t w = __float_as_uint(v) ^ 0x80000000u;
+  return w != 0u ? w : PARTIAL_MINUS_ZERO;
+}
+
+__device__ __forceinline__ float decode_partial(uint32_t w)
+{
+  return __uint_as_float(w != PARTIAL_MINUS_ZERO ? w ^ 0x80000000u : 0x80000000u);
+}
+
+__device__ __forceinline__ void st_partial(uint32_t* p, float v)
+{
+  asm volatile("st.relaxed.gpu.global.b32 [%0], %1;" ::"l"(p), "r"(encode_partial(v)) : "memory");
+}
+
+__device__ __forceinline__ uint4 ld_partial4(const uint32_t* p)
+{
+  uint4 v;
+  asm volatile("ld.relaxed.gpu.global.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+// One finished row of one 128-column output group, four columns per lane of one warp: fp32 as it is, or the
+// row's absmax (the bit pattern of a non-negative float orders like the float: one warp-wide integer max), the
+// two divisions of the quantisation rule, four e4m3 bytes per lane and the scale.
+template<bool OUT_F32>
+__device__ __forceinline__ void store_group_row(float4 s, int m, int nb, void* __restrict__ C_out, float* __restrict__ C_s,
+                                                int M, int N, int lane)
+{
+  if constexpr (OUT_F32) {
+    reinterpret_cast<float4*>(reinterpret_cast<float*>(C_out) + (size_t)m * N + (size_t)nb * 128)[lane] = s;
+  }
+  else {
+    const float    mine = fmaxf(fmaxf(fabsf(s.x), fabsf(s.y)), fmaxf(fabsf(s.z), fabsf(s.w)));
+    const float    amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(mine)));
+    const float    inv  = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 0.0f;
+    const uint32_t q    = pack_e4m3x4(s.x * inv, s.y * inv, s.z * inv, s.w * inv);
+    reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(C_out) + (size_t)m * N + (size_t)nb * 128)[lane] = q;
+    if (lane == 0) {
+      C_s[(size_t)nb * M + m] = __fdiv_rn(amax, 448.0f);
+    }
+  }
+}
+
+// Reduce-scatter step of one warp over up to two split groups at once.  Warp gw of a group's 4 * cnt warps owns
+// rows gw, gw + 4 cnt, ...; per pass it takes RB of its rows in each group and adds their partial tiles CB
+// contributors at a time, ascending CTA order, four columns per lane (a warp reads one 512-byte row per load
+// instruction): 2 * RB * CB loads are in flight together, so a pass costs one L2 round trip whatever the row
+// count, repeated (bounded) while a contributor's words have not landed yet.  Then the row's
+// absmax (a warp reduction), the two divisions, and 128 bytes per row go out.  Returns false if a wait ran out.
+template<int MP, bool OUT_F32, int RB, int CB>
+__device__ __forceinline__ bool reduce_split_groups(const SplitGroup (&g)[2],
+                                                    uint32_t* __restrict__ partials,
+                                                    void* __restrict__ C_out,
+                                                    float* __restrict__ C_s,
+                                                    int                M,
+                                                    int                N,
+                                                    int                lane,
+                                                    volatile uint32_t* abort_flag,
+                                                    uint32_t*          status)
+{
+  // (no integer division anywhere in here: a 32-bit division is a dependent chain of ~150 clk, and a dozen of
+  // them in a single warp's critical path cost more than the memory round trips)
+  int max_cnt = 0;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    max_cnt = g[k].mine ? max(max_cnt, g[k].cnt) : max_cnt;
+  }
+  for (int pass = 0;; ++pass) {
+    // first row of this pass in either group; rows ascend with r, so nothing is left when both are beyond M
+    const bool more0 = g[0].mine && g[0].gw + pass * RB * 4 * g[0].cnt < M;
+    const bool more1 = g[1].mine && g[1].gw + pass * RB * 4 * g[1].cnt < M;
+    if (!more0 && !more1) {
+      break;
+    }
+    float4 sum[2][RB];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+#pragma unroll
+      for (int r = 0; r < RB; ++r) {
+        sum[k][r] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+    }
+    for (int cb = 0; cb * CB < max_cnt; ++cb) {
+      uint32_t off[2][RB][CB];  // word offset into the scratch; NONE: nothing to read for this (group, row, contributor)
+      constexpr uint32_t NONE = 0xffffffffu;
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+#pragma unroll
+        for (int j = 0; j < CB; ++j) {
+          const int  jj   = cb * CB + j;
+          const bool c_ok = g[k].mine && jj < g[k].cnt;
+          const int  c    = g[k].c_lo + (c_ok ? jj : 0);
+          // the group's first contributor reached it at K-block 0 (slot 1), the others began inside it (slot 0)
+          const int  sl   = c * 2 + (jj == 0 ? 1 : 0);
+#pragma unroll
+          for (int r = 0; r < RB; ++r) {
+            const int m  = g[k].gw + (pass * RB + r) * 4 * g[k].cnt;
+            off[k][r][j] = (c_ok && m < M) ? (uint32_t)((sl * MP + m) * 128 + lane * 4) : NONE;
+          }
+        }
+      }
+      uint4              t[2][RB][CB];
+      unsigned long long t0    = 0;
+      uint32_t           spins = 0;
+      for (;;) {
+        bool landed = true;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+#pragma unroll
+          for (int r = 0; r < RB; ++r) {
+#pragma unroll
+            for (int j = 0; j < CB; ++j) {
+              if (off[k][r][j] != NONE) {
+                t[k][r][j] = ld_partial4(partials + off[k][r][j]);
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+#pragma unroll
+          for (int r = 0; r < RB; ++r) {
+#pragma unroll
+            for (int j = 0; j < CB; ++j) {
+              if (off[k][r][j] != NONE) {
+                landed = landed && t[k][r][j].x != 0u && t[k][r][j].y != 0u && t[k][r][j].z != 0u && t[k][r][j].w != 0u;
+              }
+            }
+          }
+        }
+#ifdef LLMMM_PROFILE
+        if (threadIdx.x == deccfg::EPI_WARP0 * 32 && pass == 0 && cb == 0 && spins == 0) {
+          g_prof_cta[blockIdx.x][6] = global_timer_ns();  // first poll has returned
+        }
+#endif
+        if (__all_sync(0xffffffffu, landed)) {
+#ifdef LLMMM_PROFILE
+          if (threadIdx.x == deccfg::EPI_WARP0 * 32 && pass == 0 && cb == 0) {
+            g_prof_cta[blockIdx.x][10] = global_timer_ns();  // first batch complete
+            g_prof_cta[blockIdx.x][11] = spins + 1;          // polls it took (a count, not a time)
+          }
+#endif
+          break;
+        }
+        ++spins;
+        if ((spins & 0x7) == 0) {
+          if (*abort_flag) {
+            return false;
+          }
+          const unsigned long long now = global_timer_ns();
+          if (t0 == 0) {
+            t0 = now;
+          }
+          else if (now - t0 > WAIT_LIMIT_NS) {
+            *abort_flag = DEV_WAIT_SPLITK;
+            atomicCAS(status, 0u, (uint32_t)DEV_WAIT_SPLITK);
+            return false;
+          }
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+#pragma unroll
+        for (int j = 0; j < CB; ++j) {  // ascending CTA order: the result does not depend on timing
+#pragma unroll
+          for (int r = 0; r < RB; ++r) {
+            if (off[k][r][j] != NONE) {
+              // consumed: the words go back to zero for the next launch
+              __stcg(reinterpret_cast<uint4*>(partials + off[k][r][j]), make_uint4(0u, 0u, 0u, 0u));
+              sum[k][r].x += decode_partial(t[k][r][j].x);
+              sum[k][r].y += decode_partial(t[k][r][j].y);
+              sum[k][r].z += decode_partial(t[k][r][j].z);
+              sum[k][r].w += decode_partial(t[k][r][j].w);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+#pragma unroll
+      for (int r = 0; r < RB; ++r) {
+        const int m = g[k].gw + (pass * RB + r) * 4 * g[k].cnt;
+        if (!g[k].mine || m >= M) {
+          continue;
+        }
+        store_group_row<OUT_F32>(sum[k][r], m, g[k].nb, C_out, C_s, M, N, lane);
+      }
+    }
+  }
+  return true;
+}
+
 // CLUSTER = false: stream-K over all weight blocks, partial tiles through the caller's scratch (above).
 // CLUSTER = true : one thread-block cluster per output group; CTA r of the C in the cluster takes the r-th
-//   slice of the group's K range, and the partial tiles are added through distributed shared memory: after
-//   a cluster barrier (every CTA's TMA ring is idle) the other CTAs store their partial into the leader's
-//   ring, a second barrier, and the leader adds them in rank order and runs the epilogue.  No scratch, no
-//   atomics, no global round trips; used when the groups times a cluster size of 2-7 fill the GPU.
+//   slice of the group's K range, and the partial tiles are added through distributed shared memory as a
+//   reduce-scatter: after a cluster barrier (every CTA's TMA ring is idle) each CTA stores row i of its partial
+//   into the ring of CTA i % C, a second barrier, and every CTA adds the partials of its rows in rank order,
+//   quantises and stores them, one warp per row.  No scratch, no atomics, no global round trips; used when
+//   the groups times a cluster size of 2-7 fill the GPU.
 template<int MP, bool OUT_F32, bool CLUSTER>
 __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __grid_constant__ CUtensorMap tm_w,
                                                                         const __grid_constant__ CUtensorMap tm_x,
@@ -120,8 +356,7 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
                                                                         int       M,
                                                                         int       N,
                                                                         int       K,
-                                                                        float*    partials,
-                                                                        uint32_t* counters,
+                                                                        uint32_t* partials,
                                                                         int       early_weights,
                                                                         uint32_t* status)
 {
@@ -134,22 +369,18 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) {
-    PROFD(0);
-#ifdef LLMMM_PROFILE
-    g_prof_cta[blockIdx.x][0] = global_timer_ns();
-#endif
-  }
+  PROF_CTA(0);
 
   const int       KB      = K / BK;
   const uint32_t  U       = (uint32_t)(N / 128) * (uint32_t)KB;  // the launcher keeps U * 256 below 2^31
   const uint32_t  G       = gridDim.x;
-  uint32_t        c_size  = 1, c_rank = 0;
+  uint32_t        c_size  = 1, c_rank = 0, red_rows = MP;  // (cluster kernel: rows of the group a CTA owns, at most)
   uint32_t        u_begin, u_end;
   if constexpr (CLUSTER) {
     asm volatile("mov.u32 %0, %%cluster_nctaid.x;" : "=r"(c_size));
     c_rank = cluster_ctarank();
     const uint32_t group = blockIdx.x / c_size;
+    red_rows = ((uint32_t)MP + c_size - 1) / c_size;
     u_begin = group * (uint32_t)KB + (c_rank * (uint32_t)KB) / c_size;
     u_end   = group * (uint32_t)KB + ((c_rank + 1) * (uint32_t)KB) / c_size;
   }
@@ -168,25 +399,13 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
     fence_mbar_init();
     prefetch_tmap(&tm_w);
     prefetch_tmap(&tm_x);
-#ifdef LLMMM_PROFILE
-    g_prof_set[blockIdx.x][0] = global_timer_ns();
-#endif
   }
   if (warp == 1) {
-#ifdef LLMMM_PROFILE
-    if (lane == 0) g_prof_set[blockIdx.x][1] = global_timer_ns();
-#endif
     tmem_alloc<TMEM_COLS>(&bars->tmem_base);
-#ifdef LLMMM_PROFILE
-    if (lane == 0) g_prof_set[blockIdx.x][2] = global_timer_ns();
-#endif
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-#ifdef LLMMM_PROFILE
-  if (threadIdx.x == 0) g_prof_set[blockIdx.x][3] = global_timer_ns();
-#endif
   const uint32_t tmem_base = bars->tmem_base;
   // Set-up (barriers, tensor memory, descriptor prefetch) touched no global memory: it may overlap the tail
   // of the previous kernel on the stream, and the next kernel may begin its own set-up from here on.
@@ -194,10 +413,17 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
   if (warp != 0) {
     pdl_wait();  // warp 0 waits below, as a whole: a waiting lane holds up the other lanes of its warp
   }
-  if (threadIdx.x == 0) {
-    PROFD(1);
-  }
+  PROF_CTA(1);
 
+  // With 64 activation columns a promotion thread holds 64 accumulators and a 64-value partial, and the
+  // reduction of split groups wants as many loads in flight as registers allow: the control warpgroup hands
+  // registers over (the 8 warps of each of two resident CTAs start with 128 per thread).
+  if (warp < EPI_WARP0) {
+    setmaxnreg_dec<REGS_CTRL>();
+  }
+  else {
+    setmaxnreg_inc<REGS_EPI>();
+  }
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer --
     const uint64_t pol_w = policy_evict_first();  // weights are read once
@@ -220,13 +446,7 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
       }
     }
     __syncwarp();
-#ifdef LLMMM_PROFILE
-    if (lane == 0) g_prof_pdl[blockIdx.x][0] = global_timer_ns();
-#endif
     pdl_wait();
-#ifdef LLMMM_PROFILE
-    if (lane == 0) g_prof_pdl[blockIdx.x][1] = global_timer_ns();
-#endif
     if (lane == 0) {
       uint32_t it = 0;
       int      nb = nb0, kb = kb0;
@@ -251,31 +471,33 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
       cluster_sync_all();  // partial tiles have been delivered to the leader
     }
   }
-  else if (warp == 1) {
-    // -------------------------------------------------------- MMA issuer --
+  else if (warp < EPI_WARP0) {
+    // --------------------------------------------- three MMA issuers ------
+    // Warps 1, 2 and 3 take every third K-block of the run; each K-block has its own ring slot and
+    // tensor-memory partial stage, so the threads never touch the same barrier phase.
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(/*e4m3*/ 0, 0, 0, 0, 128, MP);
-      uint32_t           it    = 0;
-      for (uint32_t u = u_begin; u < u_end; ++u, ++it) {
+      const uint32_t     run   = u_end - u_begin;
+      for (uint32_t it = (uint32_t)(warp - 1); it < run; it += 3) {
         const uint32_t s  = it % L::STAGES;
         const uint32_t ph = (it / L::STAGES) & 1;
-        const uint32_t p  = s;
-        const uint32_t pp = ph;
-        mbar_wait(&bars->part_empty[p], pp ^ 1, DEV_WAIT_TMEM_EMPTY, abort_flag, status);
+        mbar_wait(&bars->part_empty[s], ph ^ 1, DEV_WAIT_TMEM_EMPTY, abort_flag, status);
         mbar_wait(&bars->full[s], ph, DEV_WAIT_SMEM_FULL, abort_flag, status);
         if (it == 0) {
-          PROFD(2);
+          PROF_CTA(2);
         }
         tc_fence_after_sync();
         const uint64_t dw = make_smem_desc_sw128(smem_u32(smem + L::OFF_W + s * W_BYTES), 0, 1024);
         const uint64_t dx = make_smem_desc_sw128(smem_u32(smem + L::OFF_X + s * L::X_BYTES), 0, 1024);
 #pragma unroll
         for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-          tc_mma_f8(tmem_base + p * L::PART_COLS, dw + (uint64_t)((kk * UMMA_K) >> 4), dx + (uint64_t)((kk * UMMA_K) >> 4), idesc, kk != 0);
+          tc_mma_f8(tmem_base + s * L::PART_COLS, dw + (uint64_t)((kk * UMMA_K) >> 4), dx + (uint64_t)((kk * UMMA_K) >> 4), idesc, kk != 0);
         }
-        tc_commit(&bars->part_full[p]);
+        tc_commit(&bars->part_full[s]);
       }
-      PROFD(3);
+      if (warp == 1) {
+        PROF_CTA(3);
+      }
     }
     if constexpr (CLUSTER) {
       __syncwarp();
@@ -285,12 +507,53 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
   }
   else {
     // ------------------------------------------- promotion + epilogue ----
-    const int      quarter = warp & 3;
-    const int      ew      = warp - 2;             // 0..3, index into bars->amax
+    const int      quarter = warp & 3;             // tensor-memory lane quarter this warp may read
+    const int      ew      = warp - EPI_WARP0;     // 0..3, index into bars->amax
     const int      n_local = quarter * 32 + lane;  // output column inside the group == TMEM lane
-    const int      et      = threadIdx.x - 64;     // 0..127
+    const int      et      = threadIdx.x - EPI_WARP0 * 32;  // 0..127
     const uint32_t t_lane  = (uint32_t)(quarter * 32) << 16;
+    const uint32_t run     = u_end - u_begin;
     uint32_t       it      = 0;
+
+    // Scale products of the run, CHUNK K-blocks at a time: thread `et` fetches elements et, et + 128, ... of
+    // the [CHUNK][MP] chunk (A_s[kb, m] and B_s[nb, kb]: the latter is simply B_s[u] for unit u), multiplies
+    // (one fp32 rounding of each scale product, as in the reference) and keeps them in registers until the
+    // chunk before has been used up.  All loads of a chunk are in flight together; for runs of up to CHUNK
+    // K-blocks there is exactly one L2 round trip, hidden behind the first operand tiles.
+    constexpr int CH = L::CHUNK;
+    constexpr int SE = CH * MP / 128;  // elements per thread
+    float*        sc = reinterpret_cast<float*>(smem + L::OFF_SC);
+    float         st[SE];
+    auto fetch_chunk = [&](uint32_t chunk) {
+#pragma unroll
+      for (int i = 0; i < SE; ++i) {
+        const uint32_t e   = (uint32_t)et + 128u * (uint32_t)i;
+        const uint32_t itx = chunk * CH + e / MP;
+        const int      m   = (int)(e % MP);
+        float          v   = 0.0f;
+        if (itx < run && m < M) {
+          const uint32_t uu = u_begin + itx;
+          v = __fmul_rn(__ldg(A_s + (size_t)(uu % (uint32_t)KB) * M + m), __ldg(B_s + uu));
+        }
+        st[i] = v;
+      }
+    };
+    auto store_chunk = [&]() {
+#pragma unroll
+      for (int i = 0; i < SE; ++i) {
+        sc[et + 128 * i] = st[i];
+      }
+    };
+    fetch_chunk(0);
+    store_chunk();
+    epilogue_bar_sync();
+    if (run > (uint32_t)CH) {
+      fetch_chunk(1);
+    }
+
+    // groups this CTA contributed a partial tile to (at most the first and the last segment of its run)
+    int pend_nb0 = 0, pend_nb1 = 0;
+    int n_pend = 0;
 
     uint32_t u     = u_begin;
     bool     first = true;  // a cluster CTA runs its one segment even if it is empty: it owes two cluster barriers
@@ -307,152 +570,120 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
       for (int i = 0; i < MP; ++i) {
         acc[i] = 0.0f;
       }
-      // Scale operands: lane l of every warp holds A_s[kb, l] and A_s[kb, 32 + l] (fetched one K-block
-      // ahead) times B_s; column m's product is broadcast with a shuffle where it is used.
-      float a_lo = (lane < M) ? __ldg(A_s + (size_t)kb0 * M + lane) : 0.0f;
-      float a_hi = (MP > 32 && lane + 32 < M) ? __ldg(A_s + (size_t)kb0 * M + 32 + lane) : 0.0f;
-      float b_nx = __ldg(B_s + (size_t)nb * KB + kb0);
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const uint32_t p  = it % L::STAGES;
         const uint32_t pp = (it / L::STAGES) & 1;
-        // one fp32 rounding of each scale product, as in the reference
-        const float sc_lo = __fmul_rn(a_lo, b_nx);
-        const float sc_hi = __fmul_rn(a_hi, b_nx);
-        if (kb + 1 < kb1) {
-          a_lo = (lane < M) ? __ldg(A_s + (size_t)(kb + 1) * M + lane) : 0.0f;
-          a_hi = (MP > 32 && lane + 32 < M) ? __ldg(A_s + (size_t)(kb + 1) * M + 32 + lane) : 0.0f;
-          b_nx = __ldg(B_s + (size_t)nb * KB + kb + 1);
+        if (it != 0 && it % CH == 0) {
+          // the next chunk's products are in `st`: swap them in once everybody is done with the old ones
+          epilogue_bar_sync();
+          store_chunk();
+          epilogue_bar_sync();
+          if ((it / CH + 1) * CH < run) {
+            fetch_chunk(it / CH + 1);
+          }
         }
+        PROF_KB(0);
         mbar_wait(&bars->part_full[p], pp, DEV_WAIT_TMEM_FULL, abort_flag, status);
+        PROF_KB(1);
         tc_fence_after_sync();
-        uint32_t v[MP];
+        // the partial goes to registers (at most 32 columns at a time) and the stage is handed back as soon as
+        // its last column has been read, before the arithmetic on it
+        constexpr int VW = MP > 32 ? 32 : MP;
+        const float4* srow = reinterpret_cast<const float4*>(sc + (it % CH) * MP);
 #pragma unroll
-        for (int c = 0; c < MP / 16; ++c) {
-          tmem_ld_32x32b_x16(tmem_base + p * L::PART_COLS + t_lane + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&v[c * 16]));
-        }
-        tmem_ld_wait();
-        // the partial is in registers: hand the stage back before any arithmetic
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(&bars->part_empty[p]);
-        }
+        for (int h = 0; h < MP / VW; ++h) {
+          uint32_t v[VW];
 #pragma unroll
-        for (int m = 0; m < MP; ++m) {
-          const float sc = __shfl_sync(0xffffffffu, (m < 32) ? sc_lo : sc_hi, m & 31);
-          acc[m]         = __fmaf_rn(__uint_as_float(v[m]), sc, acc[m]);
+          for (int c = 0; c < VW / 16; ++c) {
+            tmem_ld_32x32b_x16(tmem_base + p * L::PART_COLS + t_lane + h * VW + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&v[c * 16]));
+          }
+          tmem_ld_wait();
+          if (h == MP / VW - 1) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+              mbar_arrive(&bars->part_empty[p]);
+            }
+            PROF_KB(2);
+          }
+#pragma unroll
+          for (int m = 0; m < VW; m += 4) {
+            const float4 s4 = srow[(h * VW + m) >> 2];  // the same address in every lane: a broadcast
+            acc[h * VW + m]     = __fmaf_rn(__uint_as_float(v[m]), s4.x, acc[h * VW + m]);
+            acc[h * VW + m + 1] = __fmaf_rn(__uint_as_float(v[m + 1]), s4.y, acc[h * VW + m + 1]);
+            acc[h * VW + m + 2] = __fmaf_rn(__uint_as_float(v[m + 2]), s4.z, acc[h * VW + m + 2]);
+            acc[h * VW + m + 3] = __fmaf_rn(__uint_as_float(v[m + 3]), s4.w, acc[h * VW + m + 3]);
+          }
         }
+        PROF_KB(3);
       }
       u += (uint32_t)(kb1 - kb0);
-      if (et == 0) {
-        PROFD(4);
-#ifdef LLMMM_PROFILE
-        g_prof_cta[blockIdx.x][1] = global_timer_ns();
-#endif
+      if (u >= u_end && ew == 0) {
+        PROF_CTA(4);
       }
 
       bool finish = whole;
       if constexpr (CLUSTER) {
-        float* red = reinterpret_cast<float*>(smem + L::OFF_W);  // the leader's idle ring: [rank-1][row][n]
-        cluster_sync_all();                                      // all MMAs of all CTAs are done: rings idle
-        if (c_rank != 0) {
-          const uint32_t base = mapa_shared(smem_u32(red + ((size_t)(c_rank - 1) * MP) * 128 + n_local), 0);
+        // Reduce-scatter through distributed shared memory: row i of the group belongs to CTA i % c_size, which
+        // receives every CTA's partial of that row (its own included) in its idle ring, [source rank][i / c_size][n].
+        float*         red      = reinterpret_cast<float*>(smem + L::OFF_W);
+        const uint32_t red_addr = smem_u32(red + ((size_t)c_rank * red_rows) * 128 + n_local);
+        cluster_sync_all();  // all MMAs of all CTAs are done: rings idle
+        if (ew == 0) {
+          PROF_CTA(5);
+        }
+        {
+          uint32_t owner = 0, q = 0;  // i % c_size, i / c_size
 #pragma unroll
           for (int i = 0; i < MP; ++i) {
             if (i < M) {
-              asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(base + (uint32_t)i * 512u), "f"(acc[i]) : "memory");
+              const uint32_t dst = mapa_shared(red_addr + q * 512u, owner);
+              asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst), "f"(acc[i]) : "memory");
+            }
+            if (++owner == c_size) {
+              owner = 0;
+              ++q;
             }
           }
         }
-        cluster_sync_all();  // release/acquire at cluster scope: the stores above are visible to the leader
-        finish = (c_rank == 0);
-        if (finish) {
-          for (uint32_t rr = 1; rr < c_size; ++rr) {  // fixed order: the result does not depend on timing
-#pragma unroll
-            for (int i = 0; i < MP; ++i) {
-              if (i < M) {
-                acc[i] += red[((size_t)(rr - 1) * MP + i) * 128 + n_local];
-              }
-            }
-          }
+        cluster_sync_all();  // release/acquire at cluster scope: the stores above are visible to their owners
+        if (ew == 0) {
+          PROF_CTA(6);
         }
+        // one warp per owned row: four columns per lane, the partials added in rank order
+        for (uint32_t q = (uint32_t)ew, m = c_rank + (uint32_t)ew * c_size; m < (uint32_t)M; q += 4, m += 4 * c_size) {
+          float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          for (uint32_t rr = 0; rr < c_size; ++rr) {  // fixed order: the result does not depend on timing
+            const float4 t = reinterpret_cast<const float4*>(red + ((size_t)rr * red_rows + q) * 128)[lane];
+            sum.x += t.x;
+            sum.y += t.y;
+            sum.z += t.z;
+            sum.w += t.w;
+          }
+          store_group_row<OUT_F32>(sum, (int)m, nb, C_out, C_s, M, N, lane);
+        }
+        if (ew == 0) {
+          PROF_CTA(7);
+        }
+        finish = false;
       }
       else if (!whole) {
-        // publish this CTA's partial, then see whether it was the last to arrive
+        // publish this CTA's partial tile as flagged words; the reduction follows after the whole run
         const int slot = blockIdx.x * 2 + (kb0 == 0 ? 1 : 0);  // run begins inside the group -> slot 0
-        float*    dst  = partials + (size_t)slot * (MP * 128);
+        uint32_t* dst  = partials + (size_t)slot * (MP * 128);
 #pragma unroll
         for (int i = 0; i < MP; ++i) {
           if (i < M) {
-            __stcg(dst + i * 128 + n_local, acc[i]);
+            st_partial(dst + i * 128 + n_local, acc[i]);
           }
         }
-        __threadfence();
-        epilogue_bar_sync();
-        if (et == 0) {
-          PROFD(5);
+        if (n_pend == 0) {
+          pend_nb0 = nb;
         }
-        PROFF(0);
-        const int c_lo = cta_of_unit((uint32_t)nb * (uint32_t)KB, G, U);
-        const int c_hi = cta_of_unit((uint32_t)(nb + 1) * (uint32_t)KB - 1, G, U);
-        if (et == 0) {
-          const uint32_t old = atomicAdd(&counters[nb], 1u);
-          const bool     lst = (old == (uint32_t)(c_hi - c_lo));
-          if (lst) {
-            counters[nb] = 0;  // ready for the next launch
-          }
-          bars->last_flag = lst ? 1u : 0u;
+        else {
+          pend_nb1 = nb;
         }
-        epilogue_bar_sync();
-        if (et == 0) {
-          PROFD(6);
-        }
-        PROFF(1);
-        finish = bars->last_flag != 0;
-        if (finish) {
-          __threadfence();
-#pragma unroll
-          for (int i = 0; i < MP; ++i) {
-            acc[i] = 0.0f;
-          }
-          // Contributors are added in ascending CTA order (the result does not depend on who arrived
-          // last); four contributors' loads are in flight together, since each is an L2 round trip.
-          for (int c0 = c_lo; c0 <= c_hi; c0 += 4) {
-            const float* src[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int c = (c0 + j <= c_hi) ? c0 + j : c_hi;
-              // CTA c's run begins inside this group (slot 0) unless it began earlier (slot 1)
-              const uint32_t cs = ((uint32_t)c * U) / G;
-              const int      sl = c * 2 + ((int)(cs / (uint32_t)KB) == nb && (cs % (uint32_t)KB) != 0 ? 0 : 1);
-              src[j]             = partials + (size_t)sl * (MP * 128) + n_local;
-            }
-#pragma unroll
-            for (int i0 = 0; i0 < MP; i0 += 16) {
-              if (i0 < M) {
-                float t[4][16];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-#pragma unroll
-                  for (int i = 0; i < 16; ++i) {
-                    t[j][i] = (i0 + i < M) ? __ldcg(src[j] + (i0 + i) * 128) : 0.0f;
-                  }
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  if (c0 + j <= c_hi) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                      acc[i0 + i] += t[j][i];
-                    }
-                  }
-                }
-              }
-            }
-          }
-        }
-        epilogue_bar_sync();  // last_flag may be rewritten by the next segment
-        PROFF(2);
+        ++n_pend;
       }
 
       if (finish) {
@@ -479,7 +710,6 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
             }
           }
           epilogue_bar_sync();
-          PROFF(3);
           // thread i finishes row i's absmax and does the two divisions once for everybody
           if (et < M) {
             const float amax = fmaxf(fmaxf(bars->amax[0][et], bars->amax[1][et]), fmaxf(bars->amax[2][et], bars->amax[3][et]));
@@ -495,91 +725,140 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
             }
           }
           epilogue_bar_sync();  // bars->amax and bars->inv are reused by the next segment
-          PROFF(4);
         }
       }
     }
-#ifdef LLMMM_PROFILE
-    if (et == 0) {
-      g_prof_cta[blockIdx.x][2] = global_timer_ns();
+
+    if constexpr (!CLUSTER) {
+      // ------------------------------------------- reduce-scatter of the split groups ----
+      // Group nb was cut among CTAs c_lo..c_hi.  Its M rows are dealt out to the 4 * (c_hi - c_lo + 1) promotion
+      // warps of those CTAs: warp w of contributor j takes rows 4 j + w, 4 j + w + 4 cnt, ...  A warp reads
+      // (bounded) until the words of every contributor have landed -- all CTAs of the grid are resident, the
+      // grid is never larger than the SM count -- and reduces its rows of both groups this CTA took part in
+      // (reduce_split_groups).
+      if (n_pend > 0) {
+        if (ew == 0) {
+          PROF_CTA(5);
+        }
+        // first and last contributor of both groups: four divisions, one per lane
+        uint32_t q = 0;
+        if (lane < 4) {
+          const uint32_t nbq = (uint32_t)(lane < 2 ? pend_nb0 : pend_nb1);
+          q = (uint32_t)cta_of_unit((lane & 1) ? (nbq + 1) * (uint32_t)KB - 1 : nbq * (uint32_t)KB, G, U);
+        }
+        SplitGroup g[2];
+        int        max_cnt = 0;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          g[k].nb   = k == 0 ? pend_nb0 : pend_nb1;
+          g[k].c_lo = (int)__shfl_sync(0xffffffffu, q, 2 * k);
+          g[k].cnt  = (int)__shfl_sync(0xffffffffu, q, 2 * k + 1) - g[k].c_lo + 1;
+          g[k].gw   = 4 * ((int)blockIdx.x - g[k].c_lo) + ew;
+          g[k].mine = k < n_pend && g[k].gw < M;  // more warps than rows: some have none
+          if (g[k].mine) {
+            max_cnt = max(max_cnt, g[k].cnt);
+          }
+        }
+        if (g[0].mine || g[1].mine) {
+          if (max_cnt <= 2) {
+            reduce_split_groups<MP, OUT_F32, 4, 2>(g, partials, C_out, C_s, M, N, lane, abort_flag, status);
+          }
+          else if (max_cnt <= 4) {
+            reduce_split_groups<MP, OUT_F32, 2, 4>(g, partials, C_out, C_s, M, N, lane, abort_flag, status);
+          }
+          else {
+            reduce_split_groups<MP, OUT_F32, 1, 8>(g, partials, C_out, C_s, M, N, lane, abort_flag, status);
+          }
+        }
+        if (ew == 0) {
+          PROF_CTA(7);
+        }
+      }
     }
-#endif
+    if (ew == 0) {
+      PROF_CTA(8);
+    }
   }
 
   tc_fence_before_sync();
   __syncthreads();
-  if (threadIdx.x == 0) {
-    PROFD(7);
-  }
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc<TMEM_COLS>(tmem_base);
-  }
-  if (threadIdx.x == 32) {
-    PROFD(8);
-#ifdef LLMMM_PROFILE
-    g_prof_cta[blockIdx.x][3] = global_timer_ns();
-#endif
+    PROF_CTA(9);
   }
 }
 
 #ifdef LLMMM_PROFILE
-extern "C" void llmmm_profile_dump_pdl()
-{
-  unsigned long long c[256][4], w[256][2];
-  cudaMemcpyFromSymbol(c, g_prof_cta, sizeof(c));
-  cudaMemcpyFromSymbol(w, g_prof_pdl, sizeof(w));
-  double held = 0, setup = 0; unsigned long long first_entry = ~0ull, last_entry = 0, last_exit = 0, first_go = ~0ull; int n = 0;
-  for (int i = 0; i < 256; ++i) {
-    if (c[i][0] == 0 || w[i][1] == 0) continue;
-    held += (double)(w[i][1] - w[i][0]); setup += (double)(w[i][0] - c[i][0]); ++n;
-    if (c[i][0] < first_entry) first_entry = c[i][0];
-    if (c[i][0] > last_entry) last_entry = c[i][0];
-    if (c[i][3] > last_exit) last_exit = c[i][3];
-    if (w[i][1] < first_go) first_go = w[i][1];
-  }
-  unsigned long long st[256][4];
-  cudaMemcpyFromSymbol(st, g_prof_set, sizeof(st));
-  printf("CTA 5: entry +0, barriers initialised +%llu, tcgen05.alloc from +%llu to +%llu, CTA barrier passed +%llu, at the dependency wait +%llu, released +%llu, exit +%llu ns\n",
-         st[5][0] - c[5][0], st[5][1] - c[5][0], st[5][2] - c[5][0], st[5][3] - c[5][0], w[5][0] - c[5][0], w[5][1] - c[5][0], c[5][3] - c[5][0]);
-  unsigned long long h[16];
-  cudaMemcpyFromSymbol(h, g_prof_dec, sizeof(h));
-  printf("CTA 0 after its release (ns): first operands +%lld, MMAs issued +%lld, promotion done +%lld, all roles done +%lld, TMEM freed +%lld\n",
-         (long long)(h[2] - w[0][1]), (long long)(h[3] - w[0][1]), (long long)(h[4] - w[0][1]), (long long)(h[7] - w[0][1]), (long long)(h[8] - w[0][1]));
-  printf("last launch, %d CTAs: entries spread over %llu ns, set-up %.0f ns, held at the dependency wait %.0f ns (avg), "
-         "first entry -> first release %llu ns, first entry -> last exit %llu ns\n", n, last_entry - first_entry, setup / n,
-         held / n, first_go - first_entry, last_exit - first_entry);
-}
-
+// Profiling build only (python -m llmmm_b200.build --profile): prints the phase stamps of the last decode launch.
 extern "C" void llmmm_profile_dump_decode()
 {
-  unsigned long long h[16];
-  unsigned long long c[256][4];
+  static const char* names[11] = {"entry", "released", "first operands", "MMAs issued", "promotion done", "published",
+                                  "first poll back", "rows reduced", "roles done", "TMEM freed", "first batch in"};
+  static unsigned long long c[256][12];
   cudaMemcpyFromSymbol(c, g_prof_cta, sizeof(c));
-  unsigned long long t0 = ~0ull, t_last_entry = 0, t_loop = 0, t_exit = 0;
-  for (int i = 0; i < 148; ++i) {
-    if (c[i][0] == 0) continue;
-    if (c[i][0] < t0) t0 = c[i][0];
-    if (c[i][0] > t_last_entry) t_last_entry = c[i][0];
-    if (c[i][1] > t_loop) t_loop = c[i][1];
-    if (c[i][3] > t_exit) t_exit = c[i][3];
+  unsigned long long t0 = ~0ull, rel = ~0ull;
+  int                n  = 0;
+  for (int i = 0; i < 256; ++i) {
+    if (c[i][0] == 0) {
+      continue;
+    }
+    ++n;
+    t0  = c[i][0] < t0 ? c[i][0] : t0;
+    rel = c[i][1] < rel ? c[i][1] : rel;
   }
-  printf("all CTAs (ns from first entry): last entry %llu, last promotion loop done %llu, last exit %llu\n",
-         t_last_entry - t0, t_loop - t0, t_exit - t0);
-  unsigned long long f[256][6];
-  cudaMemcpyFromSymbol(f, g_prof_fin, sizeof(f));
-  int worst = 0;
-  for (int i = 0; i < 148; ++i) {
-    if (c[i][3] > c[worst][3]) worst = i;
+  if (n == 0) {
+    printf("no decode launch recorded\n");
+    return;
   }
-  printf("slowest CTA %d (ns from first entry): entry %llu loop done %llu | published %llu counted %llu reduced %llu amax %llu stored %llu | "
-         "roles done %llu exit %llu\n",
-         worst, c[worst][0] - t0, c[worst][1] - t0, f[worst][0] - t0, f[worst][1] - t0, f[worst][2] - t0, f[worst][3] - t0,
-         f[worst][4] - t0, c[worst][2] - t0, c[worst][3] - t0);
-  cudaMemcpyFromSymbol(h, g_prof_dec, sizeof(h));
-  printf("decode CTA 0 (ns from kernel entry): set-up done %llu, first operands %llu, MMAs issued %llu, promotion done %llu, "
-         "partial published %llu, arrival counted %llu, all roles done %llu, TMEM freed %llu\n",
-         h[1] - h[0], h[2] - h[0], h[3] - h[0], h[4] - h[0], h[5] - h[0], h[6] - h[0], h[7] - h[0], h[8] - h[0]);
+  printf("decode launch, %d CTAs; ns after the first release (min / mean / max over CTAs):\n", n);
+  for (int k = 0; k < 11; ++k) {
+    double             sum = 0;
+    long long          mn = 1ll << 62, mx = -(1ll << 62);
+    int                cnt = 0;
+    for (int i = 0; i < 256; ++i) {
+      if (c[i][0] == 0 || c[i][k] == 0) {
+        continue;
+      }
+      const long long d = (long long)(c[i][k] - rel);
+      sum += (double)d;
+      mn = d < mn ? d : mn;
+      mx = d > mx ? d : mx;
+      ++cnt;
+    }
+    if (cnt) {
+      printf("  %-18s %7lld %9.0f %7lld  (%d CTAs)\n", names[k], mn, sum / cnt, mx, cnt);
+    }
+  }
+  {
+    double polls = 0;
+    int    cnt   = 0, mx = 0;
+    for (int i = 0; i < 256; ++i) {
+      if (c[i][0] != 0 && c[i][11] != 0) {
+        polls += (double)c[i][11];
+        mx = (int)c[i][11] > mx ? (int)c[i][11] : mx;
+        ++cnt;
+      }
+    }
+    if (cnt) {
+      printf("  polls until the first batch was complete: mean %.1f, max %d\n", polls / cnt, mx);
+    }
+  }
+  {
+    unsigned long long kb[8][4];
+    cudaMemcpyFromSymbol(kb, g_prof_kb, sizeof(kb));
+    printf("  CTA 0, first promotion warp, per K-block (ns after release): waiting / partial seen / read / done\n");
+    for (int i = 0; i < 8; ++i) {
+      if (kb[i][0]) {
+        printf("    %d: %lld %lld %lld %lld\n", i, (long long)(kb[i][0] - rel), (long long)(kb[i][1] - rel), (long long)(kb[i][2] - rel),
+               (long long)(kb[i][3] - rel));
+      }
+    }
+    static unsigned long long zkb[8][4];
+    cudaMemcpyToSymbol(g_prof_kb, zkb, sizeof(zkb));
+  }
+  static unsigned long long zero[256][12];
+  cudaMemcpyToSymbol(g_prof_cta, zero, sizeof(zero));
 }
 #endif
 
@@ -588,7 +867,6 @@ extern "C" void llmmm_profile_dump_decode()
 std::atomic<int> g_static_weights{0};  // llmmm_set_static_weights()
 
 namespace {
-static_assert(deccfg::COUNTER_BYTES == WS_DECODE_COUNTER_BYTES, "layout of the registered scratch");
 Workspace  g_ws[64];
 std::mutex g_ws_mutex;
 
@@ -598,9 +876,17 @@ int padded_m(int M)
 }
 }  // namespace
 
+// Partial tiles of the stream-K kernel: two slots per CTA of M (padded) x 128 self-announcing 32-bit words.
+static size_t decode_partial_bytes(int M)
+{
+  return (size_t)deccfg::MAX_CTAS * 2 * padded_m(M) * 128 * sizeof(uint32_t);
+}
+
+// The decode kernel's partial tiles lie behind the split tiles of the pair kernels (whose region is never
+// zero): they must be all zero between launches.
 size_t decode_workspace_bytes(int M)
 {
-  return WS_HEADER_BYTES + (size_t)deccfg::MAX_CTAS * 2 * padded_m(M) * 128 * sizeof(float);
+  return split_workspace_bytes() + decode_partial_bytes(M);
 }
 
 Workspace registered_workspace(int device)
@@ -619,8 +905,7 @@ static int launch_decode_t(const void*       A,
                            int               M,
                            int               N,
                            int               K,
-                           uint32_t*         counters,
-                           float*            partials,
+                           uint32_t*         partials,
                            const DeviceInfo* info,
                            cudaStream_t      stream)
 {
@@ -643,7 +928,7 @@ static int launch_decode_t(const void*       A,
     G = (int)U;
   }
   LLMMM_CUDA_TRY(launch_pdl(fp8_decode_kernel<MP, OUT_F32, false>, dim3((unsigned)G), dim3(THREADS), L::SMEM_BYTES, stream,
-                            1, tm_w, tm_x, A_s, B_s, C, C_s, M, N, K, partials, counters, g_static_weights.load(),
+                            1, tm_w, tm_x, A_s, B_s, C, C_s, M, N, K, partials, g_static_weights.load(),
                             info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
@@ -676,48 +961,56 @@ static int launch_decode_cluster_t(const void*       A,
       fp8_decode_kernel<MP, OUT_F32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM_BYTES));
     attr_set[info->device] = true;
   }
-  float*    no_partials = nullptr;
-  uint32_t* no_counters = nullptr;
+  uint32_t* no_partials = nullptr;
   LLMMM_CUDA_TRY(launch_pdl(fp8_decode_kernel<MP, OUT_F32, true>, dim3((unsigned)((N / 128) * cluster)), dim3(THREADS),
                             L::SMEM_BYTES, stream, (unsigned)cluster, tm_w, tm_x, A_s, B_s, C, C_s, M, N, K, no_partials,
-                            no_counters, g_static_weights.load(), info->status));
+                            g_static_weights.load(), info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
 }
 
 namespace {
-// How many clusters of `size` CTAs (one CTA per SM, as the decode kernel needs) the device can hold at once.
-int cluster_capacity(const DeviceInfo* info, int size)
+// How many clusters of `size` CTAs of the cluster kernel for activation tiles of `mp` columns the device can hold
+// at once (an occupancy query, cached).
+template<int MP>
+int cluster_capacity_t(const DeviceInfo* info, int size)
+{
+  using L = DecodeSmem<MP>;
+  int clusters = 0;
+  if (cudaFuncSetAttribute(fp8_decode_kernel<MP, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM_BYTES)
+      == cudaSuccess) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim            = dim3((unsigned)(size * (info->sm_count / size)));
+    cfg.blockDim           = dim3(deccfg::THREADS);
+    cfg.dynamicSmemBytes   = L::SMEM_BYTES;
+    cudaLaunchAttribute attr[1];
+    attr[0].id               = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)size;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs                = attr;
+    cfg.numAttrs             = 1;
+    if (cudaOccupancyMaxActiveClusters(&clusters, fp8_decode_kernel<MP, false, true>, &cfg) != cudaSuccess) {
+      clusters = 0;
+    }
+  }
+  cudaGetLastError();
+  return clusters;
+}
+
+int cluster_capacity(const DeviceInfo* info, int size, int mp)
 {
   static std::mutex mu;
-  static int        cache[64][9];
-  static bool       known[64][9];
+  static int        cache[64][3][9];
+  static bool       known[64][3][9];
+  const int         slot = mp == 16 ? 0 : (mp == 32 ? 1 : 2);
   std::lock_guard<std::mutex> lock(mu);
-  if (!known[info->device][size]) {
-    using L = DecodeSmem<64>;
-    int clusters = 0;
-    if (cudaFuncSetAttribute(fp8_decode_kernel<64, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM_BYTES)
-        == cudaSuccess) {
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim            = dim3((unsigned)(size * (info->sm_count / size)));
-      cfg.blockDim           = dim3(deccfg::THREADS);
-      cfg.dynamicSmemBytes   = L::SMEM_BYTES;
-      cudaLaunchAttribute attr[1];
-      attr[0].id               = cudaLaunchAttributeClusterDimension;
-      attr[0].val.clusterDim.x = (unsigned)size;
-      attr[0].val.clusterDim.y = 1;
-      attr[0].val.clusterDim.z = 1;
-      cfg.attrs                = attr;
-      cfg.numAttrs             = 1;
-      if (cudaOccupancyMaxActiveClusters(&clusters, fp8_decode_kernel<64, false, true>, &cfg) != cudaSuccess) {
-        clusters = 0;
-      }
-    }
-    cudaGetLastError();
-    cache[info->device][size] = clusters;
-    known[info->device][size] = true;
+  if (!known[info->device][slot][size]) {
+    cache[info->device][slot][size] = mp == 16 ? cluster_capacity_t<16>(info, size)
+                                               : (mp == 32 ? cluster_capacity_t<32>(info, size) : cluster_capacity_t<64>(info, size));
+    known[info->device][slot][size] = true;
   }
-  return cache[info->device][size];
+  return cache[info->device][slot][size];
 }
 
 // Largest allowed cluster size for which every output group gets a resident cluster and every CTA at least
@@ -725,14 +1018,8 @@ int cluster_capacity(const DeviceInfo* info, int size)
 int choose_cluster(const DeviceInfo* info, int M, int N, int K)
 {
   const int groups = N / 128, kb = K / 128;
-  // Remote shared-memory stores are slow (measured: two peers delivering 32 KB each take about 4 us), so the
-  // cluster path is used only while the partial tiles are small: not for M > 32, at most 4 CTAs for M > 16.
-  if (M > 32) {
-    return 0;
-  }
-  const int max_size = (M > 16) ? 4 : 7;
-  for (int size = max_size; size >= 2; --size) {
-    if (kb >= size && groups * size <= info->sm_count && cluster_capacity(info, size) >= groups) {
+  for (int size = 7; size >= 2; --size) {
+    if (kb >= size && groups * size <= info->sm_count && cluster_capacity(info, size, padded_m(M)) >= groups) {
       // worth it only if the clusters occupy at least half of the SMs; otherwise stream-K spreads the weight
       // blocks over all of them
       return (groups * size * 2 >= info->sm_count) ? size : 0;
@@ -776,7 +1063,9 @@ int warm_decode_kernels(const DeviceInfo* info)
   LLMMM_WARM_DECODE(64, false, false) LLMMM_WARM_DECODE(64, true, false) LLMMM_WARM_DECODE(64, false, true) LLMMM_WARM_DECODE(64, true, true)
 #undef LLMMM_WARM_DECODE
   for (int size = 2; size <= 7; ++size) {
-    cluster_capacity(info, size);  // occupancy queries, cached
+    for (int mp = 16; mp <= 64; mp *= 2) {
+      cluster_capacity(info, size, mp);  // occupancy queries, cached
+    }
   }
   return LLMMM_OK;
 }
@@ -819,12 +1108,15 @@ int launch_decode(bool         out_f32,
   if (ws.ptr == nullptr || ws.bytes < decode_workspace_bytes(M)) {
     return -1;
   }
-  uint32_t* counters = static_cast<uint32_t*>(ws.ptr);
-  float*    partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws.ptr) + WS_HEADER_BYTES);
+  uint32_t* partials = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ws.ptr) + split_workspace_bytes());
+  if (g_scratch_dirty[info->device].exchange(0) != 0) {
+    // a wait ran out in an earlier launch (llmmm_check_status reported it): flagged words may have been left behind
+    LLMMM_CUDA_TRY(cudaMemsetAsync(partials, 0, ws.bytes - split_workspace_bytes(), stream));
+  }
 #define LLMMM_DECODE_CASE(MPV)                                                                                         \
   if (mp == MPV) {                                                                                                     \
-    return out_f32 ? launch_decode_t<MPV, true>(A, A_s, B, B_s, C, C_s, M, N, K, counters, partials, info, stream) :   \
-                     launch_decode_t<MPV, false>(A, A_s, B, B_s, C, C_s, M, N, K, counters, partials, info, stream);   \
+    return out_f32 ? launch_decode_t<MPV, true>(A, A_s, B, B_s, C, C_s, M, N, K, partials, info, stream) :             \
+                     launch_decode_t<MPV, false>(A, A_s, B, B_s, C, C_s, M, N, K, partials, info, stream);             \
   }
   LLMMM_DECODE_CASE(16)
   LLMMM_DECODE_CASE(32)
@@ -869,8 +1161,13 @@ int llmmm_set_workspace(void* device_ptr, size_t bytes)
     if (((uintptr_t)device_ptr & 255) != 0 || bytes < WS_HEADER_BYTES) {
       return set_error(LLMMM_ERR_SHAPE, "workspace must be 256-byte aligned and at least %zu bytes", WS_HEADER_BYTES);
     }
-    // the arrival counters must start at zero; every launch leaves them at zero again
+    // the arrival counters of the pair kernels' split tiles and the flagged words of the decode kernel's partial
+    // tiles must start at zero; every launch leaves them at zero again
     LLMMM_CUDA_TRY(cudaMemset(device_ptr, 0, WS_HEADER_BYTES));
+    if (bytes > split_workspace_bytes()) {
+      LLMMM_CUDA_TRY(cudaMemset(static_cast<uint8_t*>(device_ptr) + split_workspace_bytes(), 0, bytes - split_workspace_bytes()));
+    }
+    g_scratch_dirty[info->device].store(0);
   }
   std::lock_guard<std::mutex> lock(g_ws_mutex);
   g_ws[info->device].ptr   = device_ptr;
@@ -894,9 +1191,10 @@ namespace llmmm {
 namespace {
 
 constexpr int    NOALLOC_MAX_M = 16;
-constexpr size_t NOALLOC_BYTES = deccfg::COUNTER_BYTES + (size_t)deccfg::MAX_CTAS * 2 * 16 * 128 * sizeof(float);
+constexpr size_t NOALLOC_BYTES = (size_t)deccfg::MAX_CTAS * 2 * 16 * 128 * sizeof(uint32_t);
 
-// 16 KB of arrival counters followed by 256 x 2 partial tiles of 16 x 128 fp32: 4,210,688 bytes.
+// 160 x 2 partial tiles of 16 x 128 self-announcing 32-bit words: 2,621,440 bytes, zero when the library is
+// loaded and zero again after every call (a reader clears the words it consumed).
 static __device__ __align__(256) uint8_t g_noalloc_scratch[NOALLOC_BYTES];
 
 // In host code the array's name is only a handle for the runtime; the device
@@ -971,12 +1269,12 @@ extern "C" int llmmm_fp8_blockwise_mm_e4m3out_noalloc(const void*    A,
     // same choice as llmmm_fp8_blockwise_mm_e4m3out makes: the cluster kernel needs no scratch at all
     return launch_decode_cluster_t<16, false>(A, A_scale_t, B_t, B_scale_t, C, C_scale_t, M, N, K, cluster, info, s);
   }
-  // The array keeps whatever the previous call left.  Partial tiles are always
-  // written before they are read, but the arrival counters of the groups this
-  // call uses must start at zero.
-  LLMMM_CUDA_TRY(cudaMemsetAsync(scratch, 0, (size_t)(N / 128) * sizeof(uint32_t), s));
+  // Every call shares the array and leaves its flagged words at zero.  Only after a call whose wait ran out
+  // (llmmm_check_status reported it) may set words be left behind: then the array is cleared here first.
+  if (g_noalloc_dirty[info->device].exchange(0) != 0) {
+    LLMMM_CUDA_TRY(cudaMemsetAsync(scratch, 0, NOALLOC_BYTES, s));
+  }
   return launch_decode_t<16, false>(A, A_scale_t, B_t, B_scale_t, C, C_scale_t, M, N, K,
-                                    reinterpret_cast<uint32_t*>(scratch),
-                                    reinterpret_cast<float*>(scratch + deccfg::COUNTER_BYTES), info, s);
+                                    reinterpret_cast<uint32_t*>(scratch), info, s);
 }
 

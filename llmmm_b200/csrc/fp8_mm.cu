@@ -73,25 +73,6 @@ __device__ __forceinline__ void ffma2(float& d0, float& d1, uint32_t a0, uint32_
   d1 = __fmaf_rn(__uint_as_float(a1), sc, d1);
 }
 
-template<int REGS>
-__device__ __forceinline__ void setmaxnreg_inc()
-{
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS));
-}
-
-template<int REGS>
-__device__ __forceinline__ void setmaxnreg_dec()
-{
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS));
-}
-
-__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d)
-{
-  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
-  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
-  return lo | (hi << 16);
-}
-
 // OUT_F32 = false: C_q e4m3 + C_s;  true: C fp32, no quantisation.
 template<bool OUT_F32>
 __global__ void __launch_bounds__(fp8cfg::THREADS, 1) fp8_blockwise_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,

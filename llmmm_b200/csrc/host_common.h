@@ -60,9 +60,14 @@ int launch_decode(bool         out_f32,
                   int          K,
                   cudaStream_t stream);
 
-// Caller-owned scratch registered with llmmm_set_workspace() for a device.  Layout: arrival counters of
-// the decode kernel, arrival counters of the split tiles of the general FP8 kernel (both zero between
-// launches), then the partial tiles of whichever kernel runs.
+// Set by llmmm_check_status() when it reports a device-side wait that ran out: the decode kernel's flagged
+// partial words (registered scratch / built-in scratch) may then hold leftovers and are cleared before the next use.
+extern std::atomic<int> g_scratch_dirty[64];
+extern std::atomic<int> g_noalloc_dirty[64];
+
+// Caller-owned scratch registered with llmmm_set_workspace() for a device.  Layout: 16 KB unused, arrival
+// counters of the split tiles of the pair kernels (zero between launches), the pair kernels' partial tiles
+// (up to split_workspace_bytes()), then the decode kernel's flagged partial words (zero between launches).
 constexpr size_t WS_DECODE_COUNTER_BYTES = 16384;
 constexpr size_t WS_SK_COUNTER_BYTES     = 16384;
 constexpr size_t WS_HEADER_BYTES         = WS_DECODE_COUNTER_BYTES + WS_SK_COUNTER_BYTES;

@@ -9,6 +9,7 @@
 
 #include <cstdint>
 #include <cuda.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
 namespace llmmm {
@@ -42,6 +43,28 @@ __device__ __forceinline__ unsigned long long global_timer_ns()
 __device__ __forceinline__ uint32_t lane_id()
 {
   return threadIdx.x & 31;
+}
+
+// Warp-wide changes of the register allowance (warp-specialised kernels hand registers of their control warps
+// to the warps that hold accumulators).
+template<int REGS>
+__device__ __forceinline__ void setmaxnreg_inc()
+{
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS));
+}
+
+template<int REGS>
+__device__ __forceinline__ void setmaxnreg_dec()
+{
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS));
+}
+
+// Four floats to four e4m3 bytes (round to nearest even, saturate to +-448), first value in the low byte.
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d)
+{
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
 }
 
 // ------------------------------------------------------------- mbarrier ---

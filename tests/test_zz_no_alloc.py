@@ -6,8 +6,8 @@ agree bit for bit (this path is integer/byte output with IEEE-derived scales;
 the other FP8 tests use no looser tolerance for kernel-vs-kernel comparisons),
 on two calls in a row, since the second call meets the scratch the first one
 left behind.  The shapes are chosen so that most of them really take the
-stream-K kernel (the one that publishes partial tiles and counts arrivals in
-the built-in array) rather than the cluster kernel, which needs no scratch;
+stream-K kernel (the one that exchanges partial tiles through the built-in
+array) rather than the cluster kernel, which needs no scratch;
 the test asserts which one runs.  Collected last on purpose (file name), runs
 alone as well."""
 import numpy as np
@@ -27,7 +27,7 @@ def make_inputs(oracle, cuda, seed, M, N, K):
 
 
 # (M, N, K, kernel the launch heuristics must pick).  Order matters: the wide gate_up shape runs first and leaves
-# partial tiles and (zeroed) counters behind for the narrower ones that follow.
+# the scratch behind (all zero again, if the readers cleared what they consumed) for the narrower ones that follow.
 SHAPES = [
     (1, 19456, 2560, "stream-K"),   # 152 output groups: more than the SMs, no cluster size fits
     (16, 1280, 4096, "stream-K"),   # 10 groups: clusters of 7 would leave half of the SMs idle
