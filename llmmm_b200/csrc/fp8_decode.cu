@@ -32,8 +32,11 @@
 //   * the 1x128 output group runs across the 128 lanes in this orientation:
 //     for a whole segment the group absmax is a warp-shuffle reduction plus a
 //     4-entry exchange in shared memory between the four warps.
+#include <array>
 #include <cuda_fp8.h>
+#include <map>
 #include <mutex>
+#include <vector>
 
 #include "host_common.h"
 #include "sm100.cuh"
@@ -68,9 +71,9 @@ struct DecodeSmem {
   static constexpr uint32_t OFF_W      = 0;
   static constexpr uint32_t OFF_X      = STAGES * deccfg::W_BYTES;
   static constexpr uint32_t OFF_BAR    = OFF_X + STAGES * X_BYTES;
-  // cluster kernel: a CTA owns every c-th row of its group and receives c partials of each in its idle weight
-  // ring, c * ceil(MP / c) rows of 512 bytes
-  static_assert((MP + 8) * 512 <= STAGES * deccfg::W_BYTES, "received partial rows must fit into the idle ring");
+  // cluster kernel: the idle ring holds the CTA's own partial tile (MP rows of 512 bytes) and what it receives,
+  // c * ceil(M / c) < MP + 8 rows
+  static_assert((2 * MP + 8) * 512 <= STAGES * (deccfg::W_BYTES + X_BYTES), "partial tiles must fit into the idle ring");
   // scale products A_s[kb, m] * B_s[nb, kb] of CHUNK consecutive K-blocks of the CTA's run, [CHUNK][MP] fp32
   static constexpr int      CHUNK      = MP <= 32 ? 32 : 16;
   static constexpr uint32_t OFF_SC     = OFF_BAR + 1536;
@@ -89,6 +92,7 @@ struct DecodeBars {
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t pad[2];
+  uint64_t red;  // cluster kernel: the other CTAs' partials of this CTA's rows have landed (counted in bytes)
   float    amax[4][64];
   float    inv[64];
 };
@@ -189,14 +193,55 @@ __device__ __forceinline__ void store_group_row(float4 s, int m, int nb, void* _
   }
 }
 
-// Reduce-scatter step of one warp over up to two split groups at once.  Warp gw of a group's 4 * cnt warps owns
-// rows gw, gw + 4 cnt, ...; per pass it takes RB of its rows in each group and adds their partial tiles CB
+// Cheap wait in front of the reduction of a split group: lane j polls ONE word of contributor j's partial tile (in
+// the first row this warp owns: nobody else puts that word back to zero), so that a warp that is early does not
+// keep re-reading whole rows of every contributor -- hundreds of warps doing that would load the L2 with
+// megabytes per polling round.  Only a hint: stores may land in any order, and the reduction still checks
+// every word it uses.  Bounded like every wait.
+template<int MP>
+__device__ __forceinline__ bool wait_contributors(const SplitGroup& g, const uint32_t* partials, int lane,
+                                                  volatile uint32_t* abort_flag, uint32_t* status)
+{
+  for (int base = 0; base < g.cnt; base += 32) {
+    const int          j     = base + lane;
+    const uint32_t*    word  = partials + ((size_t)((g.c_lo + j) * 2 + (j == 0 ? 1 : 0)) * MP + g.gw) * 128 + 127;
+    unsigned long long t0    = 0;
+    uint32_t           spins = 0;
+    for (;;) {
+      uint32_t w = 1u;
+      if (j < g.cnt) {
+        asm volatile("ld.relaxed.gpu.global.b32 %0, [%1];" : "=r"(w) : "l"(word) : "memory");
+      }
+      if (__all_sync(0xffffffffu, w != 0u)) {
+        break;
+      }
+      if ((++spins & 0x7) == 0) {
+        if (*abort_flag) {
+          return false;
+        }
+        const unsigned long long now = global_timer_ns();
+        if (t0 == 0) {
+          t0 = now;
+        }
+        else if (now - t0 > WAIT_LIMIT_NS) {
+          *abort_flag = DEV_WAIT_SPLITK;
+          atomicCAS(status, 0u, (uint32_t)DEV_WAIT_SPLITK);
+          return false;
+        }
+      }
+    }
+  }
+  return true;
+}
+
+// Reduce-scatter step of one warp over NG (one or two) split groups at once.  Warp gw of a group's 4 * cnt warps
+// owns rows gw, gw + 4 cnt, ...; per pass it takes RB of its rows in each group and adds their partial tiles CB
 // contributors at a time, ascending CTA order, four columns per lane (a warp reads one 512-byte row per load
-// instruction): 2 * RB * CB loads are in flight together, so a pass costs one L2 round trip whatever the row
+// instruction): NG * RB * CB loads are in flight together, so a pass costs one L2 round trip whatever the row
 // count, repeated (bounded) while a contributor's words have not landed yet.  Then the row's
 // absmax (a warp reduction), the two divisions, and 128 bytes per row go out.  Returns false if a wait ran out.
-template<int MP, bool OUT_F32, int RB, int CB>
-__device__ __forceinline__ bool reduce_split_groups(const SplitGroup (&g)[2],
+template<int MP, bool OUT_F32, int NG, int RB, int CB>
+__device__ __forceinline__ bool reduce_split_groups(const SplitGroup (&g)[NG],
                                                     uint32_t* __restrict__ partials,
                                                     void* __restrict__ C_out,
                                                     float* __restrict__ C_s,
@@ -210,29 +255,32 @@ __device__ __forceinline__ bool reduce_split_groups(const SplitGroup (&g)[2],
   // them in a single warp's critical path cost more than the memory round trips)
   int max_cnt = 0;
 #pragma unroll
-  for (int k = 0; k < 2; ++k) {
+  for (int k = 0; k < NG; ++k) {
     max_cnt = g[k].mine ? max(max_cnt, g[k].cnt) : max_cnt;
   }
   for (int pass = 0;; ++pass) {
     // first row of this pass in either group; rows ascend with r, so nothing is left when both are beyond M
-    const bool more0 = g[0].mine && g[0].gw + pass * RB * 4 * g[0].cnt < M;
-    const bool more1 = g[1].mine && g[1].gw + pass * RB * 4 * g[1].cnt < M;
-    if (!more0 && !more1) {
+    bool more = false;
+#pragma unroll
+    for (int k = 0; k < NG; ++k) {
+      more = more || (g[k].mine && g[k].gw + pass * RB * 4 * g[k].cnt < M);
+    }
+    if (!more) {
       break;
     }
-    float4 sum[2][RB];
+    float4 sum[NG][RB];
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
+    for (int k = 0; k < NG; ++k) {
 #pragma unroll
       for (int r = 0; r < RB; ++r) {
         sum[k][r] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
       }
     }
     for (int cb = 0; cb * CB < max_cnt; ++cb) {
-      uint32_t off[2][RB][CB];  // word offset into the scratch; NONE: nothing to read for this (group, row, contributor)
+      uint32_t off[NG][RB][CB];  // word offset into the scratch; NONE: nothing to read for this (group, row, contributor)
       constexpr uint32_t NONE = 0xffffffffu;
 #pragma unroll
-      for (int k = 0; k < 2; ++k) {
+      for (int k = 0; k < NG; ++k) {
 #pragma unroll
         for (int j = 0; j < CB; ++j) {
           const int  jj   = cb * CB + j;
@@ -247,13 +295,13 @@ __device__ __forceinline__ bool reduce_split_groups(const SplitGroup (&g)[2],
           }
         }
       }
-      uint4              t[2][RB][CB];
+      uint4              t[NG][RB][CB];
       unsigned long long t0    = 0;
       uint32_t           spins = 0;
       for (;;) {
         bool landed = true;
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
+        for (int k = 0; k < NG; ++k) {
 #pragma unroll
           for (int r = 0; r < RB; ++r) {
 #pragma unroll
@@ -265,7 +313,7 @@ __device__ __forceinline__ bool reduce_split_groups(const SplitGroup (&g)[2],
           }
         }
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
+        for (int k = 0; k < NG; ++k) {
 #pragma unroll
           for (int r = 0; r < RB; ++r) {
 #pragma unroll
@@ -307,7 +355,7 @@ __device__ __forceinline__ bool reduce_split_groups(const SplitGroup (&g)[2],
         }
       }
 #pragma unroll
-      for (int k = 0; k < 2; ++k) {
+      for (int k = 0; k < NG; ++k) {
 #pragma unroll
         for (int j = 0; j < CB; ++j) {  // ascending CTA order: the result does not depend on timing
 #pragma unroll
@@ -325,7 +373,7 @@ __device__ __forceinline__ bool reduce_split_groups(const SplitGroup (&g)[2],
       }
     }
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
+    for (int k = 0; k < NG; ++k) {
 #pragma unroll
       for (int r = 0; r < RB; ++r) {
         const int m = g[k].gw + (pass * RB + r) * 4 * g[k].cnt;
@@ -342,9 +390,10 @@ __device__ __forceinline__ bool reduce_split_groups(const SplitGroup (&g)[2],
 // CLUSTER = false: stream-K over all weight blocks, partial tiles through the caller's scratch (above).
 // CLUSTER = true : one thread-block cluster per output group; CTA r of the C in the cluster takes the r-th
 //   slice of the group's K range, and the partial tiles are added through distributed shared memory as a
-//   reduce-scatter: after a cluster barrier (every CTA's TMA ring is idle) each CTA stores row i of its partial
-//   into the ring of CTA i % C, a second barrier, and every CTA adds the partials of its rows in rank order,
-//   quantises and stores them, one warp per row.  No scratch, no atomics, no global round trips; used when
+//   reduce-scatter: each CTA stages its partial tile in its own idle TMA ring; after a cluster barrier it sends
+//   every other CTA that CTA's share of the rows (bulk copies between shared memories, completion counted on the
+//   receiver's barrier), and every CTA adds the partials of its rows in rank order, quantises and stores them,
+//   one warp per row; a last cluster barrier keeps everybody until all copies are done.  No scratch, no atomics, no global round trips; used when
 //   the groups times a cluster size of 2-7 fill the GPU.
 template<int MP, bool OUT_F32, bool CLUSTER>
 __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __grid_constant__ CUtensorMap tm_w,
@@ -380,7 +429,7 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
     asm volatile("mov.u32 %0, %%cluster_nctaid.x;" : "=r"(c_size));
     c_rank = cluster_ctarank();
     const uint32_t group = blockIdx.x / c_size;
-    red_rows = ((uint32_t)MP + c_size - 1) / c_size;
+    red_rows = ((uint32_t)M + c_size - 1) / c_size;
     u_begin = group * (uint32_t)KB + (c_rank * (uint32_t)KB) / c_size;
     u_end   = group * (uint32_t)KB + ((c_rank + 1) * (uint32_t)KB) / c_size;
   }
@@ -395,6 +444,7 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
       mbar_init(&bars->part_full[s], 1);
       mbar_init(&bars->part_empty[s], 4);
     }
+    mbar_init(&bars->red, 1);
     bars->abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tm_w);
@@ -468,7 +518,7 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
     if constexpr (CLUSTER) {
       __syncwarp();
       cluster_sync_all();  // every CTA's ring is idle
-      cluster_sync_all();  // partial tiles have been delivered to the leader
+      cluster_sync_all();  // all partial rows have been delivered
     }
   }
   else if (warp < EPI_WARP0) {
@@ -586,9 +636,9 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
         mbar_wait(&bars->part_full[p], pp, DEV_WAIT_TMEM_FULL, abort_flag, status);
         PROF_KB(1);
         tc_fence_after_sync();
-        // the partial goes to registers (at most 32 columns at a time) and the stage is handed back as soon as
-        // its last column has been read, before the arithmetic on it
-        constexpr int VW = MP > 32 ? 32 : MP;
+        // the partial goes to registers and the stage is handed back as soon as its last column has been read,
+        // before the arithmetic on it
+        constexpr int VW = MP;
         const float4* srow = reinterpret_cast<const float4*>(sc + (it % CH) * MP);
 #pragma unroll
         for (int h = 0; h < MP / VW; ++h) {
@@ -624,47 +674,64 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
 
       bool finish = whole;
       if constexpr (CLUSTER) {
-        // Reduce-scatter through distributed shared memory: row i of the group belongs to CTA i % c_size, which
-        // receives every CTA's partial of that row (its own included) in its idle ring, [source rank][i / c_size][n].
-        float*         red      = reinterpret_cast<float*>(smem + L::OFF_W);
-        const uint32_t red_addr = smem_u32(red + ((size_t)c_rank * red_rows) * 128 + n_local);
-        cluster_sync_all();  // all MMAs of all CTAs are done: rings idle
+        // Reduce-scatter through distributed shared memory.  CTA o of the cluster owns rows [o R, (o+1) R) of the
+        // group, R = ceil(M / c_size).  Every CTA puts its partial tile into its own idle ring (stage[row][n]) and
+        // sends each other CTA that CTA's rows with one bulk copy (shared memory to the peer's shared memory,
+        // completion counted in bytes on the peer's barrier); plain remote stores are held to one in flight per
+        // warp and took 6 us for 64 rows.  Then one warp per owned row adds the partials in rank order.
+        float*         stage   = reinterpret_cast<float*>(smem + L::OFF_W);  // [MP][128]
+        float*         rcv     = stage + MP * 128;                           // [c_size][R][128]
+        const uint32_t R       = red_rows;
+        const uint32_t my_row0 = c_rank * R;
+        const uint32_t my_rows = (uint32_t)M > my_row0 ? min(R, (uint32_t)M - my_row0) : 0u;
+#pragma unroll
+        for (int i = 0; i < MP; ++i) {
+          if (i < M) {
+            stage[i * 128 + n_local] = acc[i];  // (this CTA's MMAs are all done: its ring is idle)
+          }
+        }
+        fence_proxy_async_smem();  // the bulk copies below read what was just written
+        if (et == 0) {
+          mbar_arrive_expect_tx(&bars->red, (c_size - 1) * my_rows * 512u);
+        }
+        cluster_sync_all();  // every CTA's ring is idle and its staging tile complete
         if (ew == 0) {
           PROF_CTA(5);
         }
-        {
-          uint32_t owner = 0, q = 0;  // i % c_size, i / c_size
-#pragma unroll
-          for (int i = 0; i < MP; ++i) {
-            if (i < M) {
-              const uint32_t dst = mapa_shared(red_addr + q * 512u, owner);
-              asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst), "f"(acc[i]) : "memory");
-            }
-            if (++owner == c_size) {
-              owner = 0;
-              ++q;
-            }
+        if (ew == 0 && (uint32_t)lane < c_size) {  // one lane per destination
+          const uint32_t o    = (uint32_t)lane;
+          const uint32_t rows = (uint32_t)M > o * R ? min(R, (uint32_t)M - o * R) : 0u;
+          if (o != c_rank && rows != 0) {
+            bulk_copy_to_peer(mapa_shared(smem_u32(rcv + (size_t)c_rank * R * 128), o), stage + (size_t)o * R * 128, rows * 512u,
+                              mapa_shared(smem_u32(&bars->red), o));
           }
         }
-        cluster_sync_all();  // release/acquire at cluster scope: the stores above are visible to their owners
+        __syncwarp();
+        if (my_rows != 0) {
+          mbar_wait(&bars->red, 0, DEV_WAIT_SPLITK, abort_flag, status);
+        }
+        // Nobody may leave while a copy can still read its staging tile or write its ring: everybody says here
+        // that its own rows have arrived, and waits for the others only after its arithmetic.
+        cluster_arrive();
         if (ew == 0) {
           PROF_CTA(6);
         }
-        // one warp per owned row: four columns per lane, the partials added in rank order
-        for (uint32_t q = (uint32_t)ew, m = c_rank + (uint32_t)ew * c_size; m < (uint32_t)M; q += 4, m += 4 * c_size) {
+        for (uint32_t q = (uint32_t)ew; q < my_rows; q += 4) {
           float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
           for (uint32_t rr = 0; rr < c_size; ++rr) {  // fixed order: the result does not depend on timing
-            const float4 t = reinterpret_cast<const float4*>(red + ((size_t)rr * red_rows + q) * 128)[lane];
+            const float* src = rr == c_rank ? stage + (size_t)(my_row0 + q) * 128 : rcv + ((size_t)rr * R + q) * 128;
+            const float4 t   = reinterpret_cast<const float4*>(src)[lane];
             sum.x += t.x;
             sum.y += t.y;
             sum.z += t.z;
             sum.w += t.w;
           }
-          store_group_row<OUT_F32>(sum, (int)m, nb, C_out, C_s, M, N, lane);
+          store_group_row<OUT_F32>(sum, (int)(my_row0 + q), nb, C_out, C_s, M, N, lane);
         }
         if (ew == 0) {
           PROF_CTA(7);
         }
+        cluster_wait();
         finish = false;
       }
       else if (!whole) {
@@ -759,15 +826,17 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
             max_cnt = max(max_cnt, g[k].cnt);
           }
         }
+        // (measured: taking one group after the other with eight rows per pass, for M > 32, was slower than
+        // several passes over both groups: 29.6 against 25.5 us for 64 x 19456 x 2560)
         if (g[0].mine || g[1].mine) {
           if (max_cnt <= 2) {
-            reduce_split_groups<MP, OUT_F32, 4, 2>(g, partials, C_out, C_s, M, N, lane, abort_flag, status);
+            reduce_split_groups<MP, OUT_F32, 2, 4, 2>(g, partials, C_out, C_s, M, N, lane, abort_flag, status);
           }
           else if (max_cnt <= 4) {
-            reduce_split_groups<MP, OUT_F32, 2, 4>(g, partials, C_out, C_s, M, N, lane, abort_flag, status);
+            reduce_split_groups<MP, OUT_F32, 2, 2, 4>(g, partials, C_out, C_s, M, N, lane, abort_flag, status);
           }
           else {
-            reduce_split_groups<MP, OUT_F32, 1, 8>(g, partials, C_out, C_s, M, N, lane, abort_flag, status);
+            reduce_split_groups<MP, OUT_F32, 2, 1, 8>(g, partials, C_out, C_s, M, N, lane, abort_flag, status);
           }
         }
         if (ew == 0) {
@@ -1027,6 +1096,42 @@ int choose_cluster(const DeviceInfo* info, int M, int N, int K)
   }
   return 0;
 }
+
+// Choices measured by llmmm_tune (tune_decode below): (device, padded M, N, K) -> cluster size, 0 = stream-K.
+std::map<std::array<int, 4>, int> g_plan_table;
+std::mutex                        g_plan_mutex;
+
+bool cluster_fits(const DeviceInfo* info, int mp, int N, int K, int size)
+{
+  const int groups = N / 128, kb = K / 128;
+  return kb >= size && groups * size <= info->sm_count && cluster_capacity(info, size, mp) >= groups;
+}
+
+bool scratch_fits(const DeviceInfo* info, int M)
+{
+  const Workspace ws = registered_workspace(info->device);
+  return ws.ptr != nullptr && ws.bytes >= decode_workspace_bytes(M);
+}
+
+// The cluster size a call gets (0: stream-K): the measured choice if llmmm_tune has seen this (N, K) on this
+// device, else the closed-form one.  A measured "stream-K" is ignored while no scratch is registered.
+int planned_cluster(const DeviceInfo* info, int M, int N, int K, bool* tuned)
+{
+  {
+    std::lock_guard<std::mutex> lock(g_plan_mutex);
+    const auto                  it = g_plan_table.find({info->device, padded_m(M), N, K});
+    if (it != g_plan_table.end() && (it->second != 0 || scratch_fits(info, M))) {
+      if (tuned != nullptr) {
+        *tuned = true;
+      }
+      return it->second;
+    }
+  }
+  if (tuned != nullptr) {
+    *tuned = false;
+  }
+  return choose_cluster(info, M, N, K);
+}
 }  // namespace
 
 bool describe_decode_plan(const DeviceInfo* info, int M, int N, int K, char* buf, size_t len)
@@ -1034,11 +1139,14 @@ bool describe_decode_plan(const DeviceInfo* info, int M, int N, int K, char* buf
   if (M > 64 || N / 128 > deccfg::MAX_GROUPS || (long long)(N / 128) * (K / 128) * 256 >= (1ll << 31)) {
     return false;
   }
-  const int mp = padded_m(M);
-  if (const int cluster = choose_cluster(info, M, N, K)) {
+  const int   mp    = padded_m(M);
+  bool        tuned = false;
+  const int   cluster = planned_cluster(info, M, N, K, &tuned);
+  const char* how     = tuned ? "measured by llmmm_tune" : "default rule";
+  if (cluster != 0) {
     snprintf(buf, len, "fp8_decode_kernel<%d, cluster>: %d output groups x clusters of %d CTAs, each CTA streams %d or %d of the "
-             "%d K-blocks; reduction through distributed shared memory, no scratch", mp, N / 128, cluster, (K / 128) / cluster,
-             (K / 128 + cluster - 1) / cluster, K / 128);
+             "%d K-blocks; reduce-scatter through distributed shared memory, no scratch (choice: %s)", mp, N / 128, cluster,
+             (K / 128) / cluster, (K / 128 + cluster - 1) / cluster, K / 128, how);
     return true;
   }
   const Workspace ws = registered_workspace(info->device);
@@ -1049,7 +1157,8 @@ bool describe_decode_plan(const DeviceInfo* info, int M, int N, int K, char* buf
   long long       G = info->sm_count < deccfg::MAX_CTAS ? info->sm_count : deccfg::MAX_CTAS;
   G                 = G < U ? G : U;
   snprintf(buf, len, "fp8_decode_kernel<%d, stream-K>: %lld weight blocks of 128x128 over %lld CTAs (%.1f each), partial tiles "
-           "through the registered scratch, last-arriving CTA reduces", mp, U, G, (double)U / (double)G);
+           "through the registered scratch, rows of a cut group reduced by its contributors' warps (choice: %s)", mp, U, G,
+           (double)U / (double)G, how);
   return true;
 }
 
@@ -1083,7 +1192,8 @@ int launch_decode(bool         out_f32,
                   int          M,
                   int          N,
                   int          K,
-                  cudaStream_t stream)
+                  cudaStream_t stream,
+                  int          force_cluster)
 {
   if (M > 64 || N / 128 > deccfg::MAX_GROUPS || (long long)(N / 128) * (K / 128) * 256 >= (1ll << 31)) {
     return -1;
@@ -1093,7 +1203,7 @@ int launch_decode(bool         out_f32,
     return LLMMM_ERR_UNSUPPORTED;
   }
   const int mp = padded_m(M);
-  if (const int cluster = choose_cluster(info, M, N, K)) {
+  if (const int cluster = force_cluster >= 0 ? force_cluster : planned_cluster(info, M, N, K, nullptr)) {
 #define LLMMM_DECODE_CLUSTER_CASE(MPV)                                                                                 \
   if (mp == MPV) {                                                                                                     \
     return out_f32 ? launch_decode_cluster_t<MPV, true>(A, A_s, B, B_s, C, C_s, M, N, K, cluster, info, stream) :      \
@@ -1125,6 +1235,105 @@ int launch_decode(bool         out_f32,
   return -1;
 }
 
+
+// The search behind llmmm_tune for decode-sized FP8 calls on an [N, K] weight (the reference declares
+// tune(N, K) on its planned functor and lists auto-tuning as to do: src/mm/fp32/impl.h:20, README.md:22).
+// For M = 16, 32 and 64 (the three activation tile widths) every plan that fits is timed with CUDA events on
+// a private stream: stream-K through the registered scratch (if one large enough is registered) and
+// clusters of 2..7 CTAs per output group.  Weights rotate over copies that together exceed the L2 cache, as
+// they do in a model whose layers are visited in turn.  The winner goes into the plan table.
+int tune_decode(const DeviceInfo* info, int N, int K)
+{
+  if (N < 128 || K < 128 || (N % 128) != 0 || (K % 128) != 0) {
+    return set_error(LLMMM_ERR_SHAPE, "N or K are not aligned. (need N%%128==0, K%%128==0; got %d %d)", N, K);
+  }
+  if (N / 128 > deccfg::MAX_GROUPS || (long long)(N / 128) * (K / 128) * 256 >= (1ll << 31)) {
+    return LLMMM_OK;  // not a decode shape: nothing to choose
+  }
+  const size_t w_bytes = (size_t)N * K;
+  int          copies  = (int)((size_t(256) << 20) / w_bytes) + 1;
+  copies               = copies < 2 ? 2 : (copies > 64 ? 64 : copies);
+  uint8_t *B = nullptr, *A = nullptr, *C = nullptr;
+  float *  B_s = nullptr, *A_s = nullptr, *C_s = nullptr;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t  e0 = nullptr, e1 = nullptr;
+  const size_t bs_bytes = (size_t)(N / 128) * (K / 128) * sizeof(float);
+  const size_t as_bytes = (size_t)(K / 128) * 64 * sizeof(float);
+  const size_t cs_bytes = (size_t)(N / 128) * 64 * sizeof(float);
+  auto cleanup = [&]() {
+    cudaFree(B);
+    cudaFree(A);
+    cudaFree(C);
+    cudaFree(B_s);
+    cudaFree(A_s);
+    cudaFree(C_s);
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    if (stream) cudaStreamDestroy(stream);
+  };
+  cudaError_t err = cudaMalloc(&B, w_bytes * copies);
+  if (err == cudaSuccess) err = cudaMalloc(&A, (size_t)64 * K);
+  if (err == cudaSuccess) err = cudaMalloc(&C, (size_t)64 * N);
+  if (err == cudaSuccess) err = cudaMalloc(&B_s, bs_bytes);
+  if (err == cudaSuccess) err = cudaMalloc(&A_s, as_bytes);
+  if (err == cudaSuccess) err = cudaMalloc(&C_s, cs_bytes);
+  if (err == cudaSuccess) err = cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking);
+  if (err == cudaSuccess) err = cudaEventCreate(&e0);
+  if (err == cudaSuccess) err = cudaEventCreate(&e1);
+  // 0x38 is 1.0 in e4m3; a float made of 0x3c bytes is 0.0115: any finite values do, the time does not depend on them
+  if (err == cudaSuccess) err = cudaMemsetAsync(B, 0x38, w_bytes * copies, stream);
+  if (err == cudaSuccess) err = cudaMemsetAsync(A, 0x38, (size_t)64 * K, stream);
+  if (err == cudaSuccess) err = cudaMemsetAsync(B_s, 0x3c, bs_bytes, stream);
+  if (err == cudaSuccess) err = cudaMemsetAsync(A_s, 0x3c, as_bytes, stream);
+  if (err != cudaSuccess) {
+    cleanup();
+    cudaGetLastError();
+    return set_error(LLMMM_ERR_CUDA, "llmmm_tune needs %zu bytes of temporary device memory: %s", w_bytes * copies,
+                     cudaGetErrorString(err));
+  }
+  int rc = LLMMM_OK;
+  for (int mp = 16; mp <= 64 && rc == LLMMM_OK; mp *= 2) {
+    std::vector<int> candidates;
+    if (scratch_fits(info, mp)) {
+      candidates.push_back(0);
+    }
+    for (int size = 2; size <= 7; ++size) {
+      if (cluster_fits(info, mp, N, K, size)) {
+        candidates.push_back(size);
+      }
+    }
+    int   best    = -1;
+    float best_ms = 0.0f;
+    for (const int cand : candidates) {
+      float cand_ms = -1.0f;
+      for (int rep = 0; rep < 4 && rc == LLMMM_OK; ++rep) {  // the first pass warms up
+        cudaEventRecord(e0, stream);
+        for (int c = 0; c < copies && rc == LLMMM_OK; ++c) {
+          rc = launch_decode(false, A, A_s, B + (size_t)c * w_bytes, B_s, C, C_s, mp, N, K, stream, cand);
+        }
+        cudaEventRecord(e1, stream);
+        if (cudaEventSynchronize(e1) != cudaSuccess) {
+          rc = set_error(LLMMM_ERR_CUDA, "llmmm_tune: a timed launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        }
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (rep > 0 && (cand_ms < 0.0f || ms < cand_ms)) {
+          cand_ms = ms;
+        }
+      }
+      if (rc == LLMMM_OK && cand_ms >= 0.0f && (best < 0 || cand_ms < best_ms)) {
+        best    = cand;
+        best_ms = cand_ms;
+      }
+    }
+    if (rc == LLMMM_OK && best >= 0) {
+      std::lock_guard<std::mutex> lock(g_plan_mutex);
+      g_plan_table[{info->device, mp, N, K}] = best;
+    }
+  }
+  cleanup();
+  return rc;
+}
 }  // namespace llmmm
 
 extern "C" {
@@ -1265,7 +1474,7 @@ extern "C" int llmmm_fp8_blockwise_mm_e4m3out_noalloc(const void*    A,
     return rc;
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (const int cluster = choose_cluster(info, M, N, K)) {
+  if (const int cluster = planned_cluster(info, M, N, K, nullptr)) {
     // same choice as llmmm_fp8_blockwise_mm_e4m3out makes: the cluster kernel needs no scratch at all
     return launch_decode_cluster_t<16, false>(A, A_scale_t, B_t, B_scale_t, C, C_scale_t, M, N, K, cluster, info, s);
   }

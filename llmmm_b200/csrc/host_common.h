@@ -47,7 +47,8 @@ bool make_tmap_2d(CUtensorMap*        out,
                   CUtensorMapSwizzle  swizzle);
 
 // Decode-sized (M <= 64) split-K FP8 path (fp8_decode.cu).  Returns -1 when it
-// does not apply, otherwise an LLMMM_* status.
+// does not apply, otherwise an LLMMM_* status.  force_cluster >= 0 overrides the planned choice
+// (0: stream-K through the registered scratch, 2..7: clusters of that size); the tuner uses it.
 int launch_decode(bool         out_f32,
                   const void*  A,
                   const float* A_s,
@@ -58,7 +59,11 @@ int launch_decode(bool         out_f32,
                   int          M,
                   int          N,
                   int          K,
-                  cudaStream_t stream);
+                  cudaStream_t stream,
+                  int          force_cluster = -1);
+// Times the candidate plans of the decode kernel for an [N, K] weight at M = 16, 32 and 64 on the current device
+// and records the winners (llmmm_tune).  Allocates and frees temporary operands.
+int tune_decode(const DeviceInfo* info, int N, int K);
 
 // Set by llmmm_check_status() when it reports a device-side wait that ran out: the decode kernel's flagged
 // partial words (registered scratch / built-in scratch) may then hold leftovers and are cleared before the next use.

@@ -1,7 +1,7 @@
-// Introspection and warm-up behind the C ABI: what the launch heuristics choose for a problem
-// (llmmm_describe_plan) and the one-time per-device set-up a first call would otherwise pay (llmmm_tune, the
-// sm_100a meaning of the tune(N, K) member the reference declares for its planned functor,
-// src/mm/fp32/impl.h:20).
+// Introspection and tuning behind the C ABI: what a call with given sizes would run (llmmm_describe_plan), and
+// llmmm_tune, the tune(N, K) member the reference declares for its planned functor (src/mm/fp32/impl.h:20): the
+// one-time per-device set-up a first call would otherwise pay, plus, for the FP8 kinds, a timed search over the
+// plans of the decode-sized kernel for that weight shape.
 #include "host_common.h"
 
 extern "C" {
@@ -40,8 +40,6 @@ int llmmm_describe_plan(int kind, int M, int N, int K, char* buf, size_t len)
 int llmmm_tune(int kind, int N, int K)
 {
   using namespace llmmm;
-  (void)N;
-  (void)K;  // the choices depend on (M, N, K) only through closed-form rules; nothing is searched or stored per shape
   const DeviceInfo* info = device_info();
   if (info == nullptr) {
     return LLMMM_ERR_UNSUPPORTED;
@@ -50,7 +48,8 @@ int llmmm_tune(int kind, int N, int K)
     return warm_fp16_kernels(info);
   }
   if (kind == LLMMM_KIND_FP8_E4M3OUT || kind == LLMMM_KIND_FP8_F32OUT) {
-    return warm_fp8_kernels(info);
+    const int rc = warm_fp8_kernels(info);
+    return rc != LLMMM_OK ? rc : tune_decode(info, N, K);
   }
   return set_error(LLMMM_ERR_UNSUPPORTED, "T is not supported. (kind %d)", kind);
 }

@@ -238,6 +238,17 @@ __device__ __forceinline__ void bulk_load(void* sdst, const void* gsrc, uint32_t
                : "memory");
 }
 
+// this CTA's shared memory -> the shared memory of a CTA of the same cluster (both given as 16-byte aligned
+// addresses, the destination and its mbarrier as shared::cluster addresses from mapa_shared); the receiver's
+// barrier gets complete_tx of `bytes`
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster_addr, const void* ssrc, uint32_t bytes, uint32_t bar_cluster_addr)
+{
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :
+               : "r"(dst_cluster_addr), "r"(smem_u32(ssrc)), "r"(bytes), "r"(bar_cluster_addr)
+               : "memory");
+}
+
 // orders accesses of the generic and the async proxy to any state space (global data handed between them)
 __device__ __forceinline__ void fence_proxy_async_all()
 {
@@ -425,6 +436,17 @@ __device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_add
 __device__ __forceinline__ void cluster_sync_all()
 {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// The two halves of cluster_sync_all(), for work that can go between them.
+__device__ __forceinline__ void cluster_arrive()
+{
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void cluster_wait()
+{
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 // TMA tile load into this CTA's shared memory whose completion is signalled on

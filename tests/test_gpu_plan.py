@@ -38,3 +38,45 @@ def test_tune_then_first_call_and_descriptions(capi, cuda):
     torch.cuda.synchronize()
     assert capi.split_launch_count() == n0 + 1
     capi.check_status()
+
+
+def _time_decode(capi, cuda, M, N, K, copies=24, reps=5):
+    """Median microseconds per launch over weight copies that together exceed L2."""
+    xq = torch.randint(0, 120, (M, K), dtype=torch.uint8, device=cuda)
+    xs = torch.rand(K // 128, M, device=cuda)
+    ws = [(torch.randint(0, 120, (N, K), dtype=torch.uint8, device=cuda), torch.rand(N // 128, K // 128, device=cuda))
+          for _ in range(copies)]
+    cq = torch.empty(M, N, dtype=torch.uint8, device=cuda)
+    cs = torch.empty(N // 128, M, device=cuda)
+    times = []
+    for _ in range(reps + 1):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for w in ws:
+            capi.fp8_blockwise_mm(xq, xs, w[0], w[1], cq, cs, M, N, K)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3 / copies)
+    return sorted(times[1:])[len(times[1:]) // 2], cq, cs
+
+
+def test_tune_measures_the_decode_plans(capi, cuda):
+    """llmmm_tune(fp8, N, K) times stream-K and every cluster size that fits for M = 16 / 32 / 64 and records
+    the winner: afterwards the plan text says so, the tuned call is not slower than the default rule's choice
+    was, and the result is the same bytes (every plan adds the partial sums of a K-block range in a fixed order;
+    the ranges differ between plans, so scales may differ in the last bit: compared through the de-quantised
+    values)."""
+    N, K = 2560, 4096
+    capi.ensure_workspace(64, N, K)
+    before = {}
+    for M in (16, 64):
+        assert "default rule" in capi.describe_plan("fp8", M, N, K)
+        before[M] = _time_decode(capi, cuda, M, N, K)
+    capi.tune("fp8", N, K)
+    for M in (16, 64):
+        assert "measured by llmmm_tune" in capi.describe_plan("fp8", M, N, K)
+        us, cq, cs = _time_decode(capi, cuda, M, N, K)
+        assert us <= before[M][0] * 1.10, (M, us, before[M][0])
+    capi.check_status()
+    # a shape the tuner has not seen keeps the default rule
+    assert "default rule" in capi.describe_plan("fp8", 16, 6144, 2560)
