@@ -85,6 +85,26 @@ def all_gather_c_n(C_q: torch.Tensor, C_s: torch.Tensor, N: int, group=None):
     return q, s
 
 
+def all_gather_c_n_blocked(C_q: torch.Tensor, C_s: torch.Tensor, group=None):
+    """N-split outputs of equal width -> (C_q blocked [R, M, N_r], C_s [N/128, M]) on every rank with one
+    all_gather_into_tensor each: rank r's slab C_q[:, n0:n1] lands as block r, unchanged, and the C_s slabs
+    concatenate along dim 0 as they are.  No transpose, padding or copy around the collective: this is the plain
+    NCCL all-gather a consumer that accepts the blocked layout pays (block r, row m holds columns
+    [r N_r, (r+1) N_r) of row m).  Uneven splits go through all_gather_c_n."""
+    world = dist.get_world_size(group)
+    out_q = torch.empty((world * C_q.shape[0], C_q.shape[1]), dtype=C_q.dtype, device=C_q.device)
+    out_s = torch.empty((world * C_s.shape[0], C_s.shape[1]), dtype=C_s.dtype, device=C_s.device)
+    dist.all_gather_into_tensor(out_q, C_q.contiguous(), group=group)
+    dist.all_gather_into_tensor(out_s, C_s.contiguous(), group=group)
+    return out_q.view(world, C_q.shape[0], C_q.shape[1]), out_s
+
+
+def unblock_c_n(C_blocked: torch.Tensor) -> torch.Tensor:
+    """[R, M, N_r] -> row-major [M, R * N_r] (one copy), for consumers that need it."""
+    R, M, Nr = C_blocked.shape
+    return C_blocked.permute(1, 0, 2).reshape(M, R * Nr)
+
+
 def all_gather_c_m(C_q: torch.Tensor, C_s: torch.Tensor, M: int, group=None):
     """M-split outputs -> full C_q[M,N] and C_s[N/128,M] on every rank."""
     world = dist.get_world_size(group)

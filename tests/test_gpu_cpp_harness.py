@@ -31,3 +31,10 @@ def test_fp16_mm_test_driver(cuda, shape):
 def test_fp8_mm_test_driver(cuda, shape):
     out = run("fp8_mm_test", *shape)
     assert "TFLOPS" in out
+
+
+def test_transpose_test_driver(cuda):
+    """The reference's transpose test (test/transpose_matrix__aligned_128_test.cc), same shapes and the same
+    element-by-element memcmp, against the drop-in header llmmm_b200/src/base/base.h."""
+    out = run("transpose_matrix__aligned_128_test")
+    assert out.count("error =     0") == 6

@@ -60,7 +60,18 @@ def _worker(rank, world, port, mode, q):
         B_q, B_s = o.quant_128x128(w)
         full_q, full_s, _ = o.fp8_blockwise_mm(A_q, A_s, B_q, B_s)
         tA_q, tA_s, tB_q, tB_s = map(torch.from_numpy, (A_q, A_s, B_q, B_s))
-        if mode == "n":
+        if mode == "nb":
+            # even split (the first two of the three groups, one per rank) gathered in the blocked layout
+            N2 = 256
+            full2_q, full2_s, _ = o.fp8_blockwise_mm(A_q, A_s, B_q[:N2], B_s[:2])
+            bq, bs = shard.shard_weights_n(tB_q[:N2], tB_s[:2], world, rank)
+            cq, cs, _ = o.fp8_blockwise_mm(A_q, A_s, bq.numpy(), bs.numpy())
+            blk, gs = shard.all_gather_c_n_blocked(torch.from_numpy(cq), torch.from_numpy(cs))
+            assert tuple(blk.shape) == (world, M, N2 // world)
+            gq = torch.cat([shard.unblock_c_n(blk), torch.from_numpy(full_q[:, N2:])], dim=1)
+            gs = torch.cat([gs, torch.from_numpy(full_s[2:])], dim=0)
+            assert (shard.unblock_c_n(blk).numpy() == full2_q).all() and (gs[:2].numpy() == full2_s).all()
+        elif mode == "n":
             bq, bs = shard.shard_weights_n(tB_q, tB_s, world, rank)
             cq, cs, _ = o.fp8_blockwise_mm(A_q, A_s, bq.numpy(), bs.numpy())
             gq, gs = shard.all_gather_c_n(torch.from_numpy(cq), torch.from_numpy(cs), N)
@@ -74,7 +85,7 @@ def _worker(rank, world, port, mode, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["n", "m"])
+@pytest.mark.parametrize("mode", ["n", "m", "nb"])
 def test_two_rank_gloo_shard_and_gather(mode, oracle):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
