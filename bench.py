@@ -35,6 +35,7 @@ WORKLOAD = ("FP8 e4m3 blockwise GEMM M=N=K=4096: A 1x128 scales, B 128x128 scale
 METRIC = "fp8_blockwise_gemm_4096_tflops"
 UNIT = "TFLOP/s"
 SETS = 6  # rotating operand sets: 6 x 49 MB = 294 MB > 126 MB L2
+REPEATS = 5  # the timed region of K steps is run this many times; the median region is the one reported
 
 
 def measured_peaks():
@@ -122,6 +123,29 @@ class ClockSampler:
         }
 
 
+def prefer_host_memory_near_gpu(index: int):
+    """Best effort, for the pinned host buffers of the end-to-end leg: ask the kernel to place this process's new
+    pages on the NUMA node the GPU hangs off (set_mempolicy(MPOL_PREFERRED); read-only for the GPU itself).  With
+    several ranks on one box each rank then copies from memory next to its own GPU instead of all from the node
+    the launcher started on.  Returns what was done, for the JSON line."""
+    import ctypes
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(index)).busId
+        bus = bus.decode() if isinstance(bus, bytes) else bus
+        path = Path("/sys/bus/pci/devices") / bus[-12:].lower() / "numa_node"
+        node = int(path.read_text())
+        if node < 0:
+            return {"numa_node": None, "policy": "unchanged (the platform reports no NUMA node for the GPU)"}
+        libc = ctypes.CDLL(None, use_errno=True)
+        mask = ctypes.c_ulong(1 << node)
+        rc = libc.syscall(238, 1, ctypes.byref(mask), ctypes.c_ulong(64))  # x86-64 set_mempolicy, MPOL_PREFERRED
+        return {"numa_node": node, "policy": "preferred" if rc == 0 else f"unchanged (set_mempolicy errno {ctypes.get_errno()})"}
+    except Exception as e:  # noqa: BLE001
+        return {"numa_node": None, "policy": "unchanged (" + repr(e)[:80] + ")"}
+
+
 # --------------------------------------------------------------- reference --
 
 def reference_arm(args) -> int:
@@ -182,7 +206,7 @@ def main() -> int:
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
-    args.warmup = max(args.warmup, 3)
+    args.warmup = max(args.warmup, SETS)  # every operand set is touched before the clock starts
 
     import torch
     import torch.distributed as dist
@@ -235,21 +259,24 @@ def main() -> int:
     sampler.start()
     for i in range(args.warmup):
         step(i)
-    barrier()
     launches0 = capi.launch_count()
     split0 = capi.split_launch_count()
     e0 = torch.cuda.Event(enable_timing=True)
     e1 = torch.cuda.Event(enable_timing=True)
     t_begin = time.perf_counter()
-    e0.record(stream)
-    for i in range(args.steps):
-        step(i)
-    e1.record(stream)
-    torch.cuda.synchronize()
-    launches = capi.launch_count() - launches0
-    split_launches = capi.split_launch_count() - split0  # launches that cut the tiles of their last wave along K
+    region_ms = []
+    for _ in range(REPEATS):
+        barrier()
+        e0.record(stream)
+        for i in range(args.steps):
+            step(i)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        region_ms.append(e0.elapsed_time(e1))
+    launches = (capi.launch_count() - launches0) // REPEATS  # per region of K steps
+    split_launches = (capi.split_launch_count() - split0) // REPEATS  # launches that cut the tiles of their last wave along K
     barrier()
-    ms_total = e0.elapsed_time(e1)
+    ms_total = statistics.median(region_ms)
     # sustained loop of the same kernel (about 1 s) so that the clock samples are taken under load
     t_load = time.perf_counter()
     reps = 0 if args.quick else max(200, int(1.0 / max(ms_total / args.steps * 1e-3, 1e-6)))
@@ -273,6 +300,7 @@ def main() -> int:
 
     # ---- end to end through the public API with host buffers (pinned), copies inside the timed region
     A_q, A_s, B_q, B_s, C_q, C_s = sets[0]
+    host_numa = prefer_host_memory_near_gpu(local)
     host_in = [t.cpu().pin_memory() for t in (A_q, A_s, B_q, B_s)]
     host_out = [torch.empty_like(t, device="cpu").pin_memory() for t in (C_q, C_s)]
     h2d = sum(t.numel() * t.element_size() for t in host_in)
@@ -310,9 +338,9 @@ def main() -> int:
     achieved = FLOP_PER_STEP / (ms_step * 1e-3) / 1e12
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
-        # dram__bytes_read.sum + dram__bytes_write.sum of this kernel on this workload, one ncu capture
-        # (profiles/fp8_blockwise_gemm_4096.md): 34.17 MB + 2.56 MB
         "traffic": 36.7e6,
+        "traffic_source": "dram__bytes_read.sum 34.17 MB + dram__bytes_write.sum 2.56 MB of one launch of this kernel on this "
+                          "workload, from one ncu --set full capture (not re-measured by this run)",
         "peak_source": f"2 x bf16_tflops ({peak_kind}; the file has no fp8 figure; burst, kernel timed alone)",
         "frac_of_nominal_4500": achieved / 4500.0,
         "kernel": "fp8_blockwise_gemm_pair_kernel<EPI_E4M3>",
@@ -326,17 +354,19 @@ def main() -> int:
                    "scratch": f"{capi.fp8_workspace_bytes(M, N, K)} bytes registered with llmmm_set_workspace"},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms, "steps": e2e_steps},
+                "ms_per_step": e2e_ms, "steps": e2e_steps, "host_memory": host_numa},
         "gpu_launches": launches,
         "split_launches": split_launches,
         "ms_per_step_fastest_rank": ms_fastest_rank,  # ms_per_step is the slowest rank's (the ranks do not communicate)
+        "repeats": REPEATS,  # ms_per_step is the median over this many timed regions of `steps` launches each
+        "ms_per_step_of_each_region_rank0": [t / args.steps for t in region_ms],
         "roofline": roofline,
     }
 
     if world > 1 and not args.no_extra and not args.quick:
         ns = nsplit_config(torch, dist, capi, dev, rank, world)
         if rank == 0:
-            line["extra"] = {"mlp7b_gate_up_nsplit": ns}
+            line["extra"] = {"mlp7b_split": ns}
     if rank == 0 and world == 1 and not args.no_extra and not args.quick:
         line["extra"] = extra_configs(torch, capi, dev, peaks)
     if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.quick:
@@ -397,6 +427,41 @@ def time_graph(torch, fn_list, iters=5):
     return statistics.median(times)
 
 
+def reference_kernels(torch, capi, dev, fp16_sets, our_fp16_us):
+    """Times the reference's own GPU kernels (the unmodified sources compiled for sm_100a into oracle/_ref by
+    oracle/Makefile: LLMMM::fp16_mm<half>, src/mm/fp16/mm.cu:7-42, and the two fused FP8 launchers
+    examples/005.fp8.mm.cu:2499-2577) at 4096^3 beside this library on the same operands.  A bench-side
+    comparison like the CPU baseline: nothing under oracle/ is on the product path."""
+    import ctypes
+    so = ROOT / "oracle" / "_ref" / "libllmmm_ref.so"
+    if not so.exists():
+        return {"unavailable": "oracle/_ref/libllmmm_ref.so was not built (needs the reference checkout at build time)"}
+    ref = ctypes.CDLL(str(so))
+    vp = ctypes.c_void_p
+    res = {}
+    fns = [(lambda s=s: ref.ref_fp16_mm_f16(vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(s[2].data_ptr()), 4096, 4096, 4096,
+                                                vp(torch.cuda.current_stream().cuda_stream)))
+           for s in fp16_sets] * 4
+    ms = time_graph(torch, fns)
+    res["ref_fp16_mm_f16"] = {"us": ms * 1e3, "tflops": 2.0 * 4096 ** 3 / (ms * 1e-3) / 1e12, "ours_us": our_fp16_us,
+                              "speedup_ours": ms * 1e3 / our_fp16_us}
+    sets = []
+    for _ in range(3):
+        A = torch.randint(0, 120, (4096, 4096), dtype=torch.uint8, device=dev)
+        B = torch.randint(0, 120, (4096, 4096), dtype=torch.uint8, device=dev)
+        sets.append((A, torch.rand(32, 4096, device=dev), B, torch.rand(32, 32, device=dev),
+                     torch.empty(4096, 4096, dtype=torch.uint8, device=dev), torch.empty(32, 4096, device=dev)))
+    capi.ensure_workspace(4096, 4096, 4096)
+    ours = time_graph(torch, [(lambda s=s: capi.fp8_blockwise_mm(*s, 4096, 4096, 4096)) for s in sets] * 4)
+    for name in ("ref_fp8_mm_opt_reg", "ref_fp8_mm_inner_split"):
+        fn = getattr(ref, name)
+        ms = time_graph(torch, [(lambda s=s: fn(*(vp(t.data_ptr()) for t in s), 4096, 4096, 4096,
+                                                 vp(torch.cuda.current_stream().cuda_stream))) for s in sets] * 4)
+        res[name] = {"us": ms * 1e3, "tflops": 2.0 * 4096 ** 3 / (ms * 1e-3) / 1e12, "ours_us": ours * 1e3,
+                     "speedup_ours": ms / ours}
+    return res
+
+
 def extra_configs(torch, capi, dev, peaks):
     """Secondary configurations of the same path: FP16 4096^3 and the Qwen3-4B decode shapes."""
     out = {}
@@ -414,6 +479,55 @@ def extra_configs(torch, capi, dev, peaks):
     out["fp16_gemm_4096"] = {"us": ms * 1e3, "tflops": tf, "frac_of_measured_bf16_burst": tf / float(peaks["bf16_tflops"]),
                              "frac_of_nominal_2250": tf / 2250.0}
     del sets, fns
+    # the same FP16 problem through torch.matmul (cuBLAS): a sanity figure for this box and its power state, not
+    # part of the product path
+    sets = []
+    for _ in range(3):
+        A = (torch.rand(4096, 4096, device=dev, generator=gen) * 2 - 1).half()
+        B = (torch.rand(4096, 4096, device=dev, generator=gen) * 2 - 1).half()
+        sets.append((A, B, torch.empty(4096, 4096, device=dev, dtype=torch.float16)))
+    ms_cublas = time_graph(torch, [(lambda s=s: torch.matmul(s[0], s[1], out=s[2])) for s in sets] * 8)
+    out["fp16_gemm_4096"]["torch_matmul_us"] = ms_cublas * 1e3
+    out["fp16_gemm_4096"]["torch_matmul_tflops"] = 2.0 * 4096 ** 3 / (ms_cublas * 1e-3) / 1e12
+    out["fp16_gemm_4096"]["ours_over_torch_matmul"] = ms_cublas / ms
+    # ... and the reference project's own kernels, rebuilt unmodified for sm_100a (mma.sync / ldmatrix; oracle/_ref,
+    # present only if the reference checkout was there at build time), on the same 4096^3 problems
+    out["reference_kernels_4096"] = reference_kernels(torch, capi, dev, sets, out["fp16_gemm_4096"]["us"])
+    del sets
+    # the four Qwen3-4B linears at prefill size (M = 4096)
+    pre = []
+    for name, (n, k) in (("qkv", (6144, 2560)), ("o", (2560, 4096)), ("gate_up", (19456, 2560)), ("down", (2560, 9728))):
+        m = 4096
+        ws = [(torch.randint(0, 120, (n, k), dtype=torch.uint8, device=dev), torch.rand(n // 128, k // 128, device=dev))
+              for _ in range(3)]
+        xq = torch.randint(0, 120, (m, k), dtype=torch.uint8, device=dev)
+        xs = torch.rand(k // 128, m, device=dev)
+        Cq = torch.empty(m, n, dtype=torch.uint8, device=dev)
+        Cs = torch.empty(n // 128, m, device=dev)
+        capi.ensure_workspace(m, n, k)
+        ms_p = time_graph(torch, [(lambda w=w: capi.fp8_blockwise_mm(xq, xs, w[0], w[1], Cq, Cs, m, n, k)) for w in ws] * 4)
+        tf_p = 2.0 * m * n * k / (ms_p * 1e-3) / 1e12
+        pre.append({"linear": name, "M": m, "N": n, "K": k, "us": ms_p * 1e3, "tflops": tf_p,
+                    "frac_of_2x_measured_bf16_burst": tf_p / (2.0 * float(peaks["bf16_tflops"]))})
+        del ws
+    out["qwen3_4b_prefill"] = pre
+    # the two 7B-scale MLP GEMMs at M = 8192 on ONE GPU (the 1-rank point of the N-split configuration)
+    mlp7 = []
+    for name, (n, k) in (("gate_up", (37888, 3584)), ("down", (3584, 18944))):
+        m = 8192
+        ws = [(torch.randint(0, 120, (n, k), dtype=torch.uint8, device=dev), torch.rand(n // 128, k // 128, device=dev))
+              for _ in range(2)]
+        xq = torch.randint(0, 120, (m, k), dtype=torch.uint8, device=dev)
+        xs = torch.rand(k // 128, m, device=dev)
+        Cq = torch.empty(m, n, dtype=torch.uint8, device=dev)
+        Cs = torch.empty(n // 128, m, device=dev)
+        capi.ensure_workspace(m, n, k)
+        ms_p = time_graph(torch, [(lambda w=w: capi.fp8_blockwise_mm(xq, xs, w[0], w[1], Cq, Cs, m, n, k)) for w in ws] * 3)
+        tf_p = 2.0 * m * n * k / (ms_p * 1e-3) / 1e12
+        mlp7.append({"gemm": name, "M": m, "N": n, "K": k, "ranks": 1, "ms": ms_p, "tflops": tf_p,
+                     "frac_of_2x_measured_bf16_burst": tf_p / (2.0 * float(peaks["bf16_tflops"]))})
+        del ws, xq, xs, Cq, Cs
+    out["mlp7b_one_gpu"] = mlp7
     # decode shapes (HBM-bound): rotate over enough weight copies to exceed L2
     dec = []
     for (n, k) in [(6144, 2560), (2560, 4096), (19456, 2560), (2560, 9728)]:
@@ -546,24 +660,13 @@ def extra_configs(torch, capi, dev, peaks):
 
 
 def nsplit_config(torch, dist, capi, dev, rank, world):
-    """Config 5 of the task (7B-scale gate_up, M=8192, N=37888, K=3584) N-split over the ranks on 128-column
-    group boundaries, replicated activations: per-rank GEMM time, and the optional NCCL all-gather of C_q / C_s."""
+    """Config 5 of the task: the two 7B-scale MLP GEMMs at M = 8192 partitioned over the ranks.
+    gate_up (N = 37888, K = 3584): N-split on 128-column group boundaries, replicated activations; per-rank GEMM,
+    GEMM + NCCL all-gather of C_q / C_s into the blocked [ranks][M][N_r] layout (all_gather_into_tensor, nothing
+    around the collective), and the GEMM that does the gather itself with peer stores from its epilogue.
+    down (N = 3584 = 28 groups, K = 18944): N-split (uneven over 8 ranks) beside an M-split of the same GEMM."""
     from llmmm_b200 import shard
-    Mm, Nn, Kk = 8192, 37888, 3584
-    n0, n1 = shard.split_n(Nn, world, rank)
-    nr = n1 - n0
-    gen = torch.Generator(device=dev).manual_seed(11 + rank)
-    A_q = torch.randint(0, 120, (Mm, Kk), dtype=torch.uint8, device=dev, generator=gen)
-    A_s = torch.rand(Kk // 128, Mm, device=dev, generator=gen)
-    B_q = torch.randint(0, 120, (nr, Kk), dtype=torch.uint8, device=dev, generator=gen)
-    B_s = torch.rand(nr // 128, Kk // 128, device=dev, generator=gen)
-    C_q = torch.empty(Mm, nr, dtype=torch.uint8, device=dev)
-    C_s = torch.empty(nr // 128, Mm, device=dev)
-
-    capi.ensure_workspace(Mm, nr, Kk)
-
-    def gemm():
-        capi.fp8_blockwise_mm(A_q, A_s, B_q, B_s, C_q, C_s, Mm, nr, Kk)
+    Mm = 8192
 
     def timed(fn, n):
         for _ in range(2):
@@ -581,29 +684,96 @@ def nsplit_config(torch, dist, capi, dev, rank, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    gen = torch.Generator(device=dev).manual_seed(11 + rank)
+    res = {}
+
+    # ------------------------------------------------------------------ gate_up, N-split
+    Nn, Kk = 37888, 3584
+    n0, n1 = shard.split_n(Nn, world, rank)
+    nr = n1 - n0
+    even = all(shard.split_n(Nn, world, r)[1] - shard.split_n(Nn, world, r)[0] == nr for r in range(world))
+    A_q = torch.randint(0, 120, (Mm, Kk), dtype=torch.uint8, device=dev, generator=gen)
+    A_s = torch.rand(Kk // 128, Mm, device=dev, generator=gen)
+    B_q = torch.randint(0, 120, (nr, Kk), dtype=torch.uint8, device=dev, generator=gen)
+    B_s = torch.rand(nr // 128, Kk // 128, device=dev, generator=gen)
+    C_q = torch.empty(Mm, nr, dtype=torch.uint8, device=dev)
+    C_s = torch.empty(nr // 128, Mm, device=dev)
+    capi.ensure_workspace(Mm, nr, Kk)
+
+    def gemm():
+        capi.fp8_blockwise_mm(A_q, A_s, B_q, B_s, C_q, C_s, Mm, nr, Kk)
+
+    gather = (lambda: shard.all_gather_c_n_blocked(C_q, C_s)) if even else (lambda: shard.all_gather_c_n(C_q, C_s, Nn))
     ms_gemm = timed(gemm, 10)
-    ms_both = timed(lambda: (gemm(), shard.all_gather_c_n(C_q, C_s, Nn)), 5)
+    ms_both = timed(lambda: (gemm(), gather()), 5)
     flops = 2.0 * Mm * Nn * Kk
-    # the same gather done by the GEMM itself: every rank's epilogue stores its column shard into the full C of
-    # every rank (peer buffers from torch symmetric memory), checked against the NCCL-gathered result
+    sent = (world - 1) * (Mm * nr + 4 * (nr // 128) * Mm)  # bytes a rank sends (and receives) for the gather
+    g = {"shape": "M=8192 N=37888 K=3584, N-split", "ranks": world, "ms_gemm": ms_gemm,
+         "tflops_gemm_total": flops / (ms_gemm * 1e-3) / 1e12, "ms_gemm_plus_nccl_allgather": ms_both,
+         "nccl_allgather": "all_gather_into_tensor into the blocked [ranks][M][N_r] layout" if even else "padded list all_gather (uneven split)",
+         "gathered_bytes_per_rank": Mm * Nn + 4 * (Nn // 128) * Mm, "bytes_sent_per_rank": sent}
+    # The same gather done by the GEMM itself: every rank's epilogue stores its column shard into the full C of
+    # every rank (peer buffers from torch symmetric memory).  Whether the peer mapping works is agreed on by all
+    # ranks before any further collective, so that no rank waits for one that gave up.
+    po, err = None, ""
     try:
         po = shard.PeerOutputs(Mm, Nn, dev)
+    except Exception as e:  # noqa: BLE001  (a box without peer access between its GPUs)
+        err = repr(e)[:200]
+    ok = torch.tensor([1 if po is not None else 0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if bool(ok.item()):
         dq, ds = po.dsts()
         ms_fused = timed(lambda: capi.fp8_blockwise_mm_gather(A_q, A_s, B_q, B_s, dq, ds, Nn, n0, Mm, nr, Kk), 10)
         po.wait_all()
         gemm()
         q_ref, s_ref = shard.all_gather_c_n(C_q, C_s, Nn)
-        same = bool(torch.equal(po.C_q, q_ref) and torch.equal(po.C_s, s_ref))
-        ok = torch.tensor([1 if same else 0], device=dev)
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-        fused = {"ms_gemm_with_fused_gather": ms_fused, "tflops_total_with_fused_gather": flops / (ms_fused * 1e-3) / 1e12,
-                 "fused_gather_equals_nccl_gather_on_all_ranks": bool(ok.item())}
+        same = torch.tensor([1 if (torch.equal(po.C_q, q_ref) and torch.equal(po.C_s, s_ref)) else 0], device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        g.update({"ms_gemm_with_fused_gather": ms_fused, "tflops_total_with_fused_gather": flops / (ms_fused * 1e-3) / 1e12,
+                  "fused_gather_gbs_sent_per_rank": sent / (ms_fused * 1e-3) / 1e9,
+                  "fused_gather_frac_of_770_gbs_peer_copy": sent / (ms_fused * 1e-3) / 1e9 / 770.0,
+                  "fused_gather_equals_nccl_gather_on_all_ranks": bool(same.item())})
         po.close()
-    except Exception as e:  # a box without peer access between its GPUs: the NCCL figures above stand alone
-        fused = {"fused_gather_unavailable": repr(e)[:200]}
-    return {"shape": "M=8192 N=37888 K=3584, N-split", "ranks": world, "ms_gemm": ms_gemm,
-            "tflops_gemm_total": flops / (ms_gemm * 1e-3) / 1e12, "ms_gemm_plus_allgather": ms_both,
-            "gathered_bytes_per_rank": Mm * Nn + 4 * (Nn // 128) * Mm, **fused}
+        del q_ref, s_ref
+    else:
+        g["fused_gather_unavailable"] = err or "another rank could not map the peer buffers"
+    res["gate_up"] = g
+    del A_q, A_s, B_q, B_s, C_q, C_s, po
+    torch.cuda.empty_cache()
+
+    # ------------------------------------------------------------------ down, N-split beside M-split
+    Nn, Kk = 3584, 18944
+    n0, n1 = shard.split_n(Nn, world, rank)
+    nr = n1 - n0
+    m0, m1 = shard.split_m(Mm, world, rank)
+    mr = m1 - m0
+    A_q = torch.randint(0, 120, (Mm, Kk), dtype=torch.uint8, device=dev, generator=gen)
+    A_s = torch.rand(Kk // 128, Mm, device=dev, generator=gen)
+    B_q = torch.randint(0, 120, (Nn, Kk), dtype=torch.uint8, device=dev, generator=gen)
+    B_s = torch.rand(Nn // 128, Kk // 128, device=dev, generator=gen)
+    Bq_r, Bs_r = B_q[n0:n1].contiguous(), B_s[n0 // 128:n1 // 128].contiguous()
+    Aq_r, As_r = shard.shard_activations_m(A_q, A_s, world, rank)
+    Cn_q = torch.empty(Mm, nr, dtype=torch.uint8, device=dev)
+    Cn_s = torch.empty(nr // 128, Mm, device=dev)
+    Cm_q = torch.empty(mr, Nn, dtype=torch.uint8, device=dev)
+    Cm_s = torch.empty(Nn // 128, mr, device=dev)
+    capi.ensure_workspace(Mm, nr, Kk)
+    capi.ensure_workspace(mr, Nn, Kk)
+    ms_n = timed(lambda: capi.fp8_blockwise_mm(A_q, A_s, Bq_r, Bs_r, Cn_q, Cn_s, Mm, nr, Kk), 10)
+    ms_m = timed(lambda: capi.fp8_blockwise_mm(Aq_r, As_r, B_q, B_s, Cm_q, Cm_s, mr, Nn, Kk), 10)
+    ms_n_g = timed(lambda: (capi.fp8_blockwise_mm(A_q, A_s, Bq_r, Bs_r, Cn_q, Cn_s, Mm, nr, Kk),
+                            shard.all_gather_c_n(Cn_q, Cn_s, Nn)), 5)
+    ms_m_g = timed(lambda: (capi.fp8_blockwise_mm(Aq_r, As_r, B_q, B_s, Cm_q, Cm_s, mr, Nn, Kk),
+                            shard.all_gather_c_m(Cm_q, Cm_s, Mm)), 5)
+    flops = 2.0 * Mm * Nn * Kk
+    groups = [(shard.split_n(Nn, world, r)[1] - shard.split_n(Nn, world, r)[0]) // 128 for r in range(world)]
+    res["down"] = {"shape": "M=8192 N=3584 K=18944", "ranks": world, "n_split_groups_per_rank": groups,
+                   "ms_gemm_n_split": ms_n, "tflops_total_n_split": flops / (ms_n * 1e-3) / 1e12,
+                   "ms_gemm_m_split": ms_m, "tflops_total_m_split": flops / (ms_m * 1e-3) / 1e12,
+                   "ms_n_split_plus_allgather": ms_n_g, "ms_m_split_plus_allgather": ms_m_g,
+                   "faster_split": "M" if ms_m < ms_n else "N"}
+    return res
 
 
 if __name__ == "__main__":

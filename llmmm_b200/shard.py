@@ -121,7 +121,7 @@ class PeerOutputs:
     symmetric memory (`torch.distributed._symmetric_memory`: device memory created with the virtual-memory API,
     exported to the other processes of the group and mapped with access for this GPU); one process per GPU.
 
-    `dsts()` gives the destination address lists in rank order; after the GEMM, `wait_all()` (stream
+    `dsts()` gives the destination address lists (every rank once); after the GEMM, `wait_all()` (stream
     synchronisation + a barrier of the group) is the point from which every rank may read its whole C."""
 
     def __init__(self, M: int, N: int, device, group=None):
@@ -143,8 +143,11 @@ class PeerOutputs:
         dist.barrier(group=self.group)
 
     def dsts(self):
-        """(C_q destinations, C_s destinations) as raw device addresses valid on this GPU, in rank order."""
-        return list(self._hq.buffer_ptrs), list(self._hs.buffer_ptrs)
+        """(C_q destinations, C_s destinations) as raw device addresses valid on this GPU, every rank once, starting
+        with the rank after this one: the kernel stores to the destinations in list order, and if all ranks began
+        with rank 0 they would all push into the same GPU's NVLink ports at the same time."""
+        order = [(self.rank + 1 + i) % self.world for i in range(self.world)]
+        return [self._hq.buffer_ptrs[r] for r in order], [self._hs.buffer_ptrs[r] for r in order]
 
     def wait_all(self) -> None:
         torch.cuda.synchronize(self.device)
