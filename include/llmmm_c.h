@@ -140,7 +140,9 @@ size_t llmmm_fp8_swiglu_workspace_bytes(int M, int I, int K);
  *                                     y[i + 64] = x[i + 64] * cos_table[p, i] + x[i]      * sin_table[p, i]
  *   value heads pass unchanged; every head is then quantised as one 1x128 group into C [M, N] e4m3 and
  *   C_scale_t [(N/128), M] by the same rule as C above.
- *   positions [M] int32 (rows of the angle tables), cos_table / sin_table [rows, 64] fp32, weights [128] fp32.
+ *   positions [M] int32 (rows of the angle tables), cos_table / sin_table [table_rows, 64] fp32, weights [128] fp32.
+ *   A position outside [0, table_rows) is clamped to the nearest row (no access outside the tables is made) and
+ *   recorded: llmmm_check_status then returns LLMMM_ERR_DEVICE_WAIT with code 0x201.
  * Requires K%128 == 0, any M >= 1; tables, weights, A, B_t and C 16-byte aligned.  M > 64 runs one fused kernel
  * (256-row tiles, always whole: registered scratch is not used).  M <= 64 runs the
  * weight-streaming decode kernel into scratch followed by a small kernel, provided the registered scratch has
@@ -154,6 +156,7 @@ int llmmm_fp8_blockwise_mm_qk_norm_rope_e4m3out(const void*    A,
                                                 const int*     positions,
                                                 const float*   cos_table,
                                                 const float*   sin_table,
+                                                int            table_rows,
                                                 const float*   q_norm_weight,
                                                 const float*   k_norm_weight,
                                                 float          eps,
@@ -223,6 +226,46 @@ int llmmm_transpose_aligned_128(void* dst, const void* src, int M, int N, int el
 size_t llmmm_fp8_workspace_bytes(int M, int N, int K);
 int    llmmm_set_workspace(void* device_ptr, size_t bytes);
 
+/* The same scratch as an explicit argument, for hosts with several streams or threads: the call uses `workspace`
+ * (llmmm_fp8_workspace_bytes bytes, 256-byte aligned; NULL with 0 bytes = this call runs without scratch) and never
+ * looks at the buffer registered for the device, so which kernel runs depends on the arguments alone, and two
+ * streams with two buffers may overlap freely.  A buffer must be prepared once before its first use, and again
+ * after llmmm_check_status reported an expired wait: llmmm_prepare_workspace clears, asynchronously on `stream`,
+ * the parts that have to be zero between launches (every launch leaves them zero again).  No counterpart in
+ * the reference (it has no split-K, README.md:22). */
+int llmmm_prepare_workspace(void* workspace, size_t workspace_bytes, llmmm_stream_t stream);
+int llmmm_fp8_blockwise_mm_e4m3out_ws(const void*    A,
+                                      const float*   A_scale_t,
+                                      const void*    B_t,
+                                      const float*   B_scale_t,
+                                      void*          C,
+                                      float*         C_scale_t,
+                                      int            M,
+                                      int            N,
+                                      int            K,
+                                      void*          workspace,
+                                      size_t         workspace_bytes,
+                                      llmmm_stream_t stream);
+int llmmm_fp8_blockwise_mm_f32out_ws(const void*    A,
+                                     const float*   A_scale_t,
+                                     const void*    B_t,
+                                     const float*   B_scale_t,
+                                     float*         C,
+                                     int            M,
+                                     int            N,
+                                     int            K,
+                                     void*          workspace,
+                                     size_t         workspace_bytes,
+                                     llmmm_stream_t stream);
+int llmmm_fp16_mm_f16_ws(const void* A, const void* B, void* C, int M, int N, int K, void* workspace, size_t workspace_bytes,
+                         llmmm_stream_t stream);
+int llmmm_fp16_mm_bf16_ws(const void* A, const void* B, void* C, int M, int N, int K, void* workspace, size_t workspace_bytes,
+                          llmmm_stream_t stream);
+/* For every other entry point (the fused hooks, llmmm_describe_plan, llmmm_tune): binds `workspace` to the CALLING
+ * THREAD; until it is unbound (NULL, 0) every call this thread makes uses it instead of the registered buffer.
+ * One host thread per stream, each with its own bound buffer, is race-free. */
+int llmmm_bind_workspace(void* workspace, size_t workspace_bytes);
+
 /* A promise about the B_t / B_scale_t operands of later FP8 GEMM calls from this process: they are model
  * weights, never written by the kernel that runs immediately before the GEMM on the same stream.  With it
  * (enabled != 0) a decode-sized call (M <= 64) requests its first weight tiles while the preceding kernel of
@@ -284,7 +327,15 @@ int llmmm_describe_plan(int kind, int M, int N, int K, char* buf, size_t len);
 /* The tune(N, K) member of the reference's planned functor (MM_IMPL<T>::tune, src/mm/fp32/impl.h:20, a stub
  * there).  Here the per-shape choices are closed-form, so tuning is the one-time per-device set-up: function
  * attributes of every kernel of the family and the cluster occupancy queries, so that the first real call
- * (possibly inside a latency-critical loop or a stream capture) pays none of it. */
+ * (possibly inside a latency-critical loop or a stream capture) pays none of it.
+ * For the two FP8 kinds it also SEARCHES: the plans of the decode-sized kernel that fit an [N, K] weight (stream-K
+ * through the scratch registered or bound at the time, clusters of 2..7 CTAs per output group) are timed with
+ * CUDA events at M = 16, 32 and 64 over weight copies that exceed the L2 cache, and the winner is recorded per
+ * (device, M bucket, N, K); later calls with that weight shape use it and llmmm_describe_plan says "measured by
+ * llmmm_tune".  The search allocates and frees temporary operands (about 256 MB) and synchronises: call it at
+ * set-up, once per weight shape, after registering the scratch.  It also touches the decode kernels' module and
+ * looks up the built-in scratch of llmmm_fp8_blockwise_mm_e4m3out_noalloc, so a host that later hands all device
+ * memory to its own pool should call it (or one no-alloc call) before doing so. */
 int llmmm_tune(int kind, int N, int K);
 
 /* Number of kernels launched by this library in the calling process. */

@@ -46,7 +46,7 @@ def lib() -> ctypes.CDLL:
         L.llmmm_fp8_blockwise_mm_e4m3out.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
         L.llmmm_fp8_blockwise_mm_e4m3out_noalloc.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
         L.llmmm_fp8_blockwise_mm_swiglu_e4m3out.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]
-        L.llmmm_fp8_blockwise_mm_qk_norm_rope_e4m3out.argtypes = [_vp] * 11 + [ctypes.c_float, _i, _i, _i, _i, _i, _vp]
+        L.llmmm_fp8_blockwise_mm_qk_norm_rope_e4m3out.argtypes = [_vp] * 9 + [_i, _vp, _vp, ctypes.c_float, _i, _i, _i, _i, _i, _vp]
         L.llmmm_fp8_qk_norm_rope_workspace_bytes.restype = ctypes.c_size_t
         L.llmmm_fp8_qk_norm_rope_workspace_bytes.argtypes = [_i, _i, _i]
         L.llmmm_fp8_blockwise_mm_e4m3out_gather.argtypes = [_vp, _vp, _vp, _vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp),
@@ -57,6 +57,12 @@ def lib() -> ctypes.CDLL:
         L.llmmm_fp8_rmsnorm_quant_1x128.argtypes = [_vp, _vp, ctypes.c_float, _vp, _vp, _i, _i, _vp]
         L.llmmm_transpose_aligned_128.argtypes = [_vp, _vp, _i, _i, _i, _vp]
         L.llmmm_selftest_wait_expiry.argtypes = [ctypes.c_uint, _vp]
+        L.llmmm_prepare_workspace.argtypes = [_vp, ctypes.c_size_t, _vp]
+        L.llmmm_bind_workspace.argtypes = [_vp, ctypes.c_size_t]
+        L.llmmm_fp8_blockwise_mm_e4m3out_ws.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, ctypes.c_size_t, _vp]
+        L.llmmm_fp8_blockwise_mm_f32out_ws.argtypes = [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, ctypes.c_size_t, _vp]
+        for name in ("llmmm_fp16_mm_f16_ws", "llmmm_fp16_mm_bf16_ws"):
+            getattr(L, name).argtypes = [_vp, _vp, _vp, _i, _i, _i, _vp, ctypes.c_size_t, _vp]
         _lib = L
     return _lib
 
@@ -70,6 +76,8 @@ EXPORTED_SYMBOLS = (
     "llmmm_fp8_blockwise_mm_e4m3out_gather", "llmmm_fp8_rmsnorm_quant_1x128", "llmmm_fp8_swiglu_workspace_bytes",
     "llmmm_transpose_aligned_128", "llmmm_selftest_wait_expiry",
     "llmmm_fp8_blockwise_mm_qk_norm_rope_e4m3out", "llmmm_fp8_qk_norm_rope_workspace_bytes",
+    "llmmm_prepare_workspace", "llmmm_bind_workspace", "llmmm_fp8_blockwise_mm_e4m3out_ws",
+    "llmmm_fp8_blockwise_mm_f32out_ws", "llmmm_fp16_mm_f16_ws", "llmmm_fp16_mm_bf16_ws",
 )
 
 
@@ -126,6 +134,38 @@ def fp8_blockwise_mm(A_q, A_s, B_q, B_s, C_q, C_s, M: int, N: int, K: int, strea
             _dev(C_s, torch.float32), M, N, K, _stream(stream)))
 
 
+def prepare_workspace(ws: torch.Tensor, stream=None) -> None:
+    """Clears the parts of a caller-owned scratch buffer that must be zero between launches (asynchronously)."""
+    with torch.cuda.device(ws.device):
+        _check(lib().llmmm_prepare_workspace(_dev(ws), ws.numel() * ws.element_size(), _stream(stream)))
+
+
+def fp8_blockwise_mm_ws(A_q, A_s, B_q, B_s, C_q, C_s, M: int, N: int, K: int, ws, stream=None) -> None:
+    """fp8_blockwise_mm with the split-K scratch as an argument (`ws`: a prepared uint8 tensor, or None for no
+    scratch); the buffer registered for the device is ignored."""
+    with torch.cuda.device(A_q.device):
+        _check(lib().llmmm_fp8_blockwise_mm_e4m3out_ws(
+            _dev(A_q), _dev(A_s, torch.float32), _dev(B_q), _dev(B_s, torch.float32), _dev(C_q),
+            _dev(C_s, torch.float32), M, N, K, None if ws is None else _dev(ws), 0 if ws is None else ws.numel(),
+            _stream(stream)))
+
+
+def fp8_blockwise_mm_f32_ws(A_q, A_s, B_q, B_s, C, M: int, N: int, K: int, ws, stream=None) -> None:
+    with torch.cuda.device(A_q.device):
+        _check(lib().llmmm_fp8_blockwise_mm_f32out_ws(
+            _dev(A_q), _dev(A_s, torch.float32), _dev(B_q), _dev(B_s, torch.float32), _dev(C, torch.float32),
+            M, N, K, None if ws is None else _dev(ws), 0 if ws is None else ws.numel(), _stream(stream)))
+
+
+def fp16_mm_ws(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, M: int, N: int, K: int, ws, stream=None) -> None:
+    fn = {torch.float16: lib().llmmm_fp16_mm_f16_ws, torch.bfloat16: lib().llmmm_fp16_mm_bf16_ws}.get(A.dtype)
+    if fn is None:
+        raise RuntimeError("T is not supported.")
+    with torch.cuda.device(A.device):
+        _check(fn(_dev(A), _dev(B, A.dtype), _dev(C, A.dtype), M, N, K, None if ws is None else _dev(ws),
+                  0 if ws is None else ws.numel(), _stream(stream)))
+
+
 def fp8_blockwise_mm_noalloc(A_q, A_s, B_q, B_s, C_q, C_s, M: int, N: int, K: int, stream=None) -> None:
     """Decode-sized (M <= 16) FP8 blockwise GEMM whose split-K scratch is built into the
     library, for callers that cannot allocate device memory (see include/llmmm_c.h)."""
@@ -168,11 +208,15 @@ def fp8_blockwise_mm_qk_norm_rope(A_q, A_s, B_q, B_s, C_q, C_s, positions, cos, 
                                   n_q_heads: int, n_kv_heads: int, M: int, N: int, K: int, stream=None) -> None:
     """qkv projection [N, K], N = (n_q_heads + 2 n_kv_heads) * 128, with the per-head RMSNorm of query / key heads
     (weights may be None) and the rotary embedding (pairs (i, i + 64), table row positions[m]) fused in front of
-    the 1x128 output quantisation."""
+    the 1x128 output quantisation.  cos / sin are [rows, 64]; a position outside [0, rows) is clamped and reported
+    by check_status()."""
+    if cos.shape != sin.shape or cos.dim() != 2 or cos.shape[1] != 64:
+        raise RuntimeError("cos and sin must both be [rows, 64]")
     with torch.cuda.device(A_q.device):
         _check(lib().llmmm_fp8_blockwise_mm_qk_norm_rope_e4m3out(
             _dev(A_q), _dev(A_s, torch.float32), _dev(B_q), _dev(B_s, torch.float32), _dev(C_q),
             _dev(C_s, torch.float32), _dev(positions, torch.int32), _dev(cos, torch.float32), _dev(sin, torch.float32),
+            int(cos.shape[0]),
             None if q_weight is None else _dev(q_weight, torch.float32),
             None if k_weight is None else _dev(k_weight, torch.float32),
             float(eps), n_q_heads, n_kv_heads, M, N, K, _stream(stream)))

@@ -4,6 +4,8 @@
 #include <cstring>
 #include <mutex>
 
+#include <algorithm>
+
 #include "host_common.h"
 #include "pair_walk.cuh"
 #include "sm100.cuh"
@@ -226,7 +228,6 @@ SplitPlan plan_split(const DeviceInfo* info, int tiles, int k_steps, int fixed, 
   plan.split_s     = 1;
   plan.split_chunk = k_steps;
   plan.pairs       = tiles < P ? tiles : P;
-#ifndef LLMMM_NO_SPLIT
   const Workspace ws         = registered_workspace(info->device);
   const int       tail_tiles = tiles % P;
   if (ws.ptr == nullptr || ws.bytes <= WS_HEADER_BYTES || tail_tiles == 0
@@ -234,7 +235,8 @@ SplitPlan plan_split(const DeviceInfo* info, int tiles, int k_steps, int fixed, 
     return plan;
   }
   const long long slots    = (long long)((ws.bytes - WS_HEADER_BYTES) / (SPLIT_SLOT_FLOATS * sizeof(float)));
-  const long long avail    = P < slots ? P : slots;
+  // (never beyond SPLIT_MAX_PAIRS slots: the decode kernel's partial words lie behind them and must stay zero)
+  const long long avail    = std::min<long long>(std::min<long long>(P, slots), SPLIT_MAX_PAIRS);
   int             max_ways = (int)(avail / tail_tiles);
   max_ways                 = max_ways < SPLIT_MAX_WAYS ? max_ways : SPLIT_MAX_WAYS;
   int ways = 0, chunk = k_steps, best = k_steps - min_gain;
@@ -259,7 +261,6 @@ SplitPlan plan_split(const DeviceInfo* info, int tiles, int k_steps, int fixed, 
     plan.counters    = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ws.ptr) + WS_DECODE_COUNTER_BYTES);
     plan.partials    = reinterpret_cast<float*>(static_cast<uint8_t*>(ws.ptr) + WS_HEADER_BYTES);
   }
-#endif
   return plan;
 }
 
@@ -331,6 +332,9 @@ int llmmm_check_status(llmmm_stream_t stream)
     cudaMemset(info->status, 0, sizeof(word));
     llmmm::g_scratch_dirty[info->device].store(1);
     llmmm::g_noalloc_dirty[info->device].store(1);
+    if (word == llmmm::DEV_BAD_POSITION) {
+      return llmmm::set_error(LLMMM_ERR_DEVICE_WAIT, "a row position lay outside the angle tables and was clamped, code 0x%x", word);
+    }
     return llmmm::set_error(LLMMM_ERR_DEVICE_WAIT, "a device-side wait ran out, code 0x%x", word);
   }
   return LLMMM_OK;

@@ -815,4 +815,26 @@ int llmmm_fp16_mm_bf16(const void* A, const void* B, void* C, int M, int N, int 
   return llmmm::launch_fp16<__nv_bfloat16>(A, B, C, M, N, K, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int llmmm_fp16_mm_f16_ws(const void* A, const void* B, void* C, int M, int N, int K, void* workspace, size_t workspace_bytes,
+                         llmmm_stream_t stream)
+{
+  const int rc = llmmm::check_workspace_arg(workspace, workspace_bytes);
+  if (rc != LLMMM_OK) {
+    return rc;
+  }
+  llmmm::ScopedWorkspace bound(workspace, workspace_bytes);
+  return llmmm::launch_fp16<__half>(A, B, C, M, N, K, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int llmmm_fp16_mm_bf16_ws(const void* A, const void* B, void* C, int M, int N, int K, void* workspace, size_t workspace_bytes,
+                          llmmm_stream_t stream)
+{
+  const int rc = llmmm::check_workspace_arg(workspace, workspace_bytes);
+  if (rc != LLMMM_OK) {
+    return rc;
+  }
+  llmmm::ScopedWorkspace bound(workspace, workspace_bytes);
+  return llmmm::launch_fp16<__nv_bfloat16>(A, B, C, M, N, K, reinterpret_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

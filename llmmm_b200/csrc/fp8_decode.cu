@@ -958,10 +958,47 @@ size_t decode_workspace_bytes(int M)
   return split_workspace_bytes() + decode_partial_bytes(M);
 }
 
+namespace {
+thread_local Workspace t_ws;
+thread_local bool      t_ws_bound = false;
+}  // namespace
+
 Workspace registered_workspace(int device)
 {
+  if (t_ws_bound) {
+    return t_ws;
+  }
   std::lock_guard<std::mutex> lock(g_ws_mutex);
   return g_ws[device];
+}
+
+bool thread_workspace_bound()
+{
+  return t_ws_bound;
+}
+
+ScopedWorkspace::ScopedWorkspace(void* ptr, size_t bytes): prev_(t_ws), prev_bound_(t_ws_bound)
+{
+  t_ws.ptr   = ptr;
+  t_ws.bytes = ptr ? bytes : 0;
+  t_ws_bound = true;
+}
+
+ScopedWorkspace::~ScopedWorkspace()
+{
+  t_ws       = prev_;
+  t_ws_bound = prev_bound_;
+}
+
+int check_workspace_arg(const void* ptr, size_t bytes)
+{
+  if (ptr == nullptr) {
+    return bytes == 0 ? LLMMM_OK : set_error(LLMMM_ERR_SHAPE, "a null workspace must have zero bytes");
+  }
+  if (((uintptr_t)ptr & 255) != 0 || bytes < WS_HEADER_BYTES) {
+    return set_error(LLMMM_ERR_SHAPE, "workspace must be 256-byte aligned and at least %zu bytes", WS_HEADER_BYTES);
+  }
+  return LLMMM_OK;
 }
 
 template<int MP, bool OUT_F32>
@@ -1162,8 +1199,17 @@ bool describe_decode_plan(const DeviceInfo* info, int M, int N, int K, char* buf
   return true;
 }
 
+namespace {
+int noalloc_scratch(const DeviceInfo* info, uint8_t** out);  // (below: the entry point without scratch)
+}
+
 int warm_decode_kernels(const DeviceInfo* info)
 {
+  // touches this module, so that its built-in scratch exists from here on, and looks its address up
+  uint8_t* builtin = nullptr;
+  if (const int rc = noalloc_scratch(info, &builtin)) {
+    return rc;
+  }
 #define LLMMM_WARM_DECODE(MPV, F32, CL)                                                                                \
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_decode_kernel<MPV, F32, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
                                       (int)DecodeSmem<MPV>::SMEM_BYTES));
@@ -1219,8 +1265,8 @@ int launch_decode(bool         out_f32,
     return -1;
   }
   uint32_t* partials = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ws.ptr) + split_workspace_bytes());
-  if (g_scratch_dirty[info->device].exchange(0) != 0) {
-    // a wait ran out in an earlier launch (llmmm_check_status reported it): flagged words may have been left behind
+  if (!thread_workspace_bound() && g_scratch_dirty[info->device].exchange(0) != 0) {
+    // a wait ran out in an earlier launch (llmmm_check_status reported it): words may have been left behind
     LLMMM_CUDA_TRY(cudaMemsetAsync(partials, 0, ws.bytes - split_workspace_bytes(), stream));
   }
 #define LLMMM_DECODE_CASE(MPV)                                                                                         \
@@ -1359,6 +1405,40 @@ int llmmm_set_static_weights(int enabled)
   return LLMMM_OK;
 }
 
+int llmmm_prepare_workspace(void* device_ptr, size_t bytes, llmmm_stream_t stream)
+{
+  using namespace llmmm;
+  if (device_info() == nullptr) {
+    return LLMMM_ERR_UNSUPPORTED;
+  }
+  if (device_ptr == nullptr) {
+    return set_error(LLMMM_ERR_SHAPE, "null pointer argument");
+  }
+  const int rc = check_workspace_arg(device_ptr, bytes);
+  if (rc != LLMMM_OK) {
+    return rc;
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  LLMMM_CUDA_TRY(cudaMemsetAsync(device_ptr, 0, WS_HEADER_BYTES, s));
+  if (bytes > split_workspace_bytes()) {
+    LLMMM_CUDA_TRY(cudaMemsetAsync(static_cast<uint8_t*>(device_ptr) + split_workspace_bytes(), 0, bytes - split_workspace_bytes(), s));
+  }
+  return LLMMM_OK;
+}
+
+int llmmm_bind_workspace(void* device_ptr, size_t bytes)
+{
+  using namespace llmmm;
+  const int rc = check_workspace_arg(device_ptr, bytes);
+  if (rc != LLMMM_OK) {
+    return rc;
+  }
+  t_ws.ptr   = device_ptr;
+  t_ws.bytes = device_ptr ? bytes : 0;
+  t_ws_bound = device_ptr != nullptr;
+  return LLMMM_OK;
+}
+
 int llmmm_set_workspace(void* device_ptr, size_t bytes)
 {
   using namespace llmmm;
@@ -1367,8 +1447,8 @@ int llmmm_set_workspace(void* device_ptr, size_t bytes)
     return LLMMM_ERR_UNSUPPORTED;
   }
   if (device_ptr != nullptr) {
-    if (((uintptr_t)device_ptr & 255) != 0 || bytes < WS_HEADER_BYTES) {
-      return set_error(LLMMM_ERR_SHAPE, "workspace must be 256-byte aligned and at least %zu bytes", WS_HEADER_BYTES);
+    if (check_workspace_arg(device_ptr, bytes) != LLMMM_OK) {
+      return LLMMM_ERR_SHAPE;
     }
     // the arrival counters of the pair kernels' split tiles and the flagged words of the decode kernel's partial
     // tiles must start at zero; every launch leaves them at zero again

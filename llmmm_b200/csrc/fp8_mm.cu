@@ -626,10 +626,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
 
       // scale operands are fetched PREFETCH K-blocks ahead (an L2 hit under the TMA traffic takes
       // longer than one K-block); the empty asm pins their first use to their own iteration
-#ifndef LLMMM_FP8_PREFETCH
-#define LLMMM_FP8_PREFETCH 2
-#endif
-      constexpr int PREFETCH = LLMMM_FP8_PREFETCH;
+      constexpr int PREFETCH = 2;
       float         a_pf[PREFETCH], b_pf[PREFETCH], b2_pf[PREFETCH];
 #pragma unroll
       for (int j = 0; j < PREFETCH; ++j) {
@@ -833,7 +830,11 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
           // (16-byte chunks XOR-swizzled by row) and every lane reads its own row from there.
           uint8_t*  stg   = smem + (half == 0 ? OFF_A : OFF_B) + (STAGES - 1) * A_BYTES + quarter * 4096;
           asm volatile("" : "+f"(acc[127]));  // (behind the normalisation)
-          const int p_own = __ldg(rope.pos + (m_ok ? m : 0));
+          const int p_raw = __ldg(rope.pos + (m_ok ? m : 0));
+          const int p_own = min(max(p_raw, 0), rope.rows - 1);
+          if (p_own != p_raw) {
+            atomicCAS(status, 0u, (uint32_t)DEV_BAD_POSITION);  // the access outside the tables is not made
+          }
           const int part  = lane & 7;  // 0..3: cos chunk, 4..7: sin chunk
           const float* tab = part < 4 ? rope.cos : rope.sin;
 #pragma unroll
@@ -1148,11 +1149,9 @@ static int launch_fp8(const void*  A,
   if (info == nullptr) {
     return LLMMM_ERR_UNSUPPORTED;
   }
-#ifndef LLMMM_FP8_NO_PAIR
   if (fp8_use_pair_kernel(info, M, N)) {
     return launch_fp8_pair<OUT_F32>(A, A_s, B, B_s, C, C_s, M, N, K, info, stream);
   }
-#endif
   CUtensorMap tm_a, tm_b;
   if (!make_tmap_2d(&tm_a, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)M, (uint64_t)K, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B)
       || !make_tmap_2d(&tm_b, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B)) {
@@ -1295,6 +1294,47 @@ int llmmm_fp8_blockwise_mm_e4m3out(const void*    A,
   return llmmm::launch_fp8<false>(A, A_scale_t, B_t, B_scale_t, C, C_scale_t, M, N, K, s);
 }
 
+int llmmm_fp8_blockwise_mm_e4m3out_ws(const void*    A,
+                                      const float*   A_scale_t,
+                                      const void*    B_t,
+                                      const float*   B_scale_t,
+                                      void*          C,
+                                      float*         C_scale_t,
+                                      int            M,
+                                      int            N,
+                                      int            K,
+                                      void*          workspace,
+                                      size_t         workspace_bytes,
+                                      llmmm_stream_t stream)
+{
+  const int rc = llmmm::check_workspace_arg(workspace, workspace_bytes);
+  if (rc != LLMMM_OK) {
+    return rc;
+  }
+  llmmm::ScopedWorkspace bound(workspace, workspace_bytes);  // this call sees `workspace`, whatever is registered
+  return llmmm_fp8_blockwise_mm_e4m3out(A, A_scale_t, B_t, B_scale_t, C, C_scale_t, M, N, K, stream);
+}
+
+int llmmm_fp8_blockwise_mm_f32out_ws(const void*    A,
+                                     const float*   A_scale_t,
+                                     const void*    B_t,
+                                     const float*   B_scale_t,
+                                     float*         C,
+                                     int            M,
+                                     int            N,
+                                     int            K,
+                                     void*          workspace,
+                                     size_t         workspace_bytes,
+                                     llmmm_stream_t stream)
+{
+  const int rc = llmmm::check_workspace_arg(workspace, workspace_bytes);
+  if (rc != LLMMM_OK) {
+    return rc;
+  }
+  llmmm::ScopedWorkspace bound(workspace, workspace_bytes);
+  return llmmm_fp8_blockwise_mm_f32out(A, A_scale_t, B_t, B_scale_t, C, M, N, K, stream);
+}
+
 int llmmm_fp8_blockwise_mm_e4m3out_gather(const void*    A,
                                           const float*   A_scale_t,
                                           const void*    B_t,
@@ -1401,6 +1441,7 @@ int llmmm_fp8_blockwise_mm_qk_norm_rope_e4m3out(const void*    A,
                                                 const int*     positions,
                                                 const float*   cos_table,
                                                 const float*   sin_table,
+                                                int            table_rows,
                                                 const float*   q_norm_weight,
                                                 const float*   k_norm_weight,
                                                 float          eps,
@@ -1431,11 +1472,14 @@ int llmmm_fp8_blockwise_mm_qk_norm_rope_e4m3out(const void*    A,
   if (!(eps >= 0.0f)) {
     return set_error(LLMMM_ERR_SHAPE, "eps must be non-negative");
   }
+  if (table_rows < 1) {
+    return set_error(LLMMM_ERR_SHAPE, "the angle tables need at least one row (got table_rows=%d)", table_rows);
+  }
   const DeviceInfo* info = device_info();
   if (info == nullptr) {
     return LLMMM_ERR_UNSUPPORTED;
   }
-  const RopeHook hook{cos_table, sin_table, positions, q_norm_weight, k_norm_weight, eps, n_q_heads, n_kv_heads, 0};
+  const RopeHook hook{cos_table, sin_table, positions, q_norm_weight, k_norm_weight, eps, n_q_heads, n_kv_heads, table_rows};
   cudaStream_t   s = reinterpret_cast<cudaStream_t>(stream);
   if (M <= 64) {
     // Decode-sized: the weight-streaming decode kernel leaves the [M, N] accumulator in the registered scratch
@@ -1447,7 +1491,7 @@ int llmmm_fp8_blockwise_mm_qk_norm_rope_e4m3out(const void*    A,
       float*    acc = reinterpret_cast<float*>(static_cast<uint8_t*>(ws.ptr) + off);
       const int rc  = launch_decode(true, A, A_scale_t, B_t, B_scale_t, acc, nullptr, M, N, K, s);
       if (rc == LLMMM_OK) {
-        return launch_rope_quant(acc, C, C_scale_t, hook, M, N, s);
+        return launch_rope_quant(acc, C, C_scale_t, hook, M, N, info->status, s);
       }
       if (rc > 0) {
         return rc;

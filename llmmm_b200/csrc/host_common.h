@@ -81,7 +81,27 @@ struct Workspace {
   void*  ptr   = nullptr;
   size_t bytes = 0;
 };
+// The scratch a launch on the calling thread may use: the buffer bound to this thread (explicit-workspace entry
+// points, llmmm_bind_workspace) if there is one, else the one registered for the device.
 Workspace registered_workspace(int device);
+// True while the calling thread has its own scratch bound (its owner keeps it clean; the per-device "dirty" mark
+// of the registered buffer does not apply to it).
+bool thread_workspace_bound();
+
+// Binds a scratch buffer to the calling thread for the lifetime of the object (nullptr: "no scratch").
+class ScopedWorkspace {
+public:
+  ScopedWorkspace(void* ptr, size_t bytes);
+  ~ScopedWorkspace();
+  ScopedWorkspace(const ScopedWorkspace&)            = delete;
+  ScopedWorkspace& operator=(const ScopedWorkspace&) = delete;
+
+private:
+  Workspace prev_;
+  bool      prev_bound_;
+};
+// 256-byte aligned and at least the header, or null with zero bytes; sets the error text otherwise.
+int check_workspace_arg(const void* ptr, size_t bytes);
 
 // Scratch the pair kernels want for splitting the tiles of their last wave (pair_walk.cuh).
 size_t split_workspace_bytes();
@@ -104,9 +124,9 @@ struct RopeHook {
   float        eps;
   int          n_q;
   int          n_kv;
-  int          pad;
+  int          rows;  // rows of the angle tables: a position outside [0, rows) is clamped and reported in the status word
 };
-int launch_rope_quant(const float* acc, void* C, float* C_s, const RopeHook& hook, int M, int N, cudaStream_t stream);
+int launch_rope_quant(const float* acc, void* C, float* C_s, const RopeHook& hook, int M, int N, uint32_t* status, cudaStream_t stream);
 
 // What the launch heuristics choose for a problem, as text (llmmm_describe_plan), and the one-time set-up of
 // every kernel of a family on the current device (llmmm_tune): function attributes, occupancy queries.

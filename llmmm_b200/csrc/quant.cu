@@ -265,7 +265,7 @@ int launch_swiglu_quant(const float* acc, void* H, float* H_s, int M, int I, cud
 // prefill-sized kernel up to the order of the sum of squares.
 __global__ void __launch_bounds__(256)
   rope_quant_1x128_kernel(const float* __restrict__ acc, uint8_t* __restrict__ C, float* __restrict__ C_s,
-                          const __grid_constant__ RopeHook hook, int M, int N)
+                          const __grid_constant__ RopeHook hook, int M, int N, uint32_t* status)
 {
   pdl_launch_dependents();
   pdl_wait();
@@ -296,7 +296,12 @@ __global__ void __launch_bounds__(256)
       hi.x = hi.x * inv * wh.x;
       hi.y = hi.y * inv * wh.y;
     }
-    const size_t p = (size_t)__ldg(hook.pos + m) * 64;
+    const int p_raw = __ldg(hook.pos + m);
+    const int p_row = min(max(p_raw, 0), hook.rows - 1);
+    if (p_row != p_raw && lane == 0) {
+      atomicCAS(status, 0u, (uint32_t)DEV_BAD_POSITION);  // the access outside the tables is not made
+    }
+    const size_t p = (size_t)p_row * 64;
     const float2 c = __ldg(reinterpret_cast<const float2*>(hook.cos + p) + lane);
     const float2 s = __ldg(reinterpret_cast<const float2*>(hook.sin + p) + lane);
     const float2 l0 = lo, h0 = hi;
@@ -318,11 +323,12 @@ __global__ void __launch_bounds__(256)
   }
 }
 
-int launch_rope_quant(const float* acc, void* C, float* C_s, const RopeHook& hook, int M, int N, cudaStream_t stream)
+int launch_rope_quant(const float* acc, void* C, float* C_s, const RopeHook& hook, int M, int N, uint32_t* status,
+                      cudaStream_t stream)
 {
   const int warps = M * (N / 128);
   LLMMM_CUDA_TRY(launch_pdl(rope_quant_1x128_kernel, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, stream, 1, acc,
-                            static_cast<uint8_t*>(C), C_s, hook, M, N));
+                            static_cast<uint8_t*>(C), C_s, hook, M, N, status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
 }

@@ -23,6 +23,7 @@ enum : uint32_t {
   DEV_WAIT_TMEM_EMPTY = 0x104,
   DEV_WAIT_SPLITK     = 0x105,
   DEV_WAIT_SELFTEST   = 0x1ff,
+  DEV_BAD_POSITION    = 0x201,  // not a wait: a row position outside the angle tables was clamped (qkv hook)
 };
 
 // Wall-clock limit of one wait, in nanoseconds of %globaltimer.

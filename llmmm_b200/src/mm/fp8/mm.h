@@ -76,6 +76,7 @@ inline void fp8_gemm_blockwise_quant_A_1x128__B_128x128__qk_norm_rope__C_1x128__
                                                                                            const int*           positions,
                                                                                            const float*         cos_table,
                                                                                            const float*         sin_table,
+                                                                                           int                  table_rows,
                                                                                            const float*         q_norm_weight,
                                                                                            const float*         k_norm_weight,
                                                                                            float                eps,
@@ -88,7 +89,7 @@ inline void fp8_gemm_blockwise_quant_A_1x128__B_128x128__qk_norm_rope__C_1x128__
 {
   LLMMM::throw_on_error(llmmm_fp8_blockwise_mm_qk_norm_rope_e4m3out(
     A, A_scale_transposed, B_transposed, B_scale_transposed, C, C_scale_transposed, positions, cos_table, sin_table,
-    q_norm_weight, k_norm_weight, eps, n_q_heads, n_kv_heads, M, N, K, stream));
+    table_rows, q_norm_weight, k_norm_weight, eps, n_q_heads, n_kv_heads, M, N, K, stream));
 }
 
 inline void fp8_gemm_blockwise_quant_A_1x128__B_128x128__output_fp32(const __nv_fp8_e4m3* A,

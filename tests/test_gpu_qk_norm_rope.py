@@ -146,7 +146,44 @@ def test_argument_errors(capi, cuda):
     z8 = torch.zeros(128 * 512, dtype=torch.uint8, device=cuda)
     zf = torch.zeros(128 * 512, dtype=torch.float32, device=cuda)
     zi = torch.zeros(128, dtype=torch.int32, device=cuda)
+    zt = torch.zeros(16, 64, dtype=torch.float32, device=cuda)
     with pytest.raises(RuntimeError, match="n_q_heads"):
-        capi.fp8_blockwise_mm_qk_norm_rope(z8, zf, z8, zf, z8, zf, zi, zf, zf, None, None, EPS, 2, 2, 128, 512, 256)
+        capi.fp8_blockwise_mm_qk_norm_rope(z8, zf, z8, zf, z8, zf, zi, zt, zt, None, None, EPS, 2, 2, 128, 512, 256)
     with pytest.raises(RuntimeError, match="not aligned"):
-        capi.fp8_blockwise_mm_qk_norm_rope(z8, zf, z8, zf, z8, zf, zi, zf, zf, None, None, EPS, 2, 1, 128, 512, 200)
+        capi.fp8_blockwise_mm_qk_norm_rope(z8, zf, z8, zf, z8, zf, zi, zt, zt, None, None, EPS, 2, 1, 128, 512, 200)
+    with pytest.raises(RuntimeError, match=r"\[rows, 64\]"):
+        capi.fp8_blockwise_mm_qk_norm_rope(z8, zf, z8, zf, z8, zf, zi, zf, zf, None, None, EPS, 2, 1, 128, 512, 256)
+
+
+@pytest.mark.parametrize("M", [8, 256])
+def test_positions_outside_the_tables_are_clamped_and_reported(capi, cuda, M):
+    """The angle tables have `rows` rows; a position below 0 or at / beyond `rows` must not be used as an index.  The
+    kernels (the fused epilogue for M > 64, the small hook kernel for M <= 64) clamp it to the nearest row, so the
+    result equals the one for the clamped positions, and record code 0x201 in the status word."""
+    N, K, n_q, n_kv, rows = 512, 256, 2, 1, 16
+    g = torch.Generator(device=cuda).manual_seed(5)
+    A = torch.randint(0, 120, (M, K), dtype=torch.uint8, device=cuda, generator=g)
+    As = torch.rand(K // 128, M, device=cuda, generator=g)
+    B = torch.randint(0, 120, (N, K), dtype=torch.uint8, device=cuda, generator=g)
+    Bs = torch.rand(N // 128, K // 128, device=cuda, generator=g)
+    ang = torch.rand(rows, 64, device=cuda, generator=g) * 6.28
+    cos, sin = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+    pos = (torch.arange(M, device=cuda, dtype=torch.int32) % rows).contiguous()
+    bad = pos.clone()
+    bad[0], bad[M - 1] = -7, rows + 1000
+    good = bad.clamp(0, rows - 1)
+    capi.ensure_qk_norm_rope_workspace(M, N, K)
+    out = []
+    for p in (good, bad):
+        Cq = torch.zeros(M, N, dtype=torch.uint8, device=cuda)
+        Cs = torch.zeros(N // 128, M, device=cuda)
+        capi.fp8_blockwise_mm_qk_norm_rope(A, As, B, Bs, Cq, Cs, p, cos, sin, None, None, EPS, n_q, n_kv, M, N, K)
+        torch.cuda.synchronize()
+        if p is good:
+            capi.check_status()
+        else:
+            with pytest.raises(RuntimeError, match="0x201"):
+                capi.check_status()
+        out.append((Cq, Cs))
+    assert torch.equal(out[0][0], out[1][0]) and torch.equal(out[0][1], out[1][1])
+    capi.check_status()  # the word was cleared by the report
