@@ -161,8 +161,9 @@ __global__ void __launch_bounds__(256)
 }
 
 // RMSNorm fused in front of the activation quantiser: y = x * rsqrt(mean(x^2) + eps) * weight, then the 1x128
-// quantisation of y.  One CTA per row: the first pass over the row sums the squares (the row comes from HBM),
-// the second pass re-reads it from L2, scales and quantises one 128-wide group per warp at a time.
+// quantisation of y.  One CTA per row: it sums the squares, then scales and quantises one 128-wide group per
+// warp at a time.  A row of up to 8192 values is kept in registers in between (one pass over memory); a longer
+// one is re-read from L2.
 constexpr int RN_THREADS = 256;
 
 __global__ void __launch_bounds__(RN_THREADS)
@@ -176,13 +177,35 @@ __global__ void __launch_bounds__(RN_THREADS)
   const int     warp = threadIdx.x >> 5;
   const int     m    = blockIdx.x;
   const float4* row  = reinterpret_cast<const float4*>(x + (size_t)m * K);
-  float         ss   = 0.0f;
-  for (int i = threadIdx.x; i < K / 4; i += RN_THREADS) {
-    const float4 v = __ldg(row + i);
-    ss             = fmaf(v.x, v.x, ss);
-    ss             = fmaf(v.y, v.y, ss);
-    ss             = fmaf(v.z, v.z, ss);
-    ss             = fmaf(v.w, v.w, ss);
+  // Rows of up to 8192 values stay in registers between the two phases (8 float4 per thread): element
+  // threadIdx.x + 256 j of the row, as float4, is lane `lane` of the 128-wide group warp + 8 j, so the thread
+  // that read a value for the sum of squares is the one that quantises it, and x is read from memory once.
+  constexpr int RESIDENT = 8;
+  const bool    resident = K <= RESIDENT * RN_THREADS * 4;
+  float4        v[RESIDENT];
+  float         ss = 0.0f;
+  if (resident) {
+#pragma unroll
+    for (int j = 0; j < RESIDENT; ++j) {
+      const int i = threadIdx.x + j * RN_THREADS;
+      v[j]        = i < K / 4 ? __ldg(row + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+#pragma unroll
+    for (int j = 0; j < RESIDENT; ++j) {  // (zeros beyond the row add nothing: same sum, same order as below)
+      ss = fmaf(v[j].x, v[j].x, ss);
+      ss = fmaf(v[j].y, v[j].y, ss);
+      ss = fmaf(v[j].z, v[j].z, ss);
+      ss = fmaf(v[j].w, v[j].w, ss);
+    }
+  }
+  else {
+    for (int i = threadIdx.x; i < K / 4; i += RN_THREADS) {
+      const float4 t = __ldg(row + i);
+      ss             = fmaf(t.x, t.x, ss);
+      ss             = fmaf(t.y, t.y, ss);
+      ss             = fmaf(t.z, t.z, ss);
+      ss             = fmaf(t.w, t.w, ss);
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -199,19 +222,32 @@ __global__ void __launch_bounds__(RN_THREADS)
   }
   const float inv = __frsqrt_rn(__fdiv_rn(total, (float)K) + eps);
   const float4* wrow = reinterpret_cast<const float4*>(weight);
-  for (int g = warp; g < K / 128; g += RN_THREADS / 32) {
-    const float4 v = __ldg(row + g * 32 + lane);
+  auto emit = [&](int g, const float4& t) {
     const float4 w = __ldg(wrow + g * 32 + lane);
     float4       y;
-    y.x = __fmul_rn(__fmul_rn(v.x, inv), w.x);
-    y.y = __fmul_rn(__fmul_rn(v.y, inv), w.y);
-    y.z = __fmul_rn(__fmul_rn(v.z, inv), w.z);
-    y.w = __fmul_rn(__fmul_rn(v.w, inv), w.w);
+    y.x = __fmul_rn(__fmul_rn(t.x, inv), w.x);
+    y.y = __fmul_rn(__fmul_rn(t.y, inv), w.y);
+    y.z = __fmul_rn(__fmul_rn(t.z, inv), w.z);
+    y.w = __fmul_rn(__fmul_rn(t.w, inv), w.w);
     const float amax = warp_max(amax4(y));
-    const float s    = __fdiv_rn(amax, 448.0f);
-    reinterpret_cast<uint32_t*>(q + (size_t)m * K + (size_t)g * 128)[lane] = quant4(y, s);
+    const float sc   = __fdiv_rn(amax, 448.0f);
+    reinterpret_cast<uint32_t*>(q + (size_t)m * K + (size_t)g * 128)[lane] = quant4(y, sc);
     if (lane == 0) {
-      scale[(size_t)g * M + m] = s;
+      scale[(size_t)g * M + m] = sc;
+    }
+  };
+  if (resident) {
+#pragma unroll
+    for (int j = 0; j < RESIDENT; ++j) {
+      const int g = warp + j * (RN_THREADS / 32);
+      if (g < K / 128) {
+        emit(g, v[j]);
+      }
+    }
+  }
+  else {
+    for (int g = warp; g < K / 128; g += RN_THREADS / 32) {
+      emit(g, __ldg(row + g * 32 + lane));  // second pass: from L2
     }
   }
 }
