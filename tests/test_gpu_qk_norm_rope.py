@@ -7,7 +7,14 @@ relative errors, and the rotation, which mixes two values of similar size; plus 
 root, 2^-22 relative).  On the outputs: scales within 3e-5 relative of the oracle's, de-quantised values within
 the oracle's own error + 1 e4m3 ulp * scale + that bound, bytes overwhelmingly identical.  Two properties are
 bit-exact: value heads equal the plain GEMM's output, and with identity angles (cos 1, sin 0) and no norm weights
-the whole output equals the plain GEMM's."""
+the whole output equals the plain GEMM's.
+
+Budget of the approximate intrinsic in the fused epilogue (CUDA's documented maximum error): `rsqrtf` is 2 ulp =
+2.4e-7 relative, applied once per head as a common factor of its 128 values (the small hook kernel of the
+M <= 64 path uses the correctly rounded `__fsqrt_rn` / `__frcp_rn`).  The sum of squares is taken in four FMA
+chains (<= 128 * 2^-24 = 7.6e-6 relative in the worst case, 1e-6 typical) and halves under the square root.  Both
+are far inside the 3e-5 gate, whose larger part is the accumulation noise of the GEMM carried through the
+rotation."""
 import numpy as np
 import pytest
 import torch

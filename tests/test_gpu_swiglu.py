@@ -6,7 +6,13 @@ stated here: the fp32 h the kernel quantises may differ from the fp64 truth by 2
 the fast exponential / division, about 2^-21 relative).  On the outputs that means: scales within 2e-5 relative
 of the oracle's, de-quantised values within the oracle's own error + 1 e4m3 ulp * scale + that bound, bytes
 overwhelmingly identical, and the consumer property: feeding (H_q, H_s) to the down projection gives what
-feeding the oracle's (H_q, H_s) gives, within the same bound."""
+feeding the oracle's (H_q, H_s) gives, within the same bound.
+
+Budget of the approximate intrinsics in the epilogue (CUDA's documented maximum errors): `__expf(x)` is
+2 + floor(|1.173 x|) ulp -- where silu's value matters (|g| <= 16, beyond that exp(-g) is below 2^-23 of 1 or the
+result below 2^-23 of the row maximum) at most 20 ulp = 2.4e-6 relative of exp(-g), which enters h through
+1 / (1 + exp(-g)) with a weight <= 1; `__fdividef` is 2 ulp = 2.4e-7.  Together <= 2.7e-6 relative of h, well inside
+the 2e-5 gate, whose larger part is the accumulation noise of the GEMM."""
 import numpy as np
 import pytest
 import torch
