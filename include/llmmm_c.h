@@ -332,7 +332,8 @@ int llmmm_describe_plan(int kind, int M, int N, int K, char* buf, size_t len);
  * through the scratch registered or bound at the time, clusters of 2..7 CTAs per output group) are timed with
  * CUDA events at M = 16, 32 and 64 over weight copies that exceed the L2 cache, and the winner is recorded per
  * (device, M bucket, N, K); later calls with that weight shape use it and llmmm_describe_plan says "measured by
- * llmmm_tune".  The search allocates and frees temporary operands (about 256 MB) and synchronises: call it at
+ * llmmm_tune".  With the scratch registered it also times, at M = 128, the single-CTA kernel against the pair
+ * kernel and records which of the two calls of 65..128 rows with this weight shape get.  The search allocates and frees temporary operands (about 256 MB) and synchronises: call it at
  * set-up, once per weight shape, after registering the scratch.  It also touches the decode kernels' module and
  * looks up the built-in scratch of llmmm_fp8_blockwise_mm_e4m3out_noalloc, so a host that later hands all device
  * memory to its own pool should call it (or one no-alloc call) before doing so. */

@@ -5,12 +5,34 @@
 #include <mutex>
 
 #include <algorithm>
+#include <array>
+#include <map>
 
 #include "host_common.h"
 #include "pair_walk.cuh"
 #include "sm100.cuh"
 
 namespace llmmm {
+
+thread_local int t_force_mid = -1;
+
+namespace {
+std::map<std::array<int, 3>, int> g_mid_table;
+std::mutex                        g_mid_mutex;
+}  // namespace
+
+int mid_choice(int device, int N, int K)
+{
+  std::lock_guard<std::mutex> lock(g_mid_mutex);
+  const auto                  it = g_mid_table.find({device, N, K});
+  return it == g_mid_table.end() ? -1 : it->second;
+}
+
+void record_mid_choice(int device, int N, int K, int choice)
+{
+  std::lock_guard<std::mutex> lock(g_mid_mutex);
+  g_mid_table[{device, N, K}] = choice;
+}
 
 std::atomic<int> g_scratch_dirty[64];
 std::atomic<int> g_noalloc_dirty[64];

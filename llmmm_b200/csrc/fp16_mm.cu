@@ -302,7 +302,9 @@ struct Fp16PairBars {
   uint32_t abort_flag;
 };
 
-template<typename T>
+// SPLIT = false: every tile is whole; the code for the chunks of a cut tile (and its registers: that epilogue is what
+// drove the kernel to 255 registers and a spill) is left out.  The launcher picks the instantiation from its plan.
+template<typename T, bool SPLIT>
 __global__ void __launch_bounds__(fp16pair::THREADS, 1)
   fp16_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
                         const __grid_constant__ CUtensorMap tm_b,
@@ -512,7 +514,7 @@ __global__ void __launch_bounds__(fp16pair::THREADS, 1)
       mbar_wait(&bars->tmem_full[acc], acc_ph, DEV_WAIT_TMEM_FULL, abort_flag, status);
       tc_fence_after_sync();
       const uint32_t t_addr = tmem_base + acc * BN + ((uint32_t)(ew * 32) << 16);
-      if (kb1 - kb0 == k_iters) {
+      if (!SPLIT || kb1 - kb0 == k_iters) {
 #pragma unroll 1
         for (int c = 0; c < BN / 64; ++c) {
           uint32_t v0[32], v1[32];
@@ -527,6 +529,7 @@ __global__ void __launch_bounds__(fp16pair::THREADS, 1)
         }
         continue;
       }
+      if constexpr (SPLIT) {
       // A chunk of a split tile, the last piece of work of this pair.  This warp's 32x256 piece is handled
       // independently of the other warps: publish the fp32 partial sums (four columns per lane side by
       // side: 512 contiguous bytes per warp instruction), count the arrival, and if it is the last one
@@ -651,6 +654,7 @@ __global__ void __launch_bounds__(fp16pair::THREADS, 1)
         }
       }
       release_accumulator(acc);
+      }  // SPLIT
     }
     if (lane == 0) {
       tma_store_wait_all<0>();
@@ -682,16 +686,25 @@ static int launch_fp16_pair(const void* A, const void* B, void* C, int M, int N,
   static thread_local bool attr_set[64] = {};
   if (!attr_set[info->device]) {
     LLMMM_CUDA_TRY(
-      cudaFuncSetAttribute(fp16_gemm_pair_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+      cudaFuncSetAttribute(fp16_gemm_pair_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+    LLMMM_CUDA_TRY(
+      cudaFuncSetAttribute(fp16_gemm_pair_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
     attr_set[info->device] = true;
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   // estimated cost of a split, in K-steps of 64 (one takes about 0.33 us): publishing a chunk and counting
   // the arrival about 3 us, reading a chunk back about 1.5 us
   const SplitPlan plan = plan_split(info, tiles, (K + BK - 1) / BK, /*fixed*/ 10, /*per_way_x2*/ 9, /*min_gain*/ 6);
-  LLMMM_CUDA_TRY(launch_pdl(fp16_gemm_pair_kernel<T>, dim3(2 * plan.pairs), dim3(THREADS), SMEM_BYTES, stream, 2, tm_a, tm_b,
-                            tm_c, M, N, K, plan.dp_tiles, plan.split_pairs, plan.split_s, plan.split_chunk, plan.partials,
-                            plan.counters, info->status));
+  if (plan.split_pairs > 0) {
+    LLMMM_CUDA_TRY(launch_pdl(fp16_gemm_pair_kernel<T, true>, dim3(2 * plan.pairs), dim3(THREADS), SMEM_BYTES, stream, 2, tm_a,
+                              tm_b, tm_c, M, N, K, plan.dp_tiles, plan.split_pairs, plan.split_s, plan.split_chunk,
+                              plan.partials, plan.counters, info->status));
+  }
+  else {
+    LLMMM_CUDA_TRY(launch_pdl(fp16_gemm_pair_kernel<T, false>, dim3(2 * plan.pairs), dim3(THREADS), SMEM_BYTES, stream, 2, tm_a,
+                              tm_b, tm_c, M, N, K, plan.dp_tiles, plan.split_pairs, plan.split_s, plan.split_chunk,
+                              plan.partials, plan.counters, info->status));
+  }
   g_launches.fetch_add(1);
   return LLMMM_OK;
 }
@@ -740,8 +753,10 @@ void describe_fp16_plan(const DeviceInfo* info, bool bf16, int M, int N, int K, 
 int warm_fp16_kernels(const DeviceInfo* info)
 {
   (void)info;
-  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp16_gemm_pair_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp16pair::SMEM_BYTES));
-  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp16_gemm_pair_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp16pair::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp16_gemm_pair_kernel<__half, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp16pair::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp16_gemm_pair_kernel<__half, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp16pair::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp16_gemm_pair_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp16pair::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp16_gemm_pair_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp16pair::SMEM_BYTES));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp16_gemm_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp16cfg::SMEM_BYTES));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp16_gemm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp16cfg::SMEM_BYTES));
   return LLMMM_OK;

@@ -1286,16 +1286,15 @@ int launch_decode(bool         out_f32,
 // tune(N, K) on its planned functor and lists auto-tuning as to do: src/mm/fp32/impl.h:20, README.md:22).
 // For M = 16, 32 and 64 (the three activation tile widths) every plan that fits is timed with CUDA events on
 // a private stream: stream-K through the registered scratch (if one large enough is registered) and
-// clusters of 2..7 CTAs per output group.  Weights rotate over copies that together exceed the L2 cache, as
+// clusters of 2..7 CTAs per output group.  For 65..128 rows the single-CTA kernel is timed against the pair
+// kernel (at M = 128, with the scratch registered, without which the pair kernel has no case there).  Weights rotate over copies that together exceed the L2 cache, as
 // they do in a model whose layers are visited in turn.  The winner goes into the plan table.
 int tune_decode(const DeviceInfo* info, int N, int K)
 {
   if (N < 128 || K < 128 || (N % 128) != 0 || (K % 128) != 0) {
     return set_error(LLMMM_ERR_SHAPE, "N or K are not aligned. (need N%%128==0, K%%128==0; got %d %d)", N, K);
   }
-  if (N / 128 > deccfg::MAX_GROUPS || (long long)(N / 128) * (K / 128) * 256 >= (1ll << 31)) {
-    return LLMMM_OK;  // not a decode shape: nothing to choose
-  }
+  const bool decode_shape = !(N / 128 > deccfg::MAX_GROUPS || (long long)(N / 128) * (K / 128) * 256 >= (1ll << 31));
   const size_t w_bytes = (size_t)N * K;
   int          copies  = (int)((size_t(256) << 20) / w_bytes) + 1;
   copies               = copies < 2 ? 2 : (copies > 64 ? 64 : copies);
@@ -1304,8 +1303,8 @@ int tune_decode(const DeviceInfo* info, int N, int K)
   cudaStream_t stream = nullptr;
   cudaEvent_t  e0 = nullptr, e1 = nullptr;
   const size_t bs_bytes = (size_t)(N / 128) * (K / 128) * sizeof(float);
-  const size_t as_bytes = (size_t)(K / 128) * 64 * sizeof(float);
-  const size_t cs_bytes = (size_t)(N / 128) * 64 * sizeof(float);
+  const size_t as_bytes = (size_t)(K / 128) * 128 * sizeof(float);  // up to 128 rows: the 65..128-row bucket below
+  const size_t cs_bytes = (size_t)(N / 128) * 128 * sizeof(float);
   auto cleanup = [&]() {
     cudaFree(B);
     cudaFree(A);
@@ -1318,8 +1317,8 @@ int tune_decode(const DeviceInfo* info, int N, int K)
     if (stream) cudaStreamDestroy(stream);
   };
   cudaError_t err = cudaMalloc(&B, w_bytes * copies);
-  if (err == cudaSuccess) err = cudaMalloc(&A, (size_t)64 * K);
-  if (err == cudaSuccess) err = cudaMalloc(&C, (size_t)64 * N);
+  if (err == cudaSuccess) err = cudaMalloc(&A, (size_t)128 * K);
+  if (err == cudaSuccess) err = cudaMalloc(&C, (size_t)128 * N);
   if (err == cudaSuccess) err = cudaMalloc(&B_s, bs_bytes);
   if (err == cudaSuccess) err = cudaMalloc(&A_s, as_bytes);
   if (err == cudaSuccess) err = cudaMalloc(&C_s, cs_bytes);
@@ -1328,7 +1327,7 @@ int tune_decode(const DeviceInfo* info, int N, int K)
   if (err == cudaSuccess) err = cudaEventCreate(&e1);
   // 0x38 is 1.0 in e4m3; a float made of 0x3c bytes is 0.0115: any finite values do, the time does not depend on them
   if (err == cudaSuccess) err = cudaMemsetAsync(B, 0x38, w_bytes * copies, stream);
-  if (err == cudaSuccess) err = cudaMemsetAsync(A, 0x38, (size_t)64 * K, stream);
+  if (err == cudaSuccess) err = cudaMemsetAsync(A, 0x38, (size_t)128 * K, stream);
   if (err == cudaSuccess) err = cudaMemsetAsync(B_s, 0x3c, bs_bytes, stream);
   if (err == cudaSuccess) err = cudaMemsetAsync(A_s, 0x3c, as_bytes, stream);
   if (err != cudaSuccess) {
@@ -1338,7 +1337,42 @@ int tune_decode(const DeviceInfo* info, int N, int K)
                      cudaGetErrorString(err));
   }
   int rc = LLMMM_OK;
-  for (int mp = 16; mp <= 64 && rc == LLMMM_OK; mp *= 2) {
+  // times `copies` launches of one candidate (the first of four passes warms up); < 0 if a launch failed
+  auto time_candidate = [&](auto&& launch_one) -> float {
+    float best = -1.0f;
+    for (int rep = 0; rep < 4 && rc == LLMMM_OK; ++rep) {
+      cudaEventRecord(e0, stream);
+      for (int c = 0; c < copies && rc == LLMMM_OK; ++c) {
+        rc = launch_one(B + (size_t)c * w_bytes);
+      }
+      cudaEventRecord(e1, stream);
+      if (cudaEventSynchronize(e1) != cudaSuccess) {
+        rc = set_error(LLMMM_ERR_CUDA, "llmmm_tune: a timed launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+      }
+      float ms = 0.0f;
+      cudaEventElapsedTime(&ms, e0, e1);
+      if (rep > 0 && (best < 0.0f || ms < best)) {
+        best = ms;
+      }
+    }
+    return rc == LLMMM_OK ? best : -1.0f;
+  };
+  // 65..128 rows: single-CTA kernel against pair kernel (which needs the scratch to cut its last wave), at M = 128
+  {
+    const Workspace ws = registered_workspace(info->device);
+    if (info->max_pairs >= 1 && ws.ptr != nullptr && ws.bytes >= split_workspace_bytes()) {
+      float t[2];
+      for (int cand = 0; cand < 2 && rc == LLMMM_OK; ++cand) {
+        t_force_mid = cand;
+        t[cand]     = time_candidate([&](const uint8_t* w) { return launch_fp8_e4m3(A, A_s, w, B_s, C, C_s, 128, N, K, stream); });
+        t_force_mid = -1;
+      }
+      if (rc == LLMMM_OK && t[0] >= 0.0f && t[1] >= 0.0f) {
+        record_mid_choice(info->device, N, K, t[1] < t[0] ? 1 : 0);
+      }
+    }
+  }
+  for (int mp = 16; decode_shape && mp <= 64 && rc == LLMMM_OK; mp *= 2) {
     std::vector<int> candidates;
     if (scratch_fits(info, mp)) {
       candidates.push_back(0);
@@ -1351,22 +1385,8 @@ int tune_decode(const DeviceInfo* info, int N, int K)
     int   best    = -1;
     float best_ms = 0.0f;
     for (const int cand : candidates) {
-      float cand_ms = -1.0f;
-      for (int rep = 0; rep < 4 && rc == LLMMM_OK; ++rep) {  // the first pass warms up
-        cudaEventRecord(e0, stream);
-        for (int c = 0; c < copies && rc == LLMMM_OK; ++c) {
-          rc = launch_decode(false, A, A_s, B + (size_t)c * w_bytes, B_s, C, C_s, mp, N, K, stream, cand);
-        }
-        cudaEventRecord(e1, stream);
-        if (cudaEventSynchronize(e1) != cudaSuccess) {
-          rc = set_error(LLMMM_ERR_CUDA, "llmmm_tune: a timed launch failed: %s", cudaGetErrorString(cudaGetLastError()));
-        }
-        float ms = 0.0f;
-        cudaEventElapsedTime(&ms, e0, e1);
-        if (rep > 0 && (cand_ms < 0.0f || ms < cand_ms)) {
-          cand_ms = ms;
-        }
-      }
+      const float cand_ms =
+        time_candidate([&](const uint8_t* w) { return launch_decode(false, A, A_s, w, B_s, C, C_s, mp, N, K, stream, cand); });
       if (rc == LLMMM_OK && cand_ms >= 0.0f && (best < 0 || cand_ms < best_ms)) {
         best    = cand;
         best_ms = cand_ms;

@@ -383,17 +383,36 @@ struct Fp8PairBars {
 // registered: then the pair kernel, whose tiles can be cut along K, wins although half of each tile's rows are
 // empty (measured at M = 128: 2560x9728 45.6 -> 23.6 us, 4096x4096 21.5 -> 18.2 us; 19456x2560, 76 tiles,
 // would lose: 17.3 -> 29.3 us).
-static bool fp8_use_pair_kernel(const DeviceInfo* info, int M, int N)
+// With K given, a choice llmmm_tune measured for this weight shape takes precedence (as long as the scratch the
+// pair kernel's split needs is there).
+static bool fp8_use_pair_kernel(const DeviceInfo* info, int M, int N, int K = 0, bool* tuned = nullptr)
 {
+  if (tuned != nullptr) {
+    *tuned = false;
+  }
   if (info->max_pairs < 1) {
     return false;
   }
   if (M > 128) {
     return true;
   }
-  const int       tiles_1cta = ((M + fp8cfg::BM - 1) / fp8cfg::BM) * ((N + fp8cfg::BN - 1) / fp8cfg::BN);
-  const Workspace ws         = registered_workspace(info->device);
-  return M > 64 && ws.ptr != nullptr && ws.bytes >= split_workspace_bytes() && 2 * tiles_1cta <= info->sm_count;
+  if (M <= 64) {
+    return false;
+  }
+  const Workspace ws      = registered_workspace(info->device);
+  const bool      scratch = ws.ptr != nullptr && ws.bytes >= split_workspace_bytes();
+  if (t_force_mid >= 0) {
+    return t_force_mid == 1;
+  }
+  const int measured = K > 0 ? mid_choice(info->device, N, K) : -1;
+  if (measured >= 0 && (measured == 0 || scratch)) {
+    if (tuned != nullptr) {
+      *tuned = true;
+    }
+    return measured == 1;
+  }
+  const int tiles_1cta = ((M + fp8cfg::BM - 1) / fp8cfg::BM) * ((N + fp8cfg::BN - 1) / fp8cfg::BN);
+  return scratch && 2 * tiles_1cta <= info->sm_count;
 }
 constexpr int EPI_E4M3   = 0;
 constexpr int EPI_F32    = 1;
@@ -1149,7 +1168,7 @@ static int launch_fp8(const void*  A,
   if (info == nullptr) {
     return LLMMM_ERR_UNSUPPORTED;
   }
-  if (fp8_use_pair_kernel(info, M, N)) {
+  if (fp8_use_pair_kernel(info, M, N, K)) {
     return launch_fp8_pair<OUT_F32>(A, A_s, B, B_s, C, C_s, M, N, K, info, stream);
   }
   CUtensorMap tm_a, tm_b;
@@ -1179,26 +1198,36 @@ void describe_fp8_plan(const DeviceInfo* info, bool out_f32, int M, int N, int K
   if (describe_decode_plan(info, M, N, K, buf, len)) {
     return;
   }
-  if (fp8_use_pair_kernel(info, M, N)) {
+  bool        tuned = false;
+  const bool  pair  = fp8_use_pair_kernel(info, M, N, K, &tuned);
+  const char* how   = (M > 64 && M <= 128) ? (tuned ? " (kernel choice: measured by llmmm_tune)" : " (kernel choice: default rule)") : "";
+  if (pair) {
     using namespace fp8pair;
     const int       tiles    = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int       k_blocks = K / BK;
     const SplitPlan plan     = plan_split(info, tiles, k_blocks, 4, 5, 3, false);
     if (plan.split_pairs > 0) {
       snprintf(buf, len, "fp8_blockwise_gemm_pair_kernel<%s>: %d tiles of 256x256 on %d CTA pairs; %d whole tiles round-robin, then "
-               "%d tiles cut %d-way along K (chunks of %d K-blocks), one chunk per pair", o, tiles, plan.pairs, plan.dp_tiles,
-               tiles - plan.dp_tiles, plan.split_s, plan.split_chunk);
+               "%d tiles cut %d-way along K (chunks of %d K-blocks), one chunk per pair%s", o, tiles, plan.pairs, plan.dp_tiles,
+               tiles - plan.dp_tiles, plan.split_s, plan.split_chunk, how);
     }
     else {
       snprintf(buf, len, "fp8_blockwise_gemm_pair_kernel<%s>: %d tiles of 256x256 on %d CTA pairs (%.2f waves), %d K-blocks each, "
-               "no split", o, tiles, plan.pairs, (double)tiles / plan.pairs, k_blocks);
+               "no split%s", o, tiles, plan.pairs, (double)tiles / plan.pairs, k_blocks, how);
     }
     return;
   }
   using namespace fp8cfg;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid  = tiles < info->sm_count ? tiles : info->sm_count;
-  snprintf(buf, len, "fp8_blockwise_gemm_kernel<%s>: %d tiles of %dx%d on %d CTAs (%.2f waves)", o, tiles, BM, BN, grid, (double)tiles / grid);
+  snprintf(buf, len, "fp8_blockwise_gemm_kernel<%s>: %d tiles of %dx%d on %d CTAs (%.2f waves)%s", o, tiles, BM, BN, grid,
+           (double)tiles / grid, how);
+}
+
+int launch_fp8_e4m3(const void* A, const float* A_s, const void* B, const float* B_s, void* C, float* C_s, int M, int N, int K,
+                    cudaStream_t stream)
+{
+  return launch_fp8<false>(A, A_s, B, B_s, C, C_s, M, N, K, stream);
 }
 
 int warm_fp8_kernels(const DeviceInfo* info)

@@ -65,6 +65,17 @@ int launch_decode(bool         out_f32,
 // and records the winners (llmmm_tune).  Allocates and frees temporary operands.
 int tune_decode(const DeviceInfo* info, int N, int K);
 
+// FP8 GEMMs of 65..128 rows run on the single-CTA kernel (128-row tiles) or on the pair kernel (256-row tiles, half
+// empty, but its last wave can be cut along K).  llmmm_tune measures both for a weight shape and records the
+// winner; `mid_choice` returns it (-1: not measured, 0: single-CTA kernel, 1: pair kernel).  `t_force_mid` >= 0
+// overrides everything for the calling thread (the tuner's own launches).
+int  mid_choice(int device, int N, int K);
+void record_mid_choice(int device, int N, int K, int choice);
+extern thread_local int t_force_mid;
+// Launcher of the general FP8 kernels (fp8_mm.cu), e4m3 output; used by the tuner.
+int launch_fp8_e4m3(const void* A, const float* A_s, const void* B, const float* B_s, void* C, float* C_s, int M, int N, int K,
+                    cudaStream_t stream);
+
 // Set by llmmm_check_status() when it reports a device-side wait that ran out: the decode kernel's flagged
 // partial words (registered scratch / built-in scratch) may then hold leftovers and are cleared before the next use.
 extern std::atomic<int> g_scratch_dirty[64];

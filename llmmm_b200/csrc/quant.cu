@@ -166,6 +166,8 @@ __global__ void __launch_bounds__(256)
 // one is re-read from L2.
 constexpr int RN_THREADS = 256;
 
+// RESIDENT: float4 values of the row a thread keeps (0: none, the row is re-read from L2 for the second phase).
+template<int RESIDENT>
 __global__ void __launch_bounds__(RN_THREADS)
   rmsnorm_quant_1x128_kernel(const float* __restrict__ x, const float* __restrict__ weight, float eps, uint8_t* __restrict__ q,
                              float* __restrict__ scale, int M, int K)
@@ -177,14 +179,13 @@ __global__ void __launch_bounds__(RN_THREADS)
   const int     warp = threadIdx.x >> 5;
   const int     m    = blockIdx.x;
   const float4* row  = reinterpret_cast<const float4*>(x + (size_t)m * K);
-  // Rows of up to 8192 values stay in registers between the two phases (8 float4 per thread): element
+  // Rows of up to 8192 values stay in registers between the two phases (RESIDENT float4 per thread): element
   // threadIdx.x + 256 j of the row, as float4, is lane `lane` of the 128-wide group warp + 8 j, so the thread
   // that read a value for the sum of squares is the one that quantises it, and x is read from memory once.
-  constexpr int RESIDENT = 8;
-  const bool    resident = K <= RESIDENT * RN_THREADS * 4;
-  float4        v[RESIDENT];
-  float         ss = 0.0f;
-  if (resident) {
+  constexpr bool resident = RESIDENT > 0;
+  float4         v[resident ? RESIDENT : 1];
+  float          ss = 0.0f;
+  if constexpr (resident) {
 #pragma unroll
     for (int j = 0; j < RESIDENT; ++j) {
       const int i = threadIdx.x + j * RN_THREADS;
@@ -236,7 +237,7 @@ __global__ void __launch_bounds__(RN_THREADS)
       scale[(size_t)g * M + m] = sc;
     }
   };
-  if (resident) {
+  if constexpr (resident) {
 #pragma unroll
     for (int j = 0; j < RESIDENT; ++j) {
       const int g = warp + j * (RN_THREADS / 32);
@@ -392,7 +393,11 @@ int llmmm_fp8_rmsnorm_quant_1x128(const float* x, const float* weight, float eps
   if (device_info() == nullptr) {
     return LLMMM_ERR_UNSUPPORTED;
   }
-  LLMMM_CUDA_TRY(launch_pdl(rmsnorm_quant_1x128_kernel, dim3((unsigned)M), dim3(RN_THREADS), 0,
+  // as few resident values as the row needs: registers decide how many rows an SM works on at a time
+  auto* kernel = K <= 2 * RN_THREADS * 4 ? rmsnorm_quant_1x128_kernel<2>
+               : K <= 4 * RN_THREADS * 4 ? rmsnorm_quant_1x128_kernel<4>
+               : K <= 8 * RN_THREADS * 4 ? rmsnorm_quant_1x128_kernel<8> : rmsnorm_quant_1x128_kernel<0>;
+  LLMMM_CUDA_TRY(launch_pdl(kernel, dim3((unsigned)M), dim3(RN_THREADS), 0,
                             reinterpret_cast<cudaStream_t>(stream), 1, x, weight, eps, static_cast<uint8_t*>(q), scale, M, K));
   g_launches.fetch_add(1);
   return LLMMM_OK;

@@ -68,6 +68,7 @@ def test_tune_measures_the_decode_plans(capi, cuda):
     values)."""
     N, K = 2560, 4096
     capi.ensure_workspace(64, N, K)
+    capi.ensure_workspace(4096, N, K)  # the pair kernel's split scratch: the 65..128-row choice is measured with it
     before = {}
     for M in (16, 64):
         assert "default rule" in capi.describe_plan("fp8", M, N, K)
@@ -78,5 +79,8 @@ def test_tune_measures_the_decode_plans(capi, cuda):
         us, cq, cs = _time_decode(capi, cuda, M, N, K)
         assert us <= before[M][0] * 1.10, (M, us, before[M][0])
     capi.check_status()
+    # the same call also measured the single-CTA kernel against the pair kernel for 65..128 rows of this weight
+    assert "kernel choice: measured by llmmm_tune" in capi.describe_plan("fp8", 128, N, K)
+    assert "kernel choice: default rule" in capi.describe_plan("fp8", 128, 6144, 2560)
     # a shape the tuner has not seen keeps the default rule
     assert "default rule" in capi.describe_plan("fp8", 16, 6144, 2560)
