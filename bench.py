@@ -528,30 +528,47 @@ def extra_configs(torch, capi, dev, peaks):
                      "frac_of_2x_measured_bf16_burst": tf_p / (2.0 * float(peaks["bf16_tflops"]))})
         del ws, xq, xs, Cq, Cs
     out["mlp7b_one_gpu"] = mlp7
-    # decode shapes (HBM-bound): rotate over enough weight copies to exceed L2
+    # decode shapes (HBM-bound): rotate over enough weight copies to exceed L2.  Every shape is timed twice: with the
+    # plan the default rule picks, and after llmmm_tune has measured the plans for that weight shape.
     dec = []
-    for (n, k) in [(6144, 2560), (2560, 4096), (19456, 2560), (2560, 9728)]:
-        copies = max(3, int(300e6 // (n * k)) + 1)
-        ws = [(torch.randint(0, 120, (n, k), dtype=torch.uint8, device=dev), torch.rand(n // 128, k // 128, device=dev))
-              for _ in range(copies)]
-        for m in (1, 16, 64):
-            xq = torch.randint(0, 120, (m, k), dtype=torch.uint8, device=dev)
-            xs = torch.rand(k // 128, m, device=dev)
-            Cq = torch.empty(m, n, dtype=torch.uint8, device=dev)
-            Cs = torch.empty(n // 128, m, device=dev)
-            capi.ensure_workspace(m, n, k)
-            fns = [(lambda w=w: capi.fp8_blockwise_mm(xq, xs, w[0], w[1], Cq, Cs, m, n, k)) for w in ws] * 2
-            ms_plain = time_graph(torch, fns)
-            # the weights of a serving loop are static: with that promise each launch of the chain requests its
-            # first weight tiles while the launch before it is still finishing
-            capi.set_static_weights(True)
-            ms = time_graph(torch, fns)
-            capi.set_static_weights(False)
-            by = n * k + 4 * (n // 128) * (k // 128) + m * k + 4 * m * k // 128 + m * n + 4 * m * n // 128
-            gbs = by / (ms * 1e-3) / 1e9
-            dec.append({"M": m, "N": n, "K": k, "us": ms * 1e3, "us_without_static_weights": ms_plain * 1e3, "gbs": gbs,
-                        "frac_of_measured_hbm": gbs / float(peaks["hbm_gbs"])})
-        del ws
+    shapes = [(6144, 2560), (2560, 4096), (19456, 2560), (2560, 9728)]
+    capi.ensure_workspace(64, 19456, 2560)
+
+    def decode_rows(tag):
+        rows = []
+        for (n, k) in shapes:
+            copies = max(3, int(300e6 // (n * k)) + 1)
+            ws = [(torch.randint(0, 120, (n, k), dtype=torch.uint8, device=dev), torch.rand(n // 128, k // 128, device=dev))
+                  for _ in range(copies)]
+            for m in (1, 16, 64):
+                xq = torch.randint(0, 120, (m, k), dtype=torch.uint8, device=dev)
+                xs = torch.rand(k // 128, m, device=dev)
+                Cq = torch.empty(m, n, dtype=torch.uint8, device=dev)
+                Cs = torch.empty(n // 128, m, device=dev)
+                fns = [(lambda w=w: capi.fp8_blockwise_mm(xq, xs, w[0], w[1], Cq, Cs, m, n, k)) for w in ws] * 2
+                ms_plain = time_graph(torch, fns)
+                # the weights of a serving loop are static: with that promise each launch of the chain requests its
+                # first weight tiles while the launch before it is still finishing
+                capi.set_static_weights(True)
+                ms = time_graph(torch, fns)
+                capi.set_static_weights(False)
+                rows.append({"M": m, "N": n, "K": k, "us": ms * 1e3, "us_without_static_weights": ms_plain * 1e3,
+                             "plan": capi.describe_plan("fp8", m, n, k)[:96] + " ... / " + tag})
+            del ws
+        return rows
+
+    default_rows = decode_rows("default rule")
+    capi.set_static_weights(True)
+    for (n, k) in shapes:
+        capi.tune("fp8", n, k)
+    capi.set_static_weights(False)
+    tuned_rows = decode_rows("measured by llmmm_tune")
+    for d_, t_ in zip(default_rows, tuned_rows):
+        m, n, k = t_["M"], t_["N"], t_["K"]
+        by = n * k + 4 * (n // 128) * (k // 128) + m * k + 4 * m * k // 128 + m * n + 4 * m * n // 128
+        gbs = by / (t_["us"] * 1e-6) / 1e9
+        dec.append({**t_, "us_default_rule": d_["us"], "plan_default_rule": d_["plan"], "gbs": gbs,
+                    "frac_of_measured_hbm": gbs / float(peaks["hbm_gbs"])})
     out["qwen3_4b_decode"] = dec
     # HBM-bound helpers of the same path at 4096 x 4096: the two quantisers (4 B read + 1 B written per element,
     # plus scales) and the transposes (1 B / 4 B read and written)

@@ -632,38 +632,52 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
             fetch_chunk(it / CH + 1);
           }
         }
+        // One promotion warp has a scheduler to itself: nothing hides a shared-memory latency in front of every four
+        // FMAs.  The scale products of the first half of the rows are therefore fetched before the wait for the
+        // partial, those of the second half while the first half is being worked on.
+        constexpr int H4   = MP / 8;  // float4 values per half
+        const float4* srow = reinterpret_cast<const float4*>(sc + (it % CH) * MP);
+        float4        s_lo[H4], s_hi[H4];
+#pragma unroll
+        for (int i = 0; i < H4; ++i) {
+          s_lo[i] = srow[i];  // the same address in every lane: a broadcast
+        }
         PROF_KB(0);
         mbar_wait(&bars->part_full[p], pp, DEV_WAIT_TMEM_FULL, abort_flag, status);
         PROF_KB(1);
         tc_fence_after_sync();
         // the partial goes to registers and the stage is handed back as soon as its last column has been read,
         // before the arithmetic on it
-        constexpr int VW = MP;
-        const float4* srow = reinterpret_cast<const float4*>(sc + (it % CH) * MP);
+        uint32_t v[MP];
 #pragma unroll
-        for (int h = 0; h < MP / VW; ++h) {
-          uint32_t v[VW];
+        for (int c = 0; c < MP / 16; ++c) {
+          tmem_ld_32x32b_x16(tmem_base + p * L::PART_COLS + t_lane + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&v[c * 16]));
+        }
 #pragma unroll
-          for (int c = 0; c < VW / 16; ++c) {
-            tmem_ld_32x32b_x16(tmem_base + p * L::PART_COLS + t_lane + h * VW + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&v[c * 16]));
-          }
-          tmem_ld_wait();
-          if (h == MP / VW - 1) {
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-              mbar_arrive(&bars->part_empty[p]);
-            }
-            PROF_KB(2);
-          }
+        for (int i = 0; i < H4; ++i) {
+          s_hi[i] = srow[H4 + i];
+        }
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&bars->part_empty[p]);
+        }
+        PROF_KB(2);
 #pragma unroll
-          for (int m = 0; m < VW; m += 4) {
-            const float4 s4 = srow[(h * VW + m) >> 2];  // the same address in every lane: a broadcast
-            acc[h * VW + m]     = __fmaf_rn(__uint_as_float(v[m]), s4.x, acc[h * VW + m]);
-            acc[h * VW + m + 1] = __fmaf_rn(__uint_as_float(v[m + 1]), s4.y, acc[h * VW + m + 1]);
-            acc[h * VW + m + 2] = __fmaf_rn(__uint_as_float(v[m + 2]), s4.z, acc[h * VW + m + 2]);
-            acc[h * VW + m + 3] = __fmaf_rn(__uint_as_float(v[m + 3]), s4.w, acc[h * VW + m + 3]);
-          }
+        for (int i = 0; i < H4; ++i) {
+          acc[4 * i]     = __fmaf_rn(__uint_as_float(v[4 * i]), s_lo[i].x, acc[4 * i]);
+          acc[4 * i + 1] = __fmaf_rn(__uint_as_float(v[4 * i + 1]), s_lo[i].y, acc[4 * i + 1]);
+          acc[4 * i + 2] = __fmaf_rn(__uint_as_float(v[4 * i + 2]), s_lo[i].z, acc[4 * i + 2]);
+          acc[4 * i + 3] = __fmaf_rn(__uint_as_float(v[4 * i + 3]), s_lo[i].w, acc[4 * i + 3]);
+        }
+#pragma unroll
+        for (int i = 0; i < H4; ++i) {
+          const int m = 4 * (H4 + i);
+          acc[m]     = __fmaf_rn(__uint_as_float(v[m]), s_hi[i].x, acc[m]);
+          acc[m + 1] = __fmaf_rn(__uint_as_float(v[m + 1]), s_hi[i].y, acc[m + 1]);
+          acc[m + 2] = __fmaf_rn(__uint_as_float(v[m + 2]), s_hi[i].z, acc[m + 2]);
+          acc[m + 3] = __fmaf_rn(__uint_as_float(v[m + 3]), s_hi[i].w, acc[m + 3]);
         }
         PROF_KB(3);
       }
