@@ -46,7 +46,7 @@ namespace llmmm {
 namespace deccfg {
 constexpr int      BK            = 128;
 constexpr int      UMMA_K        = 32;
-constexpr int      MAX_STAGES    = 6;    // the ring depth depends on the activation tile, see DecodeSmem
+constexpr int      MAX_STAGES    = 8;    // the ring depth depends on the activation tile, see DecodeSmem
 constexpr int      THREADS       = 256;  // warps 0-3: producer, three MMA issuers; warps 4-7: promotion
 constexpr int      EPI_WARP0     = 4;    // first promotion warp (setmaxnreg acts on whole warpgroups of 4 warps)
 constexpr int      REGS_CTRL     = 56;   // the control warpgroup gives up 72 of its 128 registers per thread ...
@@ -54,20 +54,22 @@ constexpr int      REGS_EPI      = 200;  // ... and the promotion warpgroup take
 constexpr uint32_t W_BYTES       = 128 * BK;
 constexpr int      MAX_CTAS      = 160;  // grid of the stream-K kernel: one CTA per SM, at most this many
 constexpr int      MAX_GROUPS    = 4096; // N <= 524288
-constexpr uint32_t TMEM_COLS     = 256;  // one partial stage per ring stage (see DecodeSmem), two CTAs per SM
 }  // namespace deccfg
 
 template<int MP>
 struct DecodeSmem {
   static constexpr uint32_t X_BYTES    = MP * deccfg::BK;
-  // As deep a ring as lets two CTAs share an SM (113 KB each; tensor memory: 256 columns each): the next
-  // kernel of a launch chain then sets up, and requests static weights, beside the running one.
-  static constexpr int      STAGES     = MP <= 16 ? 6 : (MP <= 32 ? 5 : 4);
+  // Up to 32 activation columns: as deep a ring as lets two CTAs share an SM (113 KB each; tensor memory: 256
+  // columns each): the next kernel of a launch chain then sets up, and requests static weights, beside the
+  // running one.  With 64 columns a stage is 24 KB and only four would fit that way; measured, an SM to itself and
+  // eight stages is faster there (cluster shapes 9.9 / 8.2 / 12.1 us against 11.8 / 9.3 / 14.2 us at M = 64).
+  static constexpr int      STAGES     = MP <= 16 ? 6 : (MP <= 32 ? 5 : 8);
   // K-block `it` uses ring stage it % STAGES and the tensor-memory partial stage of the same index, so ONE
   // tcgen05.commit per K-block tells both the promotion warps (partial ready) and the producer (operands
   // consumed); a second commit would cost the single issuing thread another ~150 clk per K-block.
   static constexpr uint32_t PART_COLS  = MP < 32 ? 32 : MP;
-  static_assert(STAGES * PART_COLS <= deccfg::TMEM_COLS, "partial stages exceed the tensor memory allocation");
+  static constexpr uint32_t TMEM_COLS  = STAGES * PART_COLS <= 256 ? 256 : 512;  // one partial stage per ring stage
+  static_assert(STAGES * PART_COLS <= TMEM_COLS, "partial stages exceed the tensor memory allocation");
   static constexpr uint32_t OFF_W      = 0;
   static constexpr uint32_t OFF_X      = STAGES * deccfg::W_BYTES;
   static constexpr uint32_t OFF_BAR    = OFF_X + STAGES * X_BYTES;
@@ -81,7 +83,8 @@ struct DecodeSmem {
   // at least 80 KB, so that never more than two CTAs share an SM: a third one would sit in tcgen05.alloc until
   // tensor memory is freed
   static constexpr uint32_t USED_BYTES = OFF_SC + SC_BYTES + 1024;
-  static_assert(2 * (USED_BYTES + 1024) <= 228 * 1024, "two CTAs of consecutive launches must fit on one SM");
+  static_assert(MP > 32 || 2 * (USED_BYTES + 1024) <= 228 * 1024, "two CTAs of consecutive launches must fit on one SM");
+  static_assert(USED_BYTES <= 227 * 1024, "shared memory of one CTA");
   static constexpr uint32_t SMEM_BYTES = USED_BYTES > 80 * 1024 ? USED_BYTES : 80 * 1024;
 };
 
@@ -451,7 +454,7 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
     prefetch_tmap(&tm_x);
   }
   if (warp == 1) {
-    tmem_alloc<TMEM_COLS>(&bars->tmem_base);
+    tmem_alloc<L::TMEM_COLS>(&bars->tmem_base);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -867,7 +870,7 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc<TMEM_COLS>(tmem_base);
+    tmem_dealloc<L::TMEM_COLS>(tmem_base);
     PROF_CTA(9);
   }
 }
