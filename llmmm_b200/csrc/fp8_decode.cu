@@ -9,9 +9,11 @@
 //     128-row operand of tcgen05.mma.kind::f8f6f4 and the (zero-padded)
 //     activation rows are the narrow N side (16, 32 or 64 columns), so TMEM
 //     lane = output column n and TMEM column = output row m;
-//   * stream-K: the (N/128 x K/128) grid of weight blocks is cut into one
-//     contiguous run per CTA, so all SMs stream the same number of bytes
-//     whatever N is; a run crosses output groups, giving "segments";
+//   * stream-K: all SMs stream the same number of weight blocks whatever N is:
+//     the (N/128 x K/128) grid of weight blocks is cut into one contiguous run
+//     per CTA; a run crosses output groups, giving "segments" (with 64
+//     activation columns and more groups than CTAs, every CTA first takes
+//     floor(groups / CTAs) whole groups and only the left-over groups are cut);
 //   * warp 0 streams weight blocks (and the matching activation slab) through
 //     a 4-6-deep TMA ring; warps 1-3 take turns issuing the MMAs of a K-block
 //     (four per K-block, from zero, into the tensor-memory partial stage of the
@@ -427,7 +429,15 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
   const uint32_t  U       = (uint32_t)(N / 128) * (uint32_t)KB;  // the launcher keeps U * 256 below 2^31
   const uint32_t  G       = gridDim.x;
   uint32_t        c_size  = 1, c_rank = 0, red_rows = MP;  // (cluster kernel: rows of the group a CTA owns, at most)
-  uint32_t        u_begin, u_end;
+  // A CTA works through two ranges of units, [u_begin, u_end) and then [v_begin, v_end).  Stream-K kernel with 64
+  // activation columns and more output groups than CTAs: every CTA takes floor(groups / G) whole groups (the second
+  // range, finished in place), and only the groups that are left over are cut evenly among the CTAs (the first range, so that their
+  // partial tiles have long landed when the CTA comes to reduce them at its end); otherwise (fewer groups than CTAs,
+  // or narrower activation tiles) everything is "left over".  Cluster kernel: one slice of one group, no second range.
+  uint32_t        u_begin, u_end, v_begin = 0, v_end = 0;
+  // the units that are cut: [tail_base, tail_base + tail_units), among the first tail_ctas CTAs (all of them, unless
+  // there are fewer such units than CTAs: every CTA that takes part gets at least one)
+  uint32_t        tail_base = 0, tail_units = U, tail_ctas = G;
   if constexpr (CLUSTER) {
     asm volatile("mov.u32 %0, %%cluster_nctaid.x;" : "=r"(c_size));
     c_rank = cluster_ctarank();
@@ -437,9 +447,20 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
     u_end   = group * (uint32_t)KB + ((c_rank + 1) * (uint32_t)KB) / c_size;
   }
   else {
-    u_begin = (blockIdx.x * U) / G;
-    u_end   = ((blockIdx.x + 1) * U) / G;
+    // (measured on 19456 x 2560: whole groups + cut left-overs 22.7 us against 24.4 us for cutting everything at
+    // M = 64, where a cut group costs 64 rows of reduction; but 16.3 against 12.7 us at M <= 16, where the 20
+    // one-block contributors of a left-over group cost more than two or three contributors of every group)
+    const uint32_t whole_units = MP > 32 ? ((uint32_t)(N / 128) / G) * (uint32_t)KB : 0u;  // per CTA
+    tail_base  = G * whole_units;
+    tail_units = U - tail_base;
+    v_begin    = blockIdx.x * whole_units;
+    v_end      = v_begin + whole_units;
+    tail_ctas  = tail_units < G ? tail_units : G;
+    u_begin    = tail_base + (blockIdx.x < tail_ctas ? (blockIdx.x * tail_units) / tail_ctas : 0u);
+    u_end      = tail_base + (blockIdx.x < tail_ctas ? ((blockIdx.x + 1) * tail_units) / tail_ctas : 0u);
   }
+  const uint32_t len0 = u_end - u_begin;          // units of the first range
+  const uint32_t run  = len0 + (v_end - v_begin);  // units of this CTA
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::STAGES; ++s) {
@@ -481,33 +502,45 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
     // ------------------------------------------------------ TMA producer --
     const uint64_t pol_w = policy_evict_first();  // weights are read once
     const uint64_t pol_x = policy_evict_last();   // activations are re-read by every CTA
-    const int      nb0   = (int)(u_begin / (uint32_t)KB);
-    const int      kb0   = (int)(u_begin % (uint32_t)KB);
+    // walks the CTA's units in order and calls body(it, nb, kb) until it returns false
+    auto walk = [&](auto&& body) {
+      uint32_t it = 0;
+      for (int r = 0; r < 2; ++r) {
+        const uint32_t b = r == 0 ? u_begin : v_begin, e = r == 0 ? u_end : v_end;
+        if (b >= e) {
+          continue;
+        }
+        int nb = (int)(b / (uint32_t)KB), kb = (int)(b % (uint32_t)KB);
+        for (uint32_t u = b; u < e; ++u, ++it, ++kb) {
+          if (kb == KB) {
+            kb = 0;
+            ++nb;
+          }
+          if (!body(it, nb, kb)) {
+            return;
+          }
+        }
+      }
+    };
     // Weights the caller declared static (llmmm_set_static_weights) do not depend on the previous kernel
     // of the stream: the first ring of weight tiles is requested before waiting for that kernel, the
     // activation tiles of the same stages after it.
     uint32_t early = 0;
     if (lane == 0 && early_weights) {
-      int nb = nb0, kb = kb0;
-      for (uint32_t u = u_begin; u < u_end && early < (uint32_t)L::STAGES; ++u, ++early, ++kb) {
-        if (kb == KB) {
-          kb = 0;
-          ++nb;
+      walk([&](uint32_t it, int nb, int kb) {
+        if (it >= (uint32_t)L::STAGES) {
+          return false;
         }
-        mbar_arrive_expect_tx(&bars->full[early], W_BYTES + L::X_BYTES);
-        tma_load_2d_hint(smem + L::OFF_W + early * W_BYTES, &tm_w, &bars->full[early], kb * BK, nb * 128, pol_w);
-      }
+        mbar_arrive_expect_tx(&bars->full[it], W_BYTES + L::X_BYTES);
+        tma_load_2d_hint(smem + L::OFF_W + it * W_BYTES, &tm_w, &bars->full[it], kb * BK, nb * 128, pol_w);
+        early = it + 1;
+        return true;
+      });
     }
     __syncwarp();
     pdl_wait();
     if (lane == 0) {
-      uint32_t it = 0;
-      int      nb = nb0, kb = kb0;
-      for (uint32_t u = u_begin; u < u_end; ++u, ++it, ++kb) {
-        if (kb == KB) {
-          kb = 0;
-          ++nb;
-        }
+      walk([&](uint32_t it, int nb, int kb) {
         const uint32_t s  = it % L::STAGES;
         const uint32_t ph = (it / L::STAGES) & 1;
         if (it >= early) {
@@ -516,7 +549,8 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
           tma_load_2d_hint(smem + L::OFF_W + s * W_BYTES, &tm_w, &bars->full[s], kb * BK, nb * 128, pol_w);
         }
         tma_load_2d_hint(smem + L::OFF_X + s * L::X_BYTES, &tm_x, &bars->full[s], kb * BK, 0, pol_x);
-      }
+        return true;
+      });
     }
     if constexpr (CLUSTER) {
       __syncwarp();
@@ -530,7 +564,6 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
     // tensor-memory partial stage, so the threads never touch the same barrier phase.
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(/*e4m3*/ 0, 0, 0, 0, 128, MP);
-      const uint32_t     run   = u_end - u_begin;
       for (uint32_t it = (uint32_t)(warp - 1); it < run; it += 3) {
         const uint32_t s  = it % L::STAGES;
         const uint32_t ph = (it / L::STAGES) & 1;
@@ -565,7 +598,6 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
     const int      n_local = quarter * 32 + lane;  // output column inside the group == TMEM lane
     const int      et      = threadIdx.x - EPI_WARP0 * 32;  // 0..127
     const uint32_t t_lane  = (uint32_t)(quarter * 32) << 16;
-    const uint32_t run     = u_end - u_begin;
     uint32_t       it      = 0;
 
     // Scale products of the run, CHUNK K-blocks at a time: thread `et` fetches elements et, et + 128, ... of
@@ -585,7 +617,7 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
         const int      m   = (int)(e % MP);
         float          v   = 0.0f;
         if (itx < run && m < M) {
-          const uint32_t uu = u_begin + itx;
+          const uint32_t uu = itx < len0 ? u_begin + itx : v_begin + (itx - len0);
           v = __fmul_rn(__ldg(A_s + (size_t)(uu % (uint32_t)KB) * M + m), __ldg(B_s + uu));
         }
         st[i] = v;
@@ -608,13 +640,15 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
     int pend_nb0 = 0, pend_nb1 = 0;
     int n_pend = 0;
 
-    uint32_t u     = u_begin;
-    bool     first = true;  // a cluster CTA runs its one segment even if it is empty: it owes two cluster barriers
-    while (u < u_end || (CLUSTER && first)) {
+    for (int range = 0; range < (CLUSTER ? 1 : 2); ++range) {
+    uint32_t       u     = range == 0 ? u_begin : v_begin;
+    const uint32_t r_end = range == 0 ? u_end : v_end;
+    bool           first = range == 0;  // a cluster CTA runs its one segment even if it is empty: it owes two cluster barriers
+    while (u < r_end || (CLUSTER && first)) {
       first = false;
       const int      nb   = (int)(u / (uint32_t)KB);
       const int      kb0  = (int)(u % (uint32_t)KB);
-      const uint32_t left = u_end - u;
+      const uint32_t left = r_end - u;
       const int      kb1  = (left < (uint32_t)(KB - kb0)) ? kb0 + (int)left : KB;
       const bool     whole = (kb0 == 0 && kb1 == KB);
 
@@ -685,7 +719,7 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
         PROF_KB(3);
       }
       u += (uint32_t)(kb1 - kb0);
-      if (u >= u_end && ew == 0) {
+      if (it >= run && ew == 0) {
         PROF_CTA(4);
       }
 
@@ -812,6 +846,7 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
         }
       }
     }
+    }  // range
 
     if constexpr (!CLUSTER) {
       // ------------------------------------------- reduce-scatter of the split groups ----
@@ -828,7 +863,8 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
         uint32_t q = 0;
         if (lane < 4) {
           const uint32_t nbq = (uint32_t)(lane < 2 ? pend_nb0 : pend_nb1);
-          q = (uint32_t)cta_of_unit((lane & 1) ? (nbq + 1) * (uint32_t)KB - 1 : nbq * (uint32_t)KB, G, U);
+          // (cut groups lie in the tail: their units count from tail_base and are dealt among all CTAs)
+          q = (uint32_t)cta_of_unit(((lane & 1) ? (nbq + 1) * (uint32_t)KB - 1 : nbq * (uint32_t)KB) - tail_base, tail_ctas, tail_units);
         }
         SplitGroup g[2];
         int        max_cnt = 0;
@@ -852,8 +888,19 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
           else if (max_cnt <= 4) {
             reduce_split_groups<MP, OUT_F32, 2, 2, 4>(g, partials, C_out, C_s, M, N, lane, abort_flag, status);
           }
-          else {
+          else if (max_cnt <= 8) {
             reduce_split_groups<MP, OUT_F32, 2, 1, 8>(g, partials, C_out, C_s, M, N, lane, abort_flag, status);
+          }
+          else {
+            // many contributors with one or two K-blocks each (the left-over groups of a shape with more groups
+            // than CTAs): one group after the other, 24 contributors' rows in flight
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+              if (g[k].mine) {
+                const SplitGroup one[1] = {g[k]};
+                reduce_split_groups<MP, OUT_F32, 1, 1, 24>(one, partials, C_out, C_s, M, N, lane, abort_flag, status);
+              }
+            }
           }
         }
         if (ew == 0) {
@@ -1210,9 +1257,11 @@ bool describe_decode_plan(const DeviceInfo* info, int M, int N, int K, char* buf
   const long long U = (long long)(N / 128) * (K / 128);
   long long       G = info->sm_count < deccfg::MAX_CTAS ? info->sm_count : deccfg::MAX_CTAS;
   G                 = G < U ? G : U;
-  snprintf(buf, len, "fp8_decode_kernel<%d, stream-K>: %lld weight blocks of 128x128 over %lld CTAs (%.1f each), partial tiles "
-           "through the registered scratch, rows of a cut group reduced by its contributors' warps (choice: %s)", mp, U, G,
-           (double)U / (double)G, how);
+  const long long whole = mp > 32 ? (N / 128) / G : 0;  // whole output groups per CTA
+  const long long cut   = (N / 128) - whole * G;      // groups cut evenly among all CTAs
+  snprintf(buf, len, "fp8_decode_kernel<%d, stream-K>: %lld weight blocks of 128x128 over %lld CTAs (%.1f each): %lld whole output "
+           "group(s) per CTA finished in place, %lld group(s) cut evenly among all CTAs, their partial tiles through the registered "
+           "scratch and their rows reduced by the contributors' warps (choice: %s)", mp, U, G, (double)U / (double)G, whole, cut, how);
   return true;
 }
 
