@@ -11,7 +11,7 @@ FP8 fused-quant GEMM kernels, compares them with the oracle and writes
 The committed copies live in tests/golden/; tests/test_oracle_pins.py re-checks
 the oracle against them on any machine.  Usage (on a GPU box):
 
-    python oracle/pin_against_ref.py --out gpurun_out
+    python oracle/pin_against_ref.py --out <directory>
 """
 from __future__ import annotations
 
@@ -52,7 +52,7 @@ PIN_CASES = {
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default="gpurun_out")
+    ap.add_argument("--out", default="pins_out")
     args = ap.parse_args()
     out = Path(args.out)
     out.mkdir(parents=True, exist_ok=True)
