@@ -164,7 +164,7 @@ __global__ void __launch_bounds__(256)
 // quantisation of y.  One CTA per row: it sums the squares, then scales and quantises one 128-wide group per
 // warp at a time.  A row of up to 8192 values is kept in registers in between (one pass over memory); a longer
 // one is re-read from L2.
-constexpr int RN_THREADS = 128;  // small CTAs: more rows in flight per SM, a cheaper CTA barrier between the two phases
+constexpr int RN_THREADS = 256;
 
 // RESIDENT: float4 values of the row a thread keeps (0: none, the row is re-read from L2 for the second phase).
 template<int RESIDENT>
@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(RN_THREADS)
   const int     m    = blockIdx.x;
   const float4* row  = reinterpret_cast<const float4*>(x + (size_t)m * K);
   // Rows of up to 8192 values stay in registers between the two phases (RESIDENT float4 per thread): element
-  // threadIdx.x + 128 j of the row, as float4, is lane `lane` of the 128-wide group warp + 4 j, so the thread
+  // threadIdx.x + 256 j of the row, as float4, is lane `lane` of the 128-wide group warp + 8 j, so the thread
   // that read a value for the sum of squares is the one that quantises it, and x is read from memory once.
   constexpr bool resident = RESIDENT > 0;
   float4         v[resident ? RESIDENT : 1];
@@ -394,9 +394,9 @@ int llmmm_fp8_rmsnorm_quant_1x128(const float* x, const float* weight, float eps
     return LLMMM_ERR_UNSUPPORTED;
   }
   // as few resident values as the row needs: registers decide how many rows an SM works on at a time
-  auto* kernel = K <= 4 * RN_THREADS * 4 ? rmsnorm_quant_1x128_kernel<4>
-               : K <= 8 * RN_THREADS * 4 ? rmsnorm_quant_1x128_kernel<8>
-               : K <= 16 * RN_THREADS * 4 ? rmsnorm_quant_1x128_kernel<16> : rmsnorm_quant_1x128_kernel<0>;
+  auto* kernel = K <= 2 * RN_THREADS * 4 ? rmsnorm_quant_1x128_kernel<2>
+               : K <= 4 * RN_THREADS * 4 ? rmsnorm_quant_1x128_kernel<4>
+               : K <= 8 * RN_THREADS * 4 ? rmsnorm_quant_1x128_kernel<8> : rmsnorm_quant_1x128_kernel<0>;
   LLMMM_CUDA_TRY(launch_pdl(kernel, dim3((unsigned)M), dim3(RN_THREADS), 0,
                             reinterpret_cast<cudaStream_t>(stream), 1, x, weight, eps, static_cast<uint8_t*>(q), scale, M, K));
   g_launches.fetch_add(1);
