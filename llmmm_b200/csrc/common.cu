@@ -280,7 +280,7 @@ SplitPlan plan_split(const DeviceInfo* info, int tiles, int k_steps, int fixed, 
     plan.split_chunk = chunk;
     plan.split_pairs = tail_tiles * ways;
     plan.pairs       = plan.dp_tiles > 0 ? P : plan.split_pairs;
-    plan.counters    = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ws.ptr) + WS_DECODE_COUNTER_BYTES);
+    plan.counters    = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ws.ptr) + WS_RESERVED_BYTES);
     plan.partials    = reinterpret_cast<float*>(static_cast<uint8_t*>(ws.ptr) + WS_HEADER_BYTES);
   }
   return plan;

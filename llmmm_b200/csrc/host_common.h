@@ -84,9 +84,9 @@ extern std::atomic<int> g_noalloc_dirty[64];
 // Caller-owned scratch registered with llmmm_set_workspace() for a device.  Layout: 16 KB unused, arrival
 // counters of the split tiles of the pair kernels (zero between launches), the pair kernels' partial tiles
 // (up to split_workspace_bytes()), then the decode kernel's flagged partial words (zero between launches).
-constexpr size_t WS_DECODE_COUNTER_BYTES = 16384;
+constexpr size_t WS_RESERVED_BYTES = 16384;  // unused (kept so that the layout behind it does not move)
 constexpr size_t WS_SK_COUNTER_BYTES     = 16384;
-constexpr size_t WS_HEADER_BYTES         = WS_DECODE_COUNTER_BYTES + WS_SK_COUNTER_BYTES;
+constexpr size_t WS_HEADER_BYTES         = WS_RESERVED_BYTES + WS_SK_COUNTER_BYTES;
 
 struct Workspace {
   void*  ptr   = nullptr;
