@@ -348,6 +348,14 @@ constexpr uint32_t OFF_B      = OFF_A + STAGES * A_BYTES;
 constexpr uint32_t OFF_BAR    = OFF_B + STAGES * B_BYTES;
 constexpr uint32_t OFF_XCH    = OFF_BAR + 256;  // 2 x 256 floats: row maxima exchanged between the column halves (SWIGLU)
 constexpr uint32_t SMEM_BYTES = OFF_XCH + 2048 + 1024;
+// EPI_ROPE keeps the angle-table rows of the tile's 128 rows in shared memory: 32 rows x (256 B cos | 256 B sin)
+// = 16 KB per row quarter.  Quarters 0 and 1 use the two slots of the ring's sixth stage (the ring runs with
+// five), quarters 2 and 3 the 32 KB from OFF_XCH on (nothing else of this instantiation lives there); the two
+// norm weight vectors follow.
+constexpr uint32_t ROPE_TAB_BYTES  = 32 * 512;
+constexpr uint32_t OFF_ROPE_W      = OFF_XCH + 2 * ROPE_TAB_BYTES;  // 2 x 128 floats: query and key norm weights
+constexpr uint32_t SMEM_BYTES_ROPE = OFF_ROPE_W + 1024 + 1024;
+static_assert(SMEM_BYTES_ROPE <= 232448, "EPI_ROPE: table rows + ring exceed the shared memory of an SM");
 constexpr uint32_t TMEM_COLS  = 512;  // two partial stages of 256 columns
 // split tiles (pair_walk.cuh): a slot holds 16 warp-sized units of 32 rows x 128 columns
 constexpr size_t   SK_UNIT_FLOATS = 32 * 128;
@@ -438,13 +446,24 @@ __device__ __forceinline__ float4 ldg_pinned(const float4* p)
   return v;
 }
 
-// EPI_ROPE without norm weights multiplies by these
-__device__ const float4 g_ones128_v[32] = {
-  {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1},
-  {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1},
-  {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1},
-  {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}, {1, 1, 1, 1}};
-#define g_ones128 (reinterpret_cast<const float*>(g_ones128_v))
+// the same for shared memory
+__device__ __forceinline__ float4 lds_pinned(uint32_t addr)
+{
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+
+// 16 bytes from global to shared memory without passing through registers (both addresses 16-byte aligned)
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src)
+{
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_wait_all()
+{
+  asm volatile("cp.async.wait_all;" ::: "memory");
+}
 
 template<int EPI>
 __global__ void __launch_bounds__(fp8pair::THREADS, 1)
@@ -626,8 +645,57 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
     PairWalk walk(pair, n_pairs, k_blocks, dp_tiles, split_pairs, split_s, split_chunk);
     int      tile, kb_lo, kb_hi;
     uint32_t tile_count = 0;  // SWIGLU: which exchange buffer
+    // EPI_ROPE: where this warp's row quarter keeps its angle-table rows (32 rows x 512 B, 16-byte chunks
+    // XOR-swizzled by row), shared by the two warps of the quarter, and the staged norm weights
+    uint32_t rope_tab = 0, rope_w = 0;
+    // position of this lane's output row in tile t (rows beyond M use the first position); only the load is
+    // issued here, the value is looked at a main loop later
+    auto rope_row = [&](int t) -> int {
+      const int mm = (t % m_tiles) * BM + (int)rank * 128 + quarter * 32 + lane;
+      return __ldg(rope.pos + (mm < M ? mm : 0));
+    };
+    // does tile t hold a query or key head?  (the same answer in both warps of a quarter)
+    auto rope_rotated = [&](int t) -> bool { return (t / m_tiles) * (BN / 128) < rope.n_q + rope.n_kv; };
+    // Asynchronous copies of the quarter's 32 table rows: this warp brings the cos halves (half 0) or the sin
+    // halves (half 1); one instruction moves two whole 256-byte half rows.  Nothing passes through registers and
+    // nobody waits here: the rows are needed one main loop later.
+    auto rope_stage = [&](int p_raw) {
+      const int p_own = min(max(p_raw, 0), rope.rows - 1);
+      if (p_own != p_raw) {
+        atomicCAS(status, 0u, (uint32_t)DEV_BAD_POSITION);  // the access outside the tables is not made
+      }
+      const float* tab   = half == 0 ? rope.cos : rope.sin;
+      const int    chunk = lane & 15;
+#pragma unroll 4
+      for (int j = 0; j < 16; ++j) {
+        const int rr = 2 * j + (lane >> 4);
+        const int pr = __shfl_sync(0xffffffffu, p_own, rr);
+        cp_async_16(rope_tab + rr * 512 + (((half * 16 + chunk) ^ (rr & 7)) << 4), tab + (size_t)pr * 64 + chunk * 4);
+      }
+    };
+    if constexpr (EPI == EPI_ROPE) {
+      rope_tab = smem_u32(smem + (quarter == 0   ? OFF_A + (STAGES - 1) * A_BYTES
+                                  : quarter == 1 ? OFF_B + (STAGES - 1) * B_BYTES
+                                                 : OFF_XCH + (quarter - 2) * ROPE_TAB_BYTES));
+      rope_w   = smem_u32(smem + OFF_ROPE_W);
+      // the norm weights (ones without a weight vector: one straight line of arithmetic either way)
+      const int    t    = (int)threadIdx.x - 128;
+      const float* wsrc = t < 128 ? rope.q_w : rope.k_w;
+      reinterpret_cast<float*>(smem + OFF_ROPE_W)[t] = wsrc != nullptr ? __ldg(wsrc + (t & 127)) : 1.0f;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (pair < dp_tiles && rope_rotated(pair)) {
+        rope_stage(rope_row(pair));
+      }
+    }
     PROF8_STAMP(0);
     while (walk.next(tile, kb_lo, kb_hi)) {
+      // EPI_ROPE: the position of this lane's row in the pair's next tile, fetched a main loop ahead of its use
+      int rope_p_next = 0;
+      if constexpr (EPI == EPI_ROPE) {
+        if (tile + n_pairs < dp_tiles && rope_rotated(tile + n_pairs)) {
+          rope_p_next = rope_row(tile + n_pairs);
+        }
+      }
       const int  m    = (tile % m_tiles) * BM + (int)rank * 128 + quarter * 32 + lane;
       // global 128-column group of the output (and, except for SWIGLU, of the weight scales)
       const int  ng   = SWIGLU ? tile / m_tiles : (tile / m_tiles) * (BN / 128) + half;
@@ -814,83 +882,58 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
         PROF8_STAMP(5);
       }
       if constexpr (EPI == EPI_ROPE) {
-        // ng is the head: query heads first, then key heads, then value heads (which pass unchanged).  The whole
-        // warp takes part, also lanes of rows beyond M: the angle-table rows go through shared memory.
+        // ng is the head: query heads first, then key heads, then value heads (which pass unchanged).
         const int kind = ng < rope.n_q ? 0 : (ng < rope.n_q + rope.n_kv ? 1 : 2);
-        if (g_ok && kind < 2) {
-          // one straight line of arithmetic with and without weights (a branch around 128 accumulator updates
-          // costs registers at the join): without weights the factors are exactly 1
-          const float* wgt = kind == 0 ? rope.q_w : rope.k_w;
-          const bool   nrm = wgt != nullptr;
-          float        ss4[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // four chains: a single one is 128 dependent FMAs
+        if (rope_rotated(tile)) {
+          // the table rows of this tile were requested a main loop ago: mine have landed, then the other warp's
+          cp_async_wait_all();
+          asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");
+          if (g_ok && kind < 2) {
+            float ss4[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // four chains: a single one is 128 dependent FMAs
 #pragma unroll
-          for (int i = 0; i < 128; ++i) {
-            ss4[i & 3] = fmaf(acc[i], acc[i], ss4[i & 3]);
-          }
-          const float ss = (ss4[0] + ss4[1]) + (ss4[2] + ss4[3]);
-          // (the approximate instruction, 2 ulp: the exact square root and reciprocal are subroutine calls, and a
-          // call here has to save accumulators on the stack)
-          const float   inv = nrm ? rsqrtf(fmaf(ss, 1.0f / 128.0f, rope.eps)) : 1.0f;
-          const float4* w4  = reinterpret_cast<const float4*>(nrm ? wgt : g_ones128);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if ((i & 3) == 0 && i > 0) {
-              asm volatile("" : "+f"(acc[4 * i - 1]));  // four loads in flight at most: the next group starts here
+            for (int i = 0; i < 128; ++i) {
+              ss4[i & 3] = fmaf(acc[i], acc[i], ss4[i & 3]);
             }
-            const float4 wv = ldg_pinned(w4 + i);  // the same address in every lane
-            acc[4 * i]      = acc[4 * i] * inv * wv.x;
-            acc[4 * i + 1]  = acc[4 * i + 1] * inv * wv.y;
-            acc[4 * i + 2]  = acc[4 * i + 2] * inv * wv.z;
-            acc[4 * i + 3]  = acc[4 * i + 3] * inv * wv.w;
-          }
-          // Rotation.  Lane l needs row pos[m_l] of both tables (2 x 256 bytes).  Read directly, every load
-          // instruction would touch 32 different cache lines; instead the warp fetches 16 columns of its 32 rows
-          // at a time with 64-byte pieces per row (8 lines per instruction) into a 4 KB staging tile
-          // (16-byte chunks XOR-swizzled by row) and every lane reads its own row from there.
-          uint8_t*  stg   = smem + (half == 0 ? OFF_A : OFF_B) + (STAGES - 1) * A_BYTES + quarter * 4096;
-          asm volatile("" : "+f"(acc[127]));  // (behind the normalisation)
-          const int p_raw = __ldg(rope.pos + (m_ok ? m : 0));
-          const int p_own = min(max(p_raw, 0), rope.rows - 1);
-          if (p_own != p_raw) {
-            atomicCAS(status, 0u, (uint32_t)DEV_BAD_POSITION);  // the access outside the tables is not made
-          }
-          const int part  = lane & 7;  // 0..3: cos chunk, 4..7: sin chunk
-          const float* tab = part < 4 ? rope.cos : rope.sin;
+            const float ss = (ss4[0] + ss4[1]) + (ss4[2] + ss4[3]);
+            // (the approximate instruction, 2 ulp: the exact square root and reciprocal are subroutine calls, and a
+            // call here has to save accumulators on the stack)
+            const bool     nrm = (kind == 0 ? rope.q_w : rope.k_w) != nullptr;
+            const float    inv = nrm ? rsqrtf(fmaf(ss, 1.0f / 128.0f, rope.eps)) : 1.0f;
+            const uint32_t w4  = rope_w + kind * 512;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-#pragma unroll
-            for (int b = 0; b < 2; ++b) {  // four loads in flight: addresses and data of eight do not fit
-              float4 ld[4];
-#pragma unroll
-              for (int jj = 0; jj < 4; ++jj) {
-                const int rr = 4 * (4 * b + jj) + (lane >> 3);
-                const int pr = __shfl_sync(0xffffffffu, p_own, rr);
-                ld[jj] = ldg_pinned(reinterpret_cast<const float4*>(tab + (size_t)pr * 64 + 16 * c) + (part & 3));
+            for (int i = 0; i < 32; ++i) {
+              if ((i & 3) == 0 && i > 0) {
+                asm volatile("" : "+f"(acc[4 * i - 1]));  // four loads in flight at most: the next group starts here
               }
-#pragma unroll
-              for (int jj = 0; jj < 4; ++jj) {
-                const int rr = 4 * (4 * b + jj) + (lane >> 3);
-                *reinterpret_cast<float4*>(stg + rr * 128 + ((part ^ (rr & 7)) << 4)) = ld[jj];
-              }
+              const float4 wv = lds_pinned(w4 + i * 16);  // the same address in every lane
+              acc[4 * i]      = acc[4 * i] * inv * wv.x;
+              acc[4 * i + 1]  = acc[4 * i + 1] * inv * wv.y;
+              acc[4 * i + 2]  = acc[4 * i + 2] * inv * wv.z;
+              acc[4 * i + 3]  = acc[4 * i + 3] * inv * wv.w;
             }
-            __syncwarp();
+            asm volatile("" : "+f"(acc[127]));  // (the rotation's loads start behind the normalisation)
+            // Rotation of the half-split pairs (i, 64 + i) by the angles of this lane's own table row.
+            const uint32_t row = rope_tab + lane * 512;
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              const float4 cv = *reinterpret_cast<const float4*>(stg + lane * 128 + ((q4 ^ (lane & 7)) << 4));
-              const float4 sn = *reinterpret_cast<const float4*>(stg + lane * 128 + (((4 + q4) ^ (lane & 7)) << 4));
+            for (int q4 = 0; q4 < 16; ++q4) {
+              const float4 cv = lds_pinned(row + ((q4 ^ (lane & 7)) << 4));
+              const float4 sn = lds_pinned(row + 256 + ((q4 ^ (lane & 7)) << 4));
               const float  cc[4] = {cv.x, cv.y, cv.z, cv.w};
               const float  sv[4] = {sn.x, sn.y, sn.z, sn.w};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                const int   i0 = 16 * c + 4 * q4 + e;
+                const int   i0 = 4 * q4 + e;
                 const float x0 = acc[i0], x1 = acc[64 + i0];
                 acc[i0]      = __fmaf_rn(x0, cc[e], -__fmul_rn(x1, sv[e]));
                 acc[64 + i0] = __fmaf_rn(x1, cc[e], __fmul_rn(x0, sv[e]));
               }
+              if ((q4 & 1) == 1) {
+                asm volatile("" : "+f"(acc[64 + 4 * q4 + 3]));  // four loads in flight at most
+              }
             }
-            __syncwarp();
-            asm volatile("" : "+f"(acc[64 + 16 * c + 15]));  // the next chunk's loads start behind this chunk's arithmetic
           }
+          // both warps of the quarter are done with the rows: the next tile's may be requested
+          asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");
         }
       }
       if constexpr (SWIGLU) {
@@ -1004,6 +1047,11 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
           C_s[(size_t)ng * M + m] = scale;
         }
       }
+      if constexpr (EPI == EPI_ROPE) {
+        if (tile + n_pairs < dp_tiles && rope_rotated(tile + n_pairs)) {
+          rope_stage(rope_p_next);
+        }
+      }
       PROF8_T(e1);
       PROF8_ADD(p_epi, e0, e1);
       if (kb_hi - kb_lo < k_blocks) {
@@ -1050,10 +1098,11 @@ static int launch_fp8_pair_epi(const void*       A,
       || !make_tmap_2d(&tm_b, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, 128, CU_TENSOR_MAP_SWIZZLE_128B)) {
     return LLMMM_ERR_CUDA;
   }
+  constexpr uint32_t SMEM = EPI == EPI_ROPE ? SMEM_BYTES_ROPE : SMEM_BYTES;
   static thread_local bool attr_set[64] = {};
   if (!attr_set[info->device]) {
     LLMMM_CUDA_TRY(cudaFuncSetAttribute(
-      fp8_blockwise_gemm_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+      fp8_blockwise_gemm_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
     attr_set[info->device] = true;
   }
   const int tiles    = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
@@ -1065,7 +1114,7 @@ static int launch_fp8_pair_epi(const void*       A,
     // whole tiles only: this instantiation has no code for the chunks of a cut tile (no register left for it)
     plan = SplitPlan{tiles, 0, 1, k_blocks, tiles < info->max_pairs ? tiles : info->max_pairs, nullptr, nullptr};
   }
-  LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<EPI>, dim3(2 * plan.pairs), dim3(THREADS), SMEM_BYTES, stream,
+  LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<EPI>, dim3(2 * plan.pairs), dim3(THREADS), SMEM, stream,
                             2, tm_a, tm_b, A_s, B_s, C, C_s, M, N, K, plan.dp_tiles, plan.split_pairs, plan.split_s,
                             plan.split_chunk, plan.partials, plan.counters, GatherDst{}, hook, info->status));
   g_launches.fetch_add(1);
@@ -1237,7 +1286,7 @@ int warm_fp8_kernels(const DeviceInfo* info)
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
-  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES_ROPE));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8cfg::SMEM_BYTES));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8cfg::SMEM_BYTES));
   return warm_decode_kernels(info);
