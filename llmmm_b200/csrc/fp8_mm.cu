@@ -348,13 +348,23 @@ constexpr uint32_t OFF_B      = OFF_A + STAGES * A_BYTES;
 constexpr uint32_t OFF_BAR    = OFF_B + STAGES * B_BYTES;
 constexpr uint32_t OFF_XCH    = OFF_BAR + 256;  // 2 x 256 floats: row maxima exchanged between the column halves (SWIGLU)
 constexpr uint32_t SMEM_BYTES = OFF_XCH + 2048 + 1024;
+// The e4m3 epilogues transpose each promotion warp's 32 x 128-byte output tile through 4 KB of shared memory, so
+// that a store instruction writes four whole rows instead of 32 pieces of 16 bytes in 32 rows.  EPI_E4M3 and
+// EPI_GATHER keep the eight staging tiles from OFF_XCH on (the exchange buffer there is SWIGLU's alone).
+constexpr uint32_t SMEM_BYTES_STAGED = OFF_XCH + 8 * 4096 + 1024;
+static_assert(SMEM_BYTES_STAGED <= 232448, "staging tiles + ring exceed the shared memory of an SM");
 // EPI_ROPE keeps the angle-table rows of the tile's 128 rows in shared memory: 32 rows x (256 B cos | 256 B sin)
 // = 16 KB per row quarter.  Quarters 0 and 1 use the two slots of the ring's sixth stage (the ring runs with
-// five), quarters 2 and 3 the 32 KB from OFF_XCH on (nothing else of this instantiation lives there); the two
-// norm weight vectors follow.
+// five), quarters 2 and 3 the 32 KB from OFF_XCH on; the two norm weight vectors follow.  Once a tile's rows have
+// been used, the first 8 KB of each quarter's region serve as the two staging tiles of its warps.
 constexpr uint32_t ROPE_TAB_BYTES  = 32 * 512;
 constexpr uint32_t OFF_ROPE_W      = OFF_XCH + 2 * ROPE_TAB_BYTES;  // 2 x 128 floats: query and key norm weights
 constexpr uint32_t SMEM_BYTES_ROPE = OFF_ROPE_W + 1024 + 1024;
+
+constexpr uint32_t smem_bytes_of(int epi)  // (the EPI_* constants: 0 e4m3, 3 gather, 4 rope)
+{
+  return epi == 4 ? SMEM_BYTES_ROPE : (epi == 0 || epi == 3) ? SMEM_BYTES_STAGED : SMEM_BYTES;
+}
 static_assert(SMEM_BYTES_ROPE <= 232448, "EPI_ROPE: table rows + ring exceed the shared memory of an SM");
 constexpr uint32_t TMEM_COLS  = 512;  // two partial stages of 256 columns
 // split tiles (pair_walk.cuh): a slot holds 16 warp-sized units of 32 rows x 128 columns
@@ -446,6 +456,17 @@ __device__ __forceinline__ float4 ldg_pinned(const float4* p)
   return v;
 }
 
+// largest magnitude of a thread's 128 accumulators, in four chains (one chain is 128 dependent instructions)
+__device__ __forceinline__ float amax128(const float (&acc)[128])
+{
+  float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+  for (int i = 0; i < 128; ++i) {
+    a[i & 3] = fmaxf(a[i & 3], fabsf(acc[i]));
+  }
+  return fmaxf(fmaxf(a[0], a[1]), fmaxf(a[2], a[3]));
+}
+
 // the same for shared memory
 __device__ __forceinline__ float4 lds_pinned(uint32_t addr)
 {
@@ -490,10 +511,8 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
   constexpr bool OUT_F32 = (EPI == EPI_F32);
   constexpr bool SWIGLU  = (EPI == EPI_SWIGLU);
   constexpr int  TILE_N  = SWIGLU ? 128 : BN;  // output columns per tile
-  // EPI_GATHER runs the ring one stage shorter: the sixth stage's two 16 KB slots stage the output tile so that
-  // the stores to the other GPUs leave as whole 128-byte rows
-  // (EPI_ROPE stages its angle-table rows in the same slots)
-  constexpr uint32_t NSTAGES = (EPI == EPI_GATHER || EPI == EPI_ROPE) ? STAGES - 1 : STAGES;
+  // EPI_ROPE runs the ring one stage shorter: the sixth stage's two 16 KB slots hold angle-table rows
+  constexpr uint32_t NSTAGES = EPI == EPI_ROPE ? STAGES - 1 : STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Fp8PairBars*       bars       = reinterpret_cast<Fp8PairBars*>(smem + OFF_BAR);
@@ -647,19 +666,24 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
     uint32_t tile_count = 0;  // SWIGLU: which exchange buffer
     // EPI_ROPE: where this warp's row quarter keeps its angle-table rows (32 rows x 512 B, 16-byte chunks
     // XOR-swizzled by row), shared by the two warps of the quarter, and the staged norm weights
-    uint32_t rope_tab = 0, rope_w = 0;
+    const uint32_t rope_off = EPI != EPI_ROPE ? 0u
+                              : quarter == 0  ? OFF_A + (STAGES - 1) * A_BYTES
+                              : quarter == 1  ? OFF_B + (STAGES - 1) * B_BYTES
+                                              : OFF_XCH + (quarter - 2) * ROPE_TAB_BYTES;
+    const uint32_t rope_tab = smem_u32(smem + rope_off);
+    const uint32_t rope_w   = smem_u32(smem + OFF_ROPE_W);
     // position of this lane's output row in tile t (rows beyond M use the first position); only the load is
     // issued here, the value is looked at a main loop later
-    auto rope_row = [&](int t) -> int {
+    auto rope_row = [=](int t) -> int {
       const int mm = (t % m_tiles) * BM + (int)rank * 128 + quarter * 32 + lane;
       return __ldg(rope.pos + (mm < M ? mm : 0));
     };
     // does tile t hold a query or key head?  (the same answer in both warps of a quarter)
-    auto rope_rotated = [&](int t) -> bool { return (t / m_tiles) * (BN / 128) < rope.n_q + rope.n_kv; };
+    auto rope_rotated = [=](int t) -> bool { return (t / m_tiles) * (BN / 128) < rope.n_q + rope.n_kv; };
     // Asynchronous copies of the quarter's 32 table rows: this warp brings the cos halves (half 0) or the sin
     // halves (half 1); one instruction moves two whole 256-byte half rows.  Nothing passes through registers and
     // nobody waits here: the rows are needed one main loop later.
-    auto rope_stage = [&](int p_raw) {
+    auto rope_stage = [=](int p_raw) {
       const int p_own = min(max(p_raw, 0), rope.rows - 1);
       if (p_own != p_raw) {
         atomicCAS(status, 0u, (uint32_t)DEV_BAD_POSITION);  // the access outside the tables is not made
@@ -674,10 +698,6 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
       }
     };
     if constexpr (EPI == EPI_ROPE) {
-      rope_tab = smem_u32(smem + (quarter == 0   ? OFF_A + (STAGES - 1) * A_BYTES
-                                  : quarter == 1 ? OFF_B + (STAGES - 1) * B_BYTES
-                                                 : OFF_XCH + (quarter - 2) * ROPE_TAB_BYTES));
-      rope_w   = smem_u32(smem + OFF_ROPE_W);
       // the norm weights (ones without a weight vector: one straight line of arithmetic either way)
       const int    t    = (int)threadIdx.x - 128;
       const float* wsrc = t < 128 ? rope.q_w : rope.k_w;
@@ -971,15 +991,11 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
           }
         }
       }
-      else if constexpr (EPI == EPI_GATHER) {
+      else if constexpr (EPI == EPI_E4M3 || EPI == EPI_GATHER || EPI == EPI_ROPE) {
         // The whole warp takes part, also lanes of rows beyond M: the tile is transposed through shared memory.
-        uint8_t* stg = smem + (half == 0 ? OFF_A : OFF_B) + (STAGES - 1) * A_BYTES + quarter * 4096;
+        uint8_t* stg = smem + (EPI == EPI_ROPE ? rope_off + half * 4096 : OFF_XCH + (warp - 4) * 4096);
         {
-          float amax = 0.0f;
-#pragma unroll
-          for (int i = 0; i < 128; ++i) {
-            amax = fmaxf(amax, fabsf(acc[i]));
-          }
+          const float amax      = amax128(acc);
           const float scale     = __fdiv_rn(amax, 448.0f);
           const float scale_inv = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 0.0f;
           // this thread's 128 bytes go to its row of the warp's staging tile (16-byte chunks XOR-swizzled by row)
@@ -992,26 +1008,36 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
             o.w = pack_e4m3x4(acc[16 * i + 12] * scale_inv, acc[16 * i + 13] * scale_inv, acc[16 * i + 14] * scale_inv, acc[16 * i + 15] * scale_inv);
             *reinterpret_cast<uint4*>(stg + lane * 128 + ((i ^ (lane & 7)) << 4)) = o;
           }
-          if (m_ok && g_ok) {
-            const size_t s_off = (size_t)(gather.col0 / 128 + ng) * M + m;
-            for (int d = 0; d < gather.n; ++d) {
-              gather.cs[d][s_off] = scale;  // 32 consecutive floats per warp
+          if (m_ok && g_ok) {  // 32 consecutive floats per warp
+            if constexpr (EPI == EPI_GATHER) {
+              const size_t s_off = (size_t)(gather.col0 / 128 + ng) * M + m;
+              for (int d = 0; d < gather.n; ++d) {
+                gather.cs[d][s_off] = scale;
+              }
+            }
+            else {
+              C_s[(size_t)ng * M + m] = scale;
             }
           }
         }
         __syncwarp();
-        // one store instruction now covers four whole rows: lane l writes chunk l & 7 of row 4 i + (l >> 3), so
-        // that what crosses to the other GPUs are contiguous 128-byte rows, not 16-byte pieces
+        // one store instruction now covers four whole rows: lane l writes chunk l & 7 of row 4 i + (l >> 3)
+        // (for EPI_GATHER: what crosses to the other GPUs are contiguous 128-byte rows, not 16-byte pieces)
         if (g_ok) {
           const int    m_warp = m - lane;
-          const size_t col    = (size_t)gather.col0 + (size_t)ng * 128 + (size_t)((lane & 7) << 4);
+          const size_t col    = (size_t)(EPI == EPI_GATHER ? gather.col0 : 0) + (size_t)ng * 128 + (size_t)((lane & 7) << 4);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int   rr = 4 * i + (lane >> 3);
             const uint4 o  = *reinterpret_cast<const uint4*>(stg + rr * 128 + (((lane & 7) ^ (rr & 7)) << 4));
             if (m_warp + rr < M) {
-              for (int d = 0; d < gather.n; ++d) {
-                *reinterpret_cast<uint4*>(gather.c[d] + (size_t)(m_warp + rr) * gather.ld + col) = o;
+              if constexpr (EPI == EPI_GATHER) {
+                for (int d = 0; d < gather.n; ++d) {
+                  *reinterpret_cast<uint4*>(gather.c[d] + (size_t)(m_warp + rr) * gather.ld + col) = o;
+                }
+              }
+              else {
+                *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(C_out) + (size_t)(m_warp + rr) * N + col) = o;
               }
             }
           }
@@ -1019,6 +1045,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
         __syncwarp();
       }
       else if (m_ok && g_ok) {
+        static_assert(EPI == EPI_F32 || EPI == EPI_SWIGLU, "every e4m3 epilogue is handled above");
         if constexpr (OUT_F32) {
           float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(C_out) + (size_t)m * N + (size_t)ng * 128);
 #pragma unroll
@@ -1026,29 +1053,11 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
             dst[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
           }
         }
-        else {
-          float amax = 0.0f;
-#pragma unroll
-          for (int i = 0; i < 128; ++i) {
-            amax = fmaxf(amax, fabsf(acc[i]));
-          }
-          const float scale     = __fdiv_rn(amax, 448.0f);
-          const float scale_inv = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 0.0f;
-          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(C_out) + (size_t)m * N + (size_t)ng * 128);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            uint4 o;
-            o.x    = pack_e4m3x4(acc[16 * i + 0] * scale_inv, acc[16 * i + 1] * scale_inv, acc[16 * i + 2] * scale_inv, acc[16 * i + 3] * scale_inv);
-            o.y    = pack_e4m3x4(acc[16 * i + 4] * scale_inv, acc[16 * i + 5] * scale_inv, acc[16 * i + 6] * scale_inv, acc[16 * i + 7] * scale_inv);
-            o.z    = pack_e4m3x4(acc[16 * i + 8] * scale_inv, acc[16 * i + 9] * scale_inv, acc[16 * i + 10] * scale_inv, acc[16 * i + 11] * scale_inv);
-            o.w    = pack_e4m3x4(acc[16 * i + 12] * scale_inv, acc[16 * i + 13] * scale_inv, acc[16 * i + 14] * scale_inv, acc[16 * i + 15] * scale_inv);
-            dst[i] = o;
-          }
-          C_s[(size_t)ng * M + m] = scale;
-        }
       }
       if constexpr (EPI == EPI_ROPE) {
         if (tile + n_pairs < dp_tiles && rope_rotated(tile + n_pairs)) {
+          // (both warps of the quarter have read their staging tiles, which lie in the region the rows go to)
+          asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");
           rope_stage(rope_p_next);
         }
       }
@@ -1098,7 +1107,7 @@ static int launch_fp8_pair_epi(const void*       A,
       || !make_tmap_2d(&tm_b, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, 128, CU_TENSOR_MAP_SWIZZLE_128B)) {
     return LLMMM_ERR_CUDA;
   }
-  constexpr uint32_t SMEM = EPI == EPI_ROPE ? SMEM_BYTES_ROPE : SMEM_BYTES;
+  constexpr uint32_t SMEM = smem_bytes_of(EPI);
   static thread_local bool attr_set[64] = {};
   if (!attr_set[info->device]) {
     LLMMM_CUDA_TRY(cudaFuncSetAttribute(
@@ -1187,13 +1196,13 @@ static int launch_fp8_gather(const void*       A,
   static thread_local bool attr_set[64] = {};
   if (!attr_set[info->device]) {
     LLMMM_CUDA_TRY(cudaFuncSetAttribute(
-      fp8_blockwise_gemm_pair_kernel<EPI_GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+      fp8_blockwise_gemm_pair_kernel<EPI_GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES_STAGED));
     attr_set[info->device] = true;
   }
   const int       tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const SplitPlan plan  = plan_split(info, tiles, K / BK, /*fixed*/ 4, /*per_way_x2*/ 5, /*min_gain*/ 3);
   float*          none  = nullptr;
-  LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<EPI_GATHER>, dim3(2 * plan.pairs), dim3(THREADS), SMEM_BYTES, stream, 2,
+  LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<EPI_GATHER>, dim3(2 * plan.pairs), dim3(THREADS), SMEM_BYTES_STAGED, stream, 2,
                             tm_a, tm_b, A_s, B_s, static_cast<void*>(nullptr), none, M, N, K, plan.dp_tiles, plan.split_pairs,
                             plan.split_s, plan.split_chunk, plan.partials, plan.counters, dst, RopeHook{}, info->status));
   g_launches.fetch_add(1);
@@ -1282,10 +1291,10 @@ int launch_fp8_e4m3(const void* A, const float* A_s, const void* B, const float*
 int warm_fp8_kernels(const DeviceInfo* info)
 {
   (void)info;
-  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_E4M3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_E4M3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES_STAGED));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
-  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES_STAGED));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES_ROPE));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8cfg::SMEM_BYTES));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8cfg::SMEM_BYTES));
