@@ -348,24 +348,26 @@ constexpr uint32_t OFF_B      = OFF_A + STAGES * A_BYTES;
 constexpr uint32_t OFF_BAR    = OFF_B + STAGES * B_BYTES;
 constexpr uint32_t OFF_XCH    = OFF_BAR + 256;  // 2 x 256 floats: row maxima exchanged between the column halves (SWIGLU)
 constexpr uint32_t SMEM_BYTES = OFF_XCH + 2048 + 1024;
-// The e4m3 epilogues transpose each promotion warp's 32 x 128-byte output tile through 4 KB of shared memory, so
-// that a store instruction writes four whole rows instead of 32 pieces of 16 bytes in 32 rows.  EPI_E4M3 and
-// EPI_GATHER keep the eight staging tiles from OFF_XCH on (the exchange buffer there is SWIGLU's alone).
-constexpr uint32_t SMEM_BYTES_STAGED = OFF_XCH + 8 * 4096 + 1024;
+// The e4m3 epilogues transpose each promotion warp's 32 x 128-byte output tile through 4 KB of shared memory
+// (16-byte chunks XOR-swizzled by row, which is the 128-byte swizzle of a tensor map), so that the tile leaves as
+// whole rows: one TMA store per warp (EPI_E4M3) or store instructions that cover four rows each.  EPI_E4M3 and
+// EPI_GATHER keep the eight staging tiles from OFF_STG on (1024-byte aligned; SWIGLU's exchange buffer overlaps
+// it, that instantiation has no staging tiles).
+constexpr uint32_t OFF_STG           = OFF_BAR + 1024;
+constexpr uint32_t SMEM_BYTES_STAGED = OFF_STG + 8 * 4096 + 1024;
 static_assert(SMEM_BYTES_STAGED <= 232448, "staging tiles + ring exceed the shared memory of an SM");
 // EPI_ROPE keeps the angle-table rows of the tile's 128 rows in shared memory: 32 rows x (256 B cos | 256 B sin)
 // = 16 KB per row quarter.  Quarters 0 and 1 use the two slots of the ring's sixth stage (the ring runs with
-// five), quarters 2 and 3 the 32 KB from OFF_XCH on; the two norm weight vectors follow.  Once a tile's rows have
+// five), quarters 2 and 3 the 32 KB from OFF_STG on; the two norm weight vectors follow.  Once a tile's rows have
 // been used, the first 8 KB of each quarter's region serve as the two staging tiles of its warps.
 constexpr uint32_t ROPE_TAB_BYTES  = 32 * 512;
-constexpr uint32_t OFF_ROPE_W      = OFF_XCH + 2 * ROPE_TAB_BYTES;  // 2 x 128 floats: query and key norm weights
+constexpr uint32_t OFF_ROPE_W      = OFF_STG + 2 * ROPE_TAB_BYTES;  // 2 x 128 floats: query and key norm weights
 constexpr uint32_t SMEM_BYTES_ROPE = OFF_ROPE_W + 1024 + 1024;
 
 constexpr uint32_t smem_bytes_of(int epi)  // (the EPI_* constants: 0 e4m3, 3 gather, 4 rope)
 {
   return epi == 4 ? SMEM_BYTES_ROPE : (epi == 0 || epi == 3) ? SMEM_BYTES_STAGED : SMEM_BYTES;
 }
-static_assert(SMEM_BYTES_ROPE <= 232448, "EPI_ROPE: table rows + ring exceed the shared memory of an SM");
 constexpr uint32_t TMEM_COLS  = 512;  // two partial stages of 256 columns
 // split tiles (pair_walk.cuh): a slot holds 16 warp-sized units of 32 rows x 128 columns
 constexpr size_t   SK_UNIT_FLOATS = 32 * 128;
@@ -490,6 +492,7 @@ template<int EPI>
 __global__ void __launch_bounds__(fp8pair::THREADS, 1)
   fp8_blockwise_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
                                  const __grid_constant__ CUtensorMap tm_b,
+                                 const __grid_constant__ CUtensorMap tm_c,  // EPI_E4M3: C as [M, N] bytes, boxes of 32 rows x 128
                                  const float* __restrict__ A_s,
                                  const float* __restrict__ B_s,
                                  void* __restrict__ C_out,
@@ -541,6 +544,9 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
     fence_mbar_init();
     prefetch_tmap(&tm_a);
     prefetch_tmap(&tm_b);
+    if constexpr (EPI == EPI_E4M3) {
+      prefetch_tmap(&tm_c);
+    }
   }
   if (warp == 2) {
     tmem_alloc<TMEM_COLS>(&bars->tmem_base);
@@ -669,7 +675,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
     const uint32_t rope_off = EPI != EPI_ROPE ? 0u
                               : quarter == 0  ? OFF_A + (STAGES - 1) * A_BYTES
                               : quarter == 1  ? OFF_B + (STAGES - 1) * B_BYTES
-                                              : OFF_XCH + (quarter - 2) * ROPE_TAB_BYTES;
+                                              : OFF_STG + (quarter - 2) * ROPE_TAB_BYTES;
     const uint32_t rope_tab = smem_u32(smem + rope_off);
     const uint32_t rope_w   = smem_u32(smem + OFF_ROPE_W);
     // position of this lane's output row in tile t (rows beyond M use the first position); only the load is
@@ -993,7 +999,14 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
       }
       else if constexpr (EPI == EPI_E4M3 || EPI == EPI_GATHER || EPI == EPI_ROPE) {
         // The whole warp takes part, also lanes of rows beyond M: the tile is transposed through shared memory.
-        uint8_t* stg = smem + (EPI == EPI_ROPE ? rope_off + half * 4096 : OFF_XCH + (warp - 4) * 4096);
+        uint8_t* stg = smem + (EPI == EPI_ROPE ? rope_off + half * 4096 : OFF_STG + (warp - 4) * 4096);
+        if constexpr (EPI == EPI_E4M3) {
+          // the TMA store of this warp's previous tile has read the staging tile (it had a main loop's time)
+          if (lane == 0) {
+            tma_store_wait_read<0>();
+          }
+          __syncwarp();
+        }
         {
           const float amax      = amax128(acc);
           const float scale     = __fdiv_rn(amax, 448.0f);
@@ -1020,6 +1033,16 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
             }
           }
         }
+        if constexpr (EPI == EPI_E4M3) {
+          // one asynchronous store of the whole 32 x 128-byte tile; rows beyond M are clipped by the tensor map
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && g_ok && m - lane < M) {
+            tma_store_2d(&tm_c, stg, ng * 128, m - lane);
+            tma_store_commit();
+          }
+        }
+        else {
         __syncwarp();
         // one store instruction now covers four whole rows: lane l writes chunk l & 7 of row 4 i + (l >> 3)
         // (for EPI_GATHER: what crosses to the other GPUs are contiguous 128-byte rows, not 16-byte pieces)
@@ -1043,6 +1066,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
           }
         }
         __syncwarp();
+        }
       }
       else if (m_ok && g_ok) {
         static_assert(EPI == EPI_F32 || EPI == EPI_SWIGLU, "every e4m3 epilogue is handled above");
@@ -1065,6 +1089,11 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
       PROF8_ADD(p_epi, e0, e1);
       if (kb_hi - kb_lo < k_blocks) {
         PROF8_STAMP(6);
+      }
+    }
+    if constexpr (EPI == EPI_E4M3) {
+      if (lane == 0) {
+        tma_store_wait_read<0>();  // shared memory must outlive the last store's read of it
       }
     }
 #ifdef LLMMM_PROFILE
@@ -1107,6 +1136,12 @@ static int launch_fp8_pair_epi(const void*       A,
       || !make_tmap_2d(&tm_b, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, 128, CU_TENSOR_MAP_SWIZZLE_128B)) {
     return LLMMM_ERR_CUDA;
   }
+  CUtensorMap tm_c = {};
+  if constexpr (EPI == EPI_E4M3) {
+    if (!make_tmap_2d(&tm_c, C, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)N, (uint64_t)M, (uint64_t)N, 128, 32, CU_TENSOR_MAP_SWIZZLE_128B)) {
+      return LLMMM_ERR_CUDA;
+    }
+  }
   constexpr uint32_t SMEM = smem_bytes_of(EPI);
   static thread_local bool attr_set[64] = {};
   if (!attr_set[info->device]) {
@@ -1124,7 +1159,7 @@ static int launch_fp8_pair_epi(const void*       A,
     plan = SplitPlan{tiles, 0, 1, k_blocks, tiles < info->max_pairs ? tiles : info->max_pairs, nullptr, nullptr};
   }
   LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<EPI>, dim3(2 * plan.pairs), dim3(THREADS), SMEM, stream,
-                            2, tm_a, tm_b, A_s, B_s, C, C_s, M, N, K, plan.dp_tiles, plan.split_pairs, plan.split_s,
+                            2, tm_a, tm_b, tm_c, A_s, B_s, C, C_s, M, N, K, plan.dp_tiles, plan.split_pairs, plan.split_s,
                             plan.split_chunk, plan.partials, plan.counters, GatherDst{}, hook, info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
@@ -1169,7 +1204,7 @@ static int launch_fp8_swiglu(const void*       A,
   float*    no_partials = nullptr;
   uint32_t* no_counters = nullptr;
   LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<EPI_SWIGLU>, dim3(2 * pairs), dim3(THREADS), SMEM_BYTES, stream, 2,
-                            tm_a, tm_b, A_s, B_s, H, H_s, M, I, K, tiles, 0, 1, K / BK, no_partials, no_counters,
+                            tm_a, tm_b, CUtensorMap{}, A_s, B_s, H, H_s, M, I, K, tiles, 0, 1, K / BK, no_partials, no_counters,
                             GatherDst{}, RopeHook{}, info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
@@ -1203,7 +1238,7 @@ static int launch_fp8_gather(const void*       A,
   const SplitPlan plan  = plan_split(info, tiles, K / BK, /*fixed*/ 4, /*per_way_x2*/ 5, /*min_gain*/ 3);
   float*          none  = nullptr;
   LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<EPI_GATHER>, dim3(2 * plan.pairs), dim3(THREADS), SMEM_BYTES_STAGED, stream, 2,
-                            tm_a, tm_b, A_s, B_s, static_cast<void*>(nullptr), none, M, N, K, plan.dp_tiles, plan.split_pairs,
+                            tm_a, tm_b, CUtensorMap{}, A_s, B_s, static_cast<void*>(nullptr), none, M, N, K, plan.dp_tiles, plan.split_pairs,
                             plan.split_s, plan.split_chunk, plan.partials, plan.counters, dst, RopeHook{}, info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
