@@ -492,7 +492,7 @@ template<int EPI>
 __global__ void __launch_bounds__(fp8pair::THREADS, 1)
   fp8_blockwise_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
                                  const __grid_constant__ CUtensorMap tm_b,
-                                 const __grid_constant__ CUtensorMap tm_c,  // EPI_E4M3: C as [M, N] bytes, boxes of 32 rows x 128
+                                 const __grid_constant__ CUtensorMap tm_c,  // EPI_E4M3, EPI_ROPE: C as [M, N] bytes, boxes of 32 rows x 128
                                  const float* __restrict__ A_s,
                                  const float* __restrict__ B_s,
                                  void* __restrict__ C_out,
@@ -544,7 +544,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
     fence_mbar_init();
     prefetch_tmap(&tm_a);
     prefetch_tmap(&tm_b);
-    if constexpr (EPI == EPI_E4M3) {
+    if constexpr (EPI == EPI_E4M3 || EPI == EPI_ROPE) {
       prefetch_tmap(&tm_c);
     }
   }
@@ -1000,7 +1000,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
       else if constexpr (EPI == EPI_E4M3 || EPI == EPI_GATHER || EPI == EPI_ROPE) {
         // The whole warp takes part, also lanes of rows beyond M: the tile is transposed through shared memory.
         uint8_t* stg = smem + (EPI == EPI_ROPE ? rope_off + half * 4096 : OFF_STG + (warp - 4) * 4096);
-        if constexpr (EPI == EPI_E4M3) {
+        if constexpr (EPI == EPI_E4M3 || EPI == EPI_ROPE) {
           // the TMA store of this warp's previous tile has read the staging tile (it had a main loop's time)
           if (lane == 0) {
             tma_store_wait_read<0>();
@@ -1033,7 +1033,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
             }
           }
         }
-        if constexpr (EPI == EPI_E4M3) {
+        if constexpr (EPI == EPI_E4M3 || EPI == EPI_ROPE) {
           // one asynchronous store of the whole 32 x 128-byte tile; rows beyond M are clipped by the tensor map
           fence_proxy_async_smem();
           __syncwarp();
@@ -1080,7 +1080,11 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
       }
       if constexpr (EPI == EPI_ROPE) {
         if (tile + n_pairs < dp_tiles && rope_rotated(tile + n_pairs)) {
-          // (both warps of the quarter have read their staging tiles, which lie in the region the rows go to)
+          // (the stores of both warps of the quarter have read their staging tiles, which lie in the region the
+          // rows go to)
+          if (lane == 0) {
+            tma_store_wait_read<0>();
+          }
           asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");
           rope_stage(rope_p_next);
         }
@@ -1091,7 +1095,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
         PROF8_STAMP(6);
       }
     }
-    if constexpr (EPI == EPI_E4M3) {
+    if constexpr (EPI == EPI_E4M3 || EPI == EPI_ROPE) {
       if (lane == 0) {
         tma_store_wait_read<0>();  // shared memory must outlive the last store's read of it
       }
@@ -1137,7 +1141,7 @@ static int launch_fp8_pair_epi(const void*       A,
     return LLMMM_ERR_CUDA;
   }
   CUtensorMap tm_c = {};
-  if constexpr (EPI == EPI_E4M3) {
+  if constexpr (EPI == EPI_E4M3 || EPI == EPI_ROPE) {
     if (!make_tmap_2d(&tm_c, C, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)N, (uint64_t)M, (uint64_t)N, 128, 32, CU_TENSOR_MAP_SWIZZLE_128B)) {
       return LLMMM_ERR_CUDA;
     }
