@@ -364,9 +364,9 @@ constexpr uint32_t ROPE_TAB_BYTES  = 32 * 512;
 constexpr uint32_t OFF_ROPE_W      = OFF_STG + 2 * ROPE_TAB_BYTES;  // 2 x 128 floats: query and key norm weights
 constexpr uint32_t SMEM_BYTES_ROPE = OFF_ROPE_W + 1024 + 1024;
 
-constexpr uint32_t smem_bytes_of(int epi)  // (the EPI_* constants: 0 e4m3, 3 gather, 4 rope)
+constexpr uint32_t smem_bytes_of(int epi)  // (the EPI_* constants: 2 swiglu, 4 rope)
 {
-  return epi == 4 ? SMEM_BYTES_ROPE : (epi == 0 || epi == 3) ? SMEM_BYTES_STAGED : SMEM_BYTES;
+  return epi == 4 ? SMEM_BYTES_ROPE : epi == 2 ? SMEM_BYTES : SMEM_BYTES_STAGED;
 }
 constexpr uint32_t TMEM_COLS  = 512;  // two partial stages of 256 columns
 // split tiles (pair_walk.cuh): a slot holds 16 warp-sized units of 32 rows x 128 columns
@@ -492,7 +492,7 @@ template<int EPI>
 __global__ void __launch_bounds__(fp8pair::THREADS, 1)
   fp8_blockwise_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
                                  const __grid_constant__ CUtensorMap tm_b,
-                                 const __grid_constant__ CUtensorMap tm_c,  // EPI_E4M3, EPI_ROPE: C as [M, N] bytes, boxes of 32 rows x 128
+                                 const __grid_constant__ CUtensorMap tm_c,  // C as rows of bytes, boxes of 32 rows x 128 bytes (not SWIGLU, GATHER)
                                  const float* __restrict__ A_s,
                                  const float* __restrict__ B_s,
                                  void* __restrict__ C_out,
@@ -544,7 +544,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
     fence_mbar_init();
     prefetch_tmap(&tm_a);
     prefetch_tmap(&tm_b);
-    if constexpr (EPI == EPI_E4M3 || EPI == EPI_ROPE) {
+    if constexpr (EPI == EPI_E4M3 || EPI == EPI_ROPE || EPI == EPI_F32) {
       prefetch_tmap(&tm_c);
     }
   }
@@ -1068,15 +1068,32 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
         __syncwarp();
         }
       }
-      else if (m_ok && g_ok) {
-        static_assert(EPI == EPI_F32 || EPI == EPI_SWIGLU, "every e4m3 epilogue is handled above");
-        if constexpr (OUT_F32) {
-          float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(C_out) + (size_t)m * N + (size_t)ng * 128);
+      else if constexpr (OUT_F32) {
+        // A thread's row of the tile is 512 bytes; written directly, every store instruction would touch 32 rows.
+        // Four passes of 32 columns each through the warp's staging tile instead, each leaving as one TMA store
+        // (the tensor map sees C as [M, 4 N] bytes).  The whole warp takes part; rows beyond M are clipped.
+        uint8_t* stg = smem + OFF_STG + (warp - 4) * 4096;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            dst[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+        for (int ps = 0; ps < 4; ++ps) {
+          if (lane == 0) {
+            tma_store_wait_read<0>();  // the previous store has read the staging tile
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            *reinterpret_cast<float4*>(stg + lane * 128 + ((i ^ (lane & 7)) << 4)) =
+              make_float4(acc[32 * ps + 4 * i], acc[32 * ps + 4 * i + 1], acc[32 * ps + 4 * i + 2], acc[32 * ps + 4 * i + 3]);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && g_ok && m - lane < M) {
+            tma_store_2d(&tm_c, stg, ng * 512 + ps * 128, m - lane);
+            tma_store_commit();
           }
         }
+      }
+      else {
+        static_assert(EPI == EPI_SWIGLU, "every other epilogue is handled above");
       }
       if constexpr (EPI == EPI_ROPE) {
         if (tile + n_pairs < dp_tiles && rope_rotated(tile + n_pairs)) {
@@ -1095,7 +1112,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
         PROF8_STAMP(6);
       }
     }
-    if constexpr (EPI == EPI_E4M3 || EPI == EPI_ROPE) {
+    if constexpr (EPI == EPI_E4M3 || EPI == EPI_ROPE || EPI == EPI_F32) {
       if (lane == 0) {
         tma_store_wait_read<0>();  // shared memory must outlive the last store's read of it
       }
@@ -1141,8 +1158,9 @@ static int launch_fp8_pair_epi(const void*       A,
     return LLMMM_ERR_CUDA;
   }
   CUtensorMap tm_c = {};
-  if constexpr (EPI == EPI_E4M3 || EPI == EPI_ROPE) {
-    if (!make_tmap_2d(&tm_c, C, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)N, (uint64_t)M, (uint64_t)N, 128, 32, CU_TENSOR_MAP_SWIZZLE_128B)) {
+  if constexpr (EPI == EPI_E4M3 || EPI == EPI_ROPE || EPI == EPI_F32) {
+    const uint64_t row_bytes = (uint64_t)N * (EPI == EPI_F32 ? 4 : 1);
+    if (!make_tmap_2d(&tm_c, C, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, row_bytes, (uint64_t)M, row_bytes, 128, 32, CU_TENSOR_MAP_SWIZZLE_128B)) {
       return LLMMM_ERR_CUDA;
     }
   }
@@ -1331,7 +1349,7 @@ int warm_fp8_kernels(const DeviceInfo* info)
 {
   (void)info;
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_E4M3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES_STAGED));
-  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES_STAGED));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES_STAGED));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES_ROPE));
