@@ -347,7 +347,6 @@ constexpr uint32_t OFF_A      = 0;
 constexpr uint32_t OFF_B      = OFF_A + STAGES * A_BYTES;
 constexpr uint32_t OFF_BAR    = OFF_B + STAGES * B_BYTES;
 constexpr uint32_t OFF_XCH    = OFF_BAR + 256;  // 2 x 256 floats: row maxima exchanged between the column halves (SWIGLU)
-constexpr uint32_t SMEM_BYTES = OFF_XCH + 2048 + 1024;
 // The e4m3 epilogues transpose each promotion warp's 32 x 128-byte output tile through 4 KB of shared memory
 // (16-byte chunks XOR-swizzled by row, which is the 128-byte swizzle of a tensor map), so that the tile leaves as
 // whole rows: one TMA store per warp (EPI_E4M3) or store instructions that cover four rows each.  EPI_E4M3 and
@@ -364,9 +363,15 @@ constexpr uint32_t ROPE_TAB_BYTES  = 32 * 512;
 constexpr uint32_t OFF_ROPE_W      = OFF_STG + 2 * ROPE_TAB_BYTES;  // 2 x 128 floats: query and key norm weights
 constexpr uint32_t SMEM_BYTES_ROPE = OFF_ROPE_W + 1024 + 1024;
 
+// EPI_SWIGLU: a warp's output tile is 32 rows x 64 bytes (2 KB, 16-byte chunks in the 64-byte swizzle of a tensor
+// map); its eight staging tiles lie behind the exchange buffer.
+constexpr uint32_t OFF_STG_SWIGLU    = OFF_BAR + 3072;
+constexpr uint32_t SMEM_BYTES_SWIGLU = OFF_STG_SWIGLU + 8 * 2048 + 1024;
+static_assert(OFF_XCH + 2048 <= OFF_STG_SWIGLU, "exchange buffer and staging tiles overlap");
+
 constexpr uint32_t smem_bytes_of(int epi)  // (the EPI_* constants: 2 swiglu, 4 rope)
 {
-  return epi == 4 ? SMEM_BYTES_ROPE : epi == 2 ? SMEM_BYTES : SMEM_BYTES_STAGED;
+  return epi == 4 ? SMEM_BYTES_ROPE : epi == 2 ? SMEM_BYTES_SWIGLU : SMEM_BYTES_STAGED;
 }
 constexpr uint32_t TMEM_COLS  = 512;  // two partial stages of 256 columns
 // split tiles (pair_walk.cuh): a slot holds 16 warp-sized units of 32 rows x 128 columns
@@ -492,7 +497,7 @@ template<int EPI>
 __global__ void __launch_bounds__(fp8pair::THREADS, 1)
   fp8_blockwise_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a,
                                  const __grid_constant__ CUtensorMap tm_b,
-                                 const __grid_constant__ CUtensorMap tm_c,  // C as rows of bytes, boxes of 32 rows x 128 bytes (not SWIGLU, GATHER)
+                                 const __grid_constant__ CUtensorMap tm_c,  // C as rows of bytes, boxes of 32 rows x 128 bytes (SWIGLU: 64; GATHER: unused)
                                  const float* __restrict__ A_s,
                                  const float* __restrict__ B_s,
                                  void* __restrict__ C_out,
@@ -544,7 +549,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
     fence_mbar_init();
     prefetch_tmap(&tm_a);
     prefetch_tmap(&tm_b);
-    if constexpr (EPI == EPI_E4M3 || EPI == EPI_ROPE || EPI == EPI_F32) {
+    if constexpr (EPI != EPI_GATHER) {
       prefetch_tmap(&tm_c);
     }
   }
@@ -979,10 +984,16 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
         xch[half * 128 + quarter * 32 + lane] = amax;
         asm volatile("bar.sync 1, 256;" ::: "memory");
         amax = fmaxf(amax, xch[(half ^ 1) * 128 + quarter * 32 + lane]);
-        if (m_ok && g_ok) {
+        // The warp's 32 x 64 output bytes go through a staging tile and leave as one TMA store (whole rows instead
+        // of 16-byte pieces in 32 rows per store instruction); all lanes take part, rows beyond M are clipped.
+        uint8_t* stg = smem + OFF_STG_SWIGLU + (warp - 4) * 2048;
+        if (lane == 0) {
+          tma_store_wait_read<0>();  // the store of the previous tile has read the staging tile
+        }
+        __syncwarp();
+        {
           const float scale     = __fdiv_rn(amax, 448.0f);
           const float scale_inv = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 0.0f;
-          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(C_out) + (size_t)m * N + (size_t)ng * 128 + half * 64);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             uint4 o;
@@ -990,11 +1001,17 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
             o.y    = pack_e4m3x4(acc[16 * i + 4] * scale_inv, acc[16 * i + 5] * scale_inv, acc[16 * i + 6] * scale_inv, acc[16 * i + 7] * scale_inv);
             o.z    = pack_e4m3x4(acc[16 * i + 8] * scale_inv, acc[16 * i + 9] * scale_inv, acc[16 * i + 10] * scale_inv, acc[16 * i + 11] * scale_inv);
             o.w    = pack_e4m3x4(acc[16 * i + 12] * scale_inv, acc[16 * i + 13] * scale_inv, acc[16 * i + 14] * scale_inv, acc[16 * i + 15] * scale_inv);
-            dst[i] = o;
+            *reinterpret_cast<uint4*>(stg + lane * 64 + ((i ^ ((lane >> 1) & 3)) << 4)) = o;
           }
-          if (half == 0) {
+          if (m_ok && g_ok && half == 0) {
             C_s[(size_t)ng * M + m] = scale;
           }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && g_ok && m - lane < M) {
+          tma_store_2d(&tm_c, stg, ng * 128 + half * 64, m - lane);
+          tma_store_commit();
         }
       }
       else if constexpr (EPI == EPI_E4M3 || EPI == EPI_GATHER || EPI == EPI_ROPE) {
@@ -1112,7 +1129,7 @@ __global__ void __launch_bounds__(fp8pair::THREADS, 1)
         PROF8_STAMP(6);
       }
     }
-    if constexpr (EPI == EPI_E4M3 || EPI == EPI_ROPE || EPI == EPI_F32) {
+    if constexpr (EPI != EPI_GATHER) {
       if (lane == 0) {
         tma_store_wait_read<0>();  // shared memory must outlive the last store's read of it
       }
@@ -1213,10 +1230,14 @@ static int launch_fp8_swiglu(const void*       A,
       || !make_tmap_2d(&tm_b, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)2 * I, (uint64_t)K, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B)) {
     return LLMMM_ERR_CUDA;
   }
+  CUtensorMap tm_h;  // H as [M, I] bytes, boxes of 32 rows x 64 bytes
+  if (!make_tmap_2d(&tm_h, H, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)I, (uint64_t)M, (uint64_t)I, 64, 32, CU_TENSOR_MAP_SWIZZLE_64B)) {
+    return LLMMM_ERR_CUDA;
+  }
   static thread_local bool attr_set[64] = {};
   if (!attr_set[info->device]) {
     LLMMM_CUDA_TRY(cudaFuncSetAttribute(
-      fp8_blockwise_gemm_pair_kernel<EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+      fp8_blockwise_gemm_pair_kernel<EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES_SWIGLU));
     attr_set[info->device] = true;
   }
   // a tile is 256 rows x 128 output columns (128 gate + 128 up weight rows); tiles are never cut along K here:
@@ -1225,8 +1246,8 @@ static int launch_fp8_swiglu(const void*       A,
   const int pairs = tiles < info->max_pairs ? tiles : info->max_pairs;
   float*    no_partials = nullptr;
   uint32_t* no_counters = nullptr;
-  LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<EPI_SWIGLU>, dim3(2 * pairs), dim3(THREADS), SMEM_BYTES, stream, 2,
-                            tm_a, tm_b, CUtensorMap{}, A_s, B_s, H, H_s, M, I, K, tiles, 0, 1, K / BK, no_partials, no_counters,
+  LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_pair_kernel<EPI_SWIGLU>, dim3(2 * pairs), dim3(THREADS), SMEM_BYTES_SWIGLU, stream, 2,
+                            tm_a, tm_b, tm_h, A_s, B_s, H, H_s, M, I, K, tiles, 0, 1, K / BK, no_partials, no_counters,
                             GatherDst{}, RopeHook{}, info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
@@ -1350,7 +1371,7 @@ int warm_fp8_kernels(const DeviceInfo* info)
   (void)info;
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_E4M3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES_STAGED));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES_STAGED));
-  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES));
+  LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES_SWIGLU));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES_STAGED));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_pair_kernel<EPI_ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8pair::SMEM_BYTES_ROPE));
   LLMMM_CUDA_TRY(cudaFuncSetAttribute(fp8_blockwise_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp8cfg::SMEM_BYTES));
