@@ -53,6 +53,7 @@ constexpr int      THREADS       = 256;  // warps 0-3: producer, three MMA issue
 constexpr int      EPI_WARP0     = 4;    // first promotion warp (setmaxnreg acts on whole warpgroups of 4 warps)
 constexpr int      REGS_CTRL     = 56;   // the control warpgroup gives up 72 of its 128 registers per thread ...
 constexpr int      REGS_EPI      = 200;  // ... and the promotion warpgroup takes them
+static_assert(128 * REGS_CTRL + 128 * REGS_EPI <= THREADS * 128, "setmaxnreg split exceeds the CTA's registers (128 per thread at launch)");
 constexpr uint32_t W_BYTES       = 128 * BK;
 constexpr int      MAX_CTAS      = 160;  // grid of the stream-K kernel: one CTA per SM, at most this many
 constexpr int      MAX_GROUPS    = 4096; // N <= 524288

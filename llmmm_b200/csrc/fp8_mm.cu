@@ -46,13 +46,18 @@ constexpr int      PROMO_WARPS = 8;
 constexpr int      THREADS    = 128 + PROMO_WARPS * 32;  // warpgroup 0: TMA / MMA; warpgroups 1-2: promotion
 constexpr int      REGS_CTRL  = 40;                      // register budget after setmaxnreg: control warpgroup
 constexpr int      REGS_PROMO = 232;                     //   and promotion warpgroups (128*40 + 256*232 = 384*168)
+// setmaxnreg moves registers inside the CTA's allocation (the 168 per thread ptxas reports for 384 threads); a
+// split that asks for more than that makes setmaxnreg.inc wait for ever
+static_assert(128 * REGS_CTRL + 256 * REGS_PROMO <= THREADS * 168, "setmaxnreg split exceeds the CTA's registers");
 constexpr uint32_t A_BYTES    = BM * BK;
 constexpr uint32_t B_BYTES    = BN * BK;
 constexpr uint32_t STAGE_TX   = A_BYTES + B_BYTES;
 constexpr uint32_t OFF_A      = 0;
 constexpr uint32_t OFF_B      = OFF_A + STAGES * A_BYTES;
 constexpr uint32_t OFF_BAR    = OFF_B + STAGES * B_BYTES;
-constexpr uint32_t SMEM_BYTES = OFF_BAR + 256 + 1024;
+constexpr uint32_t OFF_STG    = OFF_BAR + 1024;  // eight 4 KB staging tiles: a promotion warp's 32 rows x 128 output bytes
+constexpr uint32_t SMEM_BYTES = OFF_STG + 8 * 4096 + 1024;
+static_assert(SMEM_BYTES <= 232448, "ring + staging tiles exceed the shared memory of an SM");
 constexpr uint32_t TMEM_COLS  = 512;  // two partial stages of 256 columns
 }  // namespace fp8cfg
 
@@ -73,10 +78,45 @@ __device__ __forceinline__ void ffma2(float& d0, float& d1, uint32_t a0, uint32_
   d1 = __fmaf_rn(__uint_as_float(a1), sc, d1);
 }
 
+// largest magnitude of a thread's 128 accumulators, in four chains (one chain is 128 dependent instructions)
+__device__ __forceinline__ float amax128(const float (&acc)[128])
+{
+  float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+  for (int i = 0; i < 128; ++i) {
+    a[i & 3] = fmaxf(a[i & 3], fabsf(acc[i]));
+  }
+  return fmaxf(fmaxf(a[0], a[1]), fmaxf(a[2], a[3]));
+}
+
+// Shared-memory address of a generic pointer, computed where this stands (asm volatile is not hoisted above the
+// barrier waits of a loop in front of it).
+__device__ __forceinline__ uint32_t smem_u32_pinned(const void* p)
+{
+  uint32_t a;
+  asm volatile("{\n.reg .u64 t;\ncvta.to.shared.u64 t, %1;\ncvt.u32.u64 %0, t;\n}" : "=r"(a) : "l"(p));
+  return a;
+}
+
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w)
+{
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+
+// tma_store_2d with the source given as a shared-memory address
+__device__ __forceinline__ void tma_store_2d_from(const CUtensorMap* m, uint32_t src, int x, int y)
+{
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+
 // OUT_F32 = false: C_q e4m3 + C_s;  true: C fp32, no quantisation.
 template<bool OUT_F32>
 __global__ void __launch_bounds__(fp8cfg::THREADS, 1) fp8_blockwise_gemm_kernel(const __grid_constant__ CUtensorMap tm_a,
                                                                                 const __grid_constant__ CUtensorMap tm_b,
+                                                                                const __grid_constant__ CUtensorMap tm_c,  // e4m3 output: C as [M, N] bytes, boxes of 32 rows x 128
                                                                                 const float* __restrict__ A_s,
                                                                                 const float* __restrict__ B_s,
                                                                                 void* __restrict__ C_out,
@@ -114,6 +154,9 @@ __global__ void __launch_bounds__(fp8cfg::THREADS, 1) fp8_blockwise_gemm_kernel(
     fence_mbar_init();
     prefetch_tmap(&tm_a);
     prefetch_tmap(&tm_b);
+    if constexpr (!OUT_F32) {
+      prefetch_tmap(&tm_c);
+    }
   }
   if (warp == 1) {
     tmem_alloc<TMEM_COLS>(&bars->tmem_base);
@@ -261,35 +304,52 @@ __global__ void __launch_bounds__(fp8cfg::THREADS, 1) fp8_blockwise_gemm_kernel(
       }
       }
 
-      if (m_ok && g_ok) {
-        if constexpr (OUT_F32) {
+      // The warp's 32 output rows go through a 4 KB staging tile (16-byte chunks XOR-swizzled by row = the
+      // 128-byte swizzle of the tensor map) and leave as TMA stores of whole rows; written directly, every store
+      // instruction would touch 32 rows.  All lanes take part; rows beyond M are clipped by the tensor map.
+      // (the tile's shared-memory address is derived here from scratch: the K loop has no register to carry it)
+      const uint32_t stg      = ((smem_u32_pinned(smem_raw) + 1023u) & ~1023u) + OFF_STG + (uint32_t)(warp - 4) * 4096u;
+      const bool     store_ok = g_ok && m - lane < M;
+      (void)stg;
+      (void)store_ok;
+      if constexpr (OUT_F32) {
+        // (fp32 rows are written directly: the staged form of the pair kernel does not fit this kernel's registers)
+        if (m_ok && g_ok) {
           float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(C_out) + (size_t)m * N + (size_t)ng * 128);
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             dst[i] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
           }
         }
-        else {
-          float amax = 0.0f;
+      }
+      else {
+        const float amax      = amax128(acc);
+        const float scale     = __fdiv_rn(amax, 448.0f);
+        const float scale_inv = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 0.0f;
+        tma_store_wait_read<0>();  // lane 0: the store of the previous tile has read the staging tile
+        __syncwarp();
 #pragma unroll
-          for (int i = 0; i < 128; ++i) {
-            amax = fmaxf(amax, fabsf(acc[i]));
-          }
-          const float scale     = __fdiv_rn(amax, 448.0f);
-          const float scale_inv = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 0.0f;
-          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(C_out) + (size_t)m * N + (size_t)ng * 128);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            uint4 q;
-            q.x    = pack_e4m3x4(acc[16 * i + 0] * scale_inv, acc[16 * i + 1] * scale_inv, acc[16 * i + 2] * scale_inv, acc[16 * i + 3] * scale_inv);
-            q.y    = pack_e4m3x4(acc[16 * i + 4] * scale_inv, acc[16 * i + 5] * scale_inv, acc[16 * i + 6] * scale_inv, acc[16 * i + 7] * scale_inv);
-            q.z    = pack_e4m3x4(acc[16 * i + 8] * scale_inv, acc[16 * i + 9] * scale_inv, acc[16 * i + 10] * scale_inv, acc[16 * i + 11] * scale_inv);
-            q.w    = pack_e4m3x4(acc[16 * i + 12] * scale_inv, acc[16 * i + 13] * scale_inv, acc[16 * i + 14] * scale_inv, acc[16 * i + 15] * scale_inv);
-            dst[i] = q;
-          }
+        for (int i = 0; i < 8; ++i) {
+          uint4 q;
+          q.x = pack_e4m3x4(acc[16 * i + 0] * scale_inv, acc[16 * i + 1] * scale_inv, acc[16 * i + 2] * scale_inv, acc[16 * i + 3] * scale_inv);
+          q.y = pack_e4m3x4(acc[16 * i + 4] * scale_inv, acc[16 * i + 5] * scale_inv, acc[16 * i + 6] * scale_inv, acc[16 * i + 7] * scale_inv);
+          q.z = pack_e4m3x4(acc[16 * i + 8] * scale_inv, acc[16 * i + 9] * scale_inv, acc[16 * i + 10] * scale_inv, acc[16 * i + 11] * scale_inv);
+          q.w = pack_e4m3x4(acc[16 * i + 12] * scale_inv, acc[16 * i + 13] * scale_inv, acc[16 * i + 14] * scale_inv, acc[16 * i + 15] * scale_inv);
+          sts128(stg + lane * 128 + ((i ^ (lane & 7)) << 4), q.x, q.y, q.z, q.w);
+        }
+        if (m_ok && g_ok) {
           C_s[(size_t)ng * M + m] = scale;
         }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && store_ok) {
+          tma_store_2d_from(&tm_c, stg, ng * 128, m - lane);
+          tma_store_commit();
+        }
       }
+    }
+    if (!OUT_F32 && lane == 0) {
+      tma_store_wait_read<0>();  // shared memory must outlive the last store's read of it
     }
   }
 
@@ -340,6 +400,7 @@ constexpr int      STAGES     = 6;
 constexpr int      THREADS    = 384;
 constexpr int      REGS_CTRL  = 32;  // 32/232 compiles without spills; 40/232 spilt in the promotion loop (+35 % time)
 constexpr int      REGS_PROMO = 232;
+static_assert(128 * REGS_CTRL + 256 * REGS_PROMO <= THREADS * 168, "setmaxnreg split exceeds the CTA's registers");
 constexpr uint32_t A_BYTES    = 128 * BK;                 // 16 KB: this CTA's rows
 constexpr uint32_t B_BYTES    = 128 * BK;                 // 16 KB: this CTA's half of the tile's columns
 constexpr uint32_t STAGE_TX   = 2 * (A_BYTES + B_BYTES);  // both CTAs' loads land on the leader's barrier
@@ -461,17 +522,6 @@ __device__ __forceinline__ float4 ldg_pinned(const float4* p)
   float4 v;
   asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
   return v;
-}
-
-// largest magnitude of a thread's 128 accumulators, in four chains (one chain is 128 dependent instructions)
-__device__ __forceinline__ float amax128(const float (&acc)[128])
-{
-  float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-  for (int i = 0; i < 128; ++i) {
-    a[i & 3] = fmaxf(a[i & 3], fabsf(acc[i]));
-  }
-  return fmaxf(fmaxf(a[0], a[1]), fmaxf(a[2], a[3]));
 }
 
 // the same for shared memory
@@ -1312,6 +1362,10 @@ static int launch_fp8(const void*  A,
       || !make_tmap_2d(&tm_b, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K, (uint64_t)N, (uint64_t)K, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B)) {
     return LLMMM_ERR_CUDA;
   }
+  CUtensorMap tm_c = {};  // the e4m3 output as [M, N] bytes, boxes of 32 rows x 128 bytes
+  if (!OUT_F32 && !make_tmap_2d(&tm_c, C, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)N, (uint64_t)M, (uint64_t)N, 128, 32, CU_TENSOR_MAP_SWIZZLE_128B)) {
+    return LLMMM_ERR_CUDA;
+  }
   static thread_local bool attr_set[64] = {};
   if (!attr_set[info->device]) {
     LLMMM_CUDA_TRY(cudaFuncSetAttribute(
@@ -1323,7 +1377,7 @@ static int launch_fp8(const void*  A,
   const int tiles   = m_tiles * n_tiles;
   const int grid    = tiles < info->sm_count ? tiles : info->sm_count;
   LLMMM_CUDA_TRY(launch_pdl(fp8_blockwise_gemm_kernel<OUT_F32>, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, 1, tm_a, tm_b,
-                            A_s, B_s, C, C_s, M, N, K, info->status));
+                            tm_c, A_s, B_s, C, C_s, M, N, K, info->status));
   g_launches.fetch_add(1);
   return LLMMM_OK;
 }
