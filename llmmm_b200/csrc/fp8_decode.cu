@@ -49,11 +49,19 @@ namespace deccfg {
 constexpr int      BK            = 128;
 constexpr int      UMMA_K        = 32;
 constexpr int      MAX_STAGES    = 8;    // the ring depth depends on the activation tile, see DecodeSmem
-constexpr int      THREADS       = 256;  // warps 0-3: producer, three MMA issuers; warps 4-7: promotion
+// warps 0-3: producer, three MMA issuers; warps 4-7 (up to 32 activation columns) or 4-11 (64 columns): promotion.
+// With 64 columns one promotion warp per scheduler could not keep up with the weight stream (measured: ~600 ns per
+// K-block, all of it latency: shared-memory loads, the barrier, tensor-memory loads, 64 FMAs, one after the other
+// with nothing to overlap; HBM delivers a block every 364 ns): two warps per scheduler take 32 columns each.
 constexpr int      EPI_WARP0     = 4;    // first promotion warp (setmaxnreg acts on whole warpgroups of 4 warps)
-constexpr int      REGS_CTRL     = 56;   // the control warpgroup gives up 72 of its 128 registers per thread ...
-constexpr int      REGS_EPI      = 200;  // ... and the promotion warpgroup takes them
-static_assert(128 * REGS_CTRL + 128 * REGS_EPI <= THREADS * 128, "setmaxnreg split exceeds the CTA's registers (128 per thread at launch)");
+constexpr int      REGS_CTRL     = 56;   // the control warpgroup gives up registers ...
+constexpr int      REGS_EPI      = 200;  // ... and the promotion warpgroups take them
+__host__ __device__ constexpr int promo_warps(int mp) { return mp > 32 ? 8 : 4; }
+__host__ __device__ constexpr int threads(int mp) { return 128 + 32 * promo_warps(mp); }
+__host__ __device__ constexpr int ctas_per_sm(int mp) { return mp > 32 ? 1 : 2; }
+// registers per thread at launch: 128 with 256 threads and two CTAs per SM, 168 with 384 threads and one
+static_assert(128 * REGS_CTRL + 128 * REGS_EPI <= 256 * 128, "setmaxnreg split exceeds the CTA's registers");
+static_assert(128 * REGS_CTRL + 256 * REGS_EPI <= 384 * 168, "setmaxnreg split exceeds the CTA's registers");
 constexpr uint32_t W_BYTES       = 128 * BK;
 constexpr int      MAX_CTAS      = 160;  // grid of the stream-K kernel: one CTA per SM, at most this many
 constexpr int      MAX_GROUPS    = 4096; // N <= 524288
@@ -94,7 +102,7 @@ struct DecodeSmem {
 struct DecodeBars {
   uint64_t full[deccfg::MAX_STAGES];        // operands of the stage have landed
   uint64_t part_full[deccfg::MAX_STAGES];   // the K-block's MMAs are done: partial ready, operands consumed
-  uint64_t part_empty[deccfg::MAX_STAGES];  // the 4 promotion warps have copied the partial out
+  uint64_t part_empty[deccfg::MAX_STAGES];  // the promotion warps have copied the partial out
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t pad[2];
@@ -106,7 +114,7 @@ static_assert(sizeof(DecodeBars) <= 1536, "DecodeBars outgrew its slot in shared
 
 #ifdef LLMMM_PROFILE
 // Profiling build only: %globaltimer of every CTA at its phases (see llmmm_profile_dump_decode()).
-__device__ unsigned long long g_prof_cta[256][12];
+__device__ unsigned long long g_prof_cta[256][16];
 __device__ unsigned long long g_prof_kb[8][4];  // CTA 0, first promotion warp, K-blocks 0..7: waiting, partial seen, loaded, done
 #define PROF_KB(i)                                                                                                     \
   do {                                                                                                                 \
@@ -125,9 +133,10 @@ __device__ unsigned long long g_prof_kb[8][4];  // CTA 0, first promotion warp, 
 #define PROF_KB(i)
 #endif
 
+template<int NTHREADS>  // all promotion warps of the CTA
 __device__ __forceinline__ void epilogue_bar_sync()
 {
-  asm volatile("bar.sync 1, 128;" ::: "memory");
+  asm volatile("bar.sync 1, %0;" ::"n"(NTHREADS) : "memory");
 }
 
 // unit u of the (group, K-block) grid belongs to CTA ((u+1)*G - 1) / U, the
@@ -142,7 +151,7 @@ struct SplitGroup {
   int  nb;     // output group
   int  c_lo;   // first contributing CTA
   int  cnt;    // contributors
-  int  gw;     // this warp's index among the 4 * cnt promotion warps of the contributors
+  int  gw;     // this warp's index among the promotion warps of the contributors (4 or 8 per CTA)
   bool mine;   // this warp owns at least one row of the group
 };
 
@@ -240,8 +249,8 @@ __device__ __forceinline__ bool wait_contributors(const SplitGroup& g, const uin
   return true;
 }
 
-// Reduce-scatter step of one warp over NG (one or two) split groups at once.  Warp gw of a group's 4 * cnt warps
-// owns rows gw, gw + 4 cnt, ...; per pass it takes RB of its rows in each group and adds their partial tiles CB
+// Reduce-scatter step of one warp over NG (one or two) split groups at once.  Warp gw of a group's PW * cnt warps
+// (PW promotion warps per contributor) owns rows gw, gw + PW cnt, ...; per pass it takes RB of its rows in each group and adds their partial tiles CB
 // contributors at a time, ascending CTA order, four columns per lane (a warp reads one 512-byte row per load
 // instruction): NG * RB * CB loads are in flight together, so a pass costs one L2 round trip whatever the row
 // count, repeated (bounded) while a contributor's words have not landed yet.  Then the row's
@@ -259,6 +268,7 @@ __device__ __forceinline__ bool reduce_split_groups(const SplitGroup (&g)[NG],
 {
   // (no integer division anywhere in here: a 32-bit division is a dependent chain of ~150 clk, and a dozen of
   // them in a single warp's critical path cost more than the memory round trips)
+  constexpr int PW = deccfg::promo_warps(MP);
   int max_cnt = 0;
 #pragma unroll
   for (int k = 0; k < NG; ++k) {
@@ -269,7 +279,7 @@ __device__ __forceinline__ bool reduce_split_groups(const SplitGroup (&g)[NG],
     bool more = false;
 #pragma unroll
     for (int k = 0; k < NG; ++k) {
-      more = more || (g[k].mine && g[k].gw + pass * RB * 4 * g[k].cnt < M);
+      more = more || (g[k].mine && g[k].gw + pass * RB * PW * g[k].cnt < M);
     }
     if (!more) {
       break;
@@ -296,7 +306,7 @@ __device__ __forceinline__ bool reduce_split_groups(const SplitGroup (&g)[NG],
           const int  sl   = c * 2 + (jj == 0 ? 1 : 0);
 #pragma unroll
           for (int r = 0; r < RB; ++r) {
-            const int m  = g[k].gw + (pass * RB + r) * 4 * g[k].cnt;
+            const int m  = g[k].gw + (pass * RB + r) * PW * g[k].cnt;
             off[k][r][j] = (c_ok && m < M) ? (uint32_t)((sl * MP + m) * 128 + lane * 4) : NONE;
           }
         }
@@ -382,7 +392,7 @@ __device__ __forceinline__ bool reduce_split_groups(const SplitGroup (&g)[NG],
     for (int k = 0; k < NG; ++k) {
 #pragma unroll
       for (int r = 0; r < RB; ++r) {
-        const int m = g[k].gw + (pass * RB + r) * 4 * g[k].cnt;
+        const int m = g[k].gw + (pass * RB + r) * PW * g[k].cnt;
         if (!g[k].mine || m >= M) {
           continue;
         }
@@ -402,7 +412,7 @@ __device__ __forceinline__ bool reduce_split_groups(const SplitGroup (&g)[NG],
 //   one warp per row; a last cluster barrier keeps everybody until all copies are done.  No scratch, no atomics, no global round trips; used when
 //   the groups times a cluster size of 2-7 fill the GPU.
 template<int MP, bool OUT_F32, bool CLUSTER>
-__global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __grid_constant__ CUtensorMap tm_w,
+__global__ void __launch_bounds__(deccfg::threads(MP), deccfg::ctas_per_sm(MP)) fp8_decode_kernel(const __grid_constant__ CUtensorMap tm_w,
                                                                         const __grid_constant__ CUtensorMap tm_x,
                                                                         const float* __restrict__ A_s,
                                                                         const float* __restrict__ B_s,
@@ -467,7 +477,7 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
     for (int s = 0; s < L::STAGES; ++s) {
       mbar_init(&bars->full[s], 1);
       mbar_init(&bars->part_full[s], 1);
-      mbar_init(&bars->part_empty[s], 4);
+      mbar_init(&bars->part_empty[s], promo_warps(MP));
     }
     mbar_init(&bars->red, 1);
     bars->abort_flag = 0;
@@ -490,9 +500,8 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
   }
   PROF_CTA(1);
 
-  // With 64 activation columns a promotion thread holds 64 accumulators and a 64-value partial, and the
-  // reduction of split groups wants as many loads in flight as registers allow: the control warpgroup hands
-  // registers over (the 8 warps of each of two resident CTAs start with 128 per thread).
+  // The reduction of split groups wants as many loads in flight as registers allow: the control warpgroup hands
+  // registers over to the promotion warpgroups.
   if (warp < EPI_WARP0) {
     setmaxnreg_dec<REGS_CTRL>();
   }
@@ -594,26 +603,31 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
   }
   else {
     // ------------------------------------------- promotion + epilogue ----
+    constexpr int  PW      = promo_warps(MP);      // promotion warps
+    constexpr int  PT      = 32 * PW;              // promotion threads
+    constexpr int  MPH     = MP / (PW / 4);        // activation columns (= output rows) per thread
     const int      quarter = warp & 3;             // tensor-memory lane quarter this warp may read
-    const int      ew      = warp - EPI_WARP0;     // 0..3, index into bars->amax
+    const int      ew      = warp - EPI_WARP0;     // 0..PW-1
+    const int      row0    = (ew >> 2) * MPH;      // first output row this thread accumulates
     const int      n_local = quarter * 32 + lane;  // output column inside the group == TMEM lane
-    const int      et      = threadIdx.x - EPI_WARP0 * 32;  // 0..127
+    const int      et      = threadIdx.x - EPI_WARP0 * 32;  // 0..PT-1
     const uint32_t t_lane  = (uint32_t)(quarter * 32) << 16;
     uint32_t       it      = 0;
 
-    // Scale products of the run, CHUNK K-blocks at a time: thread `et` fetches elements et, et + 128, ... of
+    // Scale products of the run, CHUNK K-blocks at a time: thread `et` fetches elements et, et + PT, ... of
     // the [CHUNK][MP] chunk (A_s[kb, m] and B_s[nb, kb]: the latter is simply B_s[u] for unit u), multiplies
     // (one fp32 rounding of each scale product, as in the reference) and keeps them in registers until the
     // chunk before has been used up.  All loads of a chunk are in flight together; for runs of up to CHUNK
     // K-blocks there is exactly one L2 round trip, hidden behind the first operand tiles.
     constexpr int CH = L::CHUNK;
-    constexpr int SE = CH * MP / 128;  // elements per thread
+    constexpr int SE = CH * MP / PT;  // elements per thread
+    static_assert(SE * PT == CH * MP, "a chunk of scale products must divide among the promotion threads");
     float*        sc = reinterpret_cast<float*>(smem + L::OFF_SC);
     float         st[SE];
     auto fetch_chunk = [&](uint32_t chunk) {
 #pragma unroll
       for (int i = 0; i < SE; ++i) {
-        const uint32_t e   = (uint32_t)et + 128u * (uint32_t)i;
+        const uint32_t e   = (uint32_t)et + (uint32_t)PT * (uint32_t)i;
         const uint32_t itx = chunk * CH + e / MP;
         const int      m   = (int)(e % MP);
         float          v   = 0.0f;
@@ -627,12 +641,12 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
     auto store_chunk = [&]() {
 #pragma unroll
       for (int i = 0; i < SE; ++i) {
-        sc[et + 128 * i] = st[i];
+        sc[et + PT * i] = st[i];
       }
     };
     fetch_chunk(0);
     store_chunk();
-    epilogue_bar_sync();
+    epilogue_bar_sync<PT>();
     if (run > (uint32_t)CH) {
       fetch_chunk(1);
     }
@@ -653,9 +667,9 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
       const int      kb1  = (left < (uint32_t)(KB - kb0)) ? kb0 + (int)left : KB;
       const bool     whole = (kb0 == 0 && kb1 == KB);
 
-      float acc[MP];
+      float acc[MPH];  // output rows row0 .. row0 + MPH - 1 of column n_local
 #pragma unroll
-      for (int i = 0; i < MP; ++i) {
+      for (int i = 0; i < MPH; ++i) {
         acc[i] = 0.0f;
       }
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
@@ -663,9 +677,9 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
         const uint32_t pp = (it / L::STAGES) & 1;
         if (it != 0 && it % CH == 0) {
           // the next chunk's products are in `st`: swap them in once everybody is done with the old ones
-          epilogue_bar_sync();
+          epilogue_bar_sync<PT>();
           store_chunk();
-          epilogue_bar_sync();
+          epilogue_bar_sync<PT>();
           if ((it / CH + 1) * CH < run) {
             fetch_chunk(it / CH + 1);
           }
@@ -673,8 +687,8 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
         // One promotion warp has a scheduler to itself: nothing hides a shared-memory latency in front of every four
         // FMAs.  The scale products of the first half of the rows are therefore fetched before the wait for the
         // partial, those of the second half while the first half is being worked on.
-        constexpr int H4   = MP / 8;  // float4 values per half
-        const float4* srow = reinterpret_cast<const float4*>(sc + (it % CH) * MP);
+        constexpr int H4   = MPH / 8;  // float4 values per half
+        const float4* srow = reinterpret_cast<const float4*>(sc + (it % CH) * MP + row0);
         float4        s_lo[H4], s_hi[H4];
 #pragma unroll
         for (int i = 0; i < H4; ++i) {
@@ -686,10 +700,10 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
         tc_fence_after_sync();
         // the partial goes to registers and the stage is handed back as soon as its last column has been read,
         // before the arithmetic on it
-        uint32_t v[MP];
+        uint32_t v[MPH];
 #pragma unroll
-        for (int c = 0; c < MP / 16; ++c) {
-          tmem_ld_32x32b_x16(tmem_base + p * L::PART_COLS + t_lane + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&v[c * 16]));
+        for (int c = 0; c < MPH / 16; ++c) {
+          tmem_ld_32x32b_x16(tmem_base + p * L::PART_COLS + t_lane + row0 + c * 16, *reinterpret_cast<uint32_t(*)[16]>(&v[c * 16]));
         }
 #pragma unroll
         for (int i = 0; i < H4; ++i) {
@@ -737,9 +751,9 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
         const uint32_t my_row0 = c_rank * R;
         const uint32_t my_rows = (uint32_t)M > my_row0 ? min(R, (uint32_t)M - my_row0) : 0u;
 #pragma unroll
-        for (int i = 0; i < MP; ++i) {
-          if (i < M) {
-            stage[i * 128 + n_local] = acc[i];  // (this CTA's MMAs are all done: its ring is idle)
+        for (int i = 0; i < MPH; ++i) {
+          if (row0 + i < M) {
+            stage[(row0 + i) * 128 + n_local] = acc[i];  // (this CTA's MMAs are all done: its ring is idle)
           }
         }
         fence_proxy_async_smem();  // the bulk copies below read what was just written
@@ -768,7 +782,7 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
         if (ew == 0) {
           PROF_CTA(6);
         }
-        for (uint32_t q = (uint32_t)ew; q < my_rows; q += 4) {
+        for (uint32_t q = (uint32_t)ew; q < my_rows; q += (uint32_t)PW) {
           float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
           for (uint32_t rr = 0; rr < c_size; ++rr) {  // fixed order: the result does not depend on timing
             const float* src = rr == c_rank ? stage + (size_t)(my_row0 + q) * 128 : rcv + ((size_t)rr * R + q) * 128;
@@ -791,9 +805,9 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
         const int slot = blockIdx.x * 2 + (kb0 == 0 ? 1 : 0);  // run begins inside the group -> slot 0
         uint32_t* dst  = partials + (size_t)slot * (MP * 128);
 #pragma unroll
-        for (int i = 0; i < MP; ++i) {
-          if (i < M) {
-            st_partial(dst + i * 128 + n_local, acc[i]);
+        for (int i = 0; i < MPH; ++i) {
+          if (row0 + i < M) {
+            st_partial(dst + (row0 + i) * 128 + n_local, acc[i]);
           }
         }
         if (n_pend == 0) {
@@ -810,40 +824,49 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
         if constexpr (OUT_F32) {
           float* C = reinterpret_cast<float*>(C_out);
 #pragma unroll
-          for (int i = 0; i < MP; ++i) {
-            if (i < M) {
-              C[(size_t)i * N + n_glob] = acc[i];
+          for (int i = 0; i < MPH; ++i) {
+            if (row0 + i < M) {
+              C[(size_t)(row0 + i) * N + n_glob] = acc[i];
             }
           }
         }
         else {
           // group absmax over the 128 lanes: one warp-wide integer max per row (the bit pattern of a
-          // non-negative float orders like the float), then 4 warps through shared memory
+          // non-negative float orders like the float), then the 4 lane quarters through shared memory
 #pragma unroll
-          for (int i = 0; i < MP; ++i) {
-            if (i < M) {
+          for (int i = 0; i < MPH; ++i) {
+            if (row0 + i < M) {
               const uint32_t a = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(acc[i])));
               if (lane == 0) {
-                bars->amax[ew][i] = __uint_as_float(a);
+                bars->amax[quarter][row0 + i] = __uint_as_float(a);
               }
             }
           }
-          epilogue_bar_sync();
+          epilogue_bar_sync<PT>();
+          if (ew == 0) {
+            PROF_CTA(12);
+          }
           // thread i finishes row i's absmax and does the two divisions once for everybody
           if (et < M) {
             const float amax = fmaxf(fmaxf(bars->amax[0][et], bars->amax[1][et]), fmaxf(bars->amax[2][et], bars->amax[3][et]));
             bars->inv[et]    = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 0.0f;
             C_s[(size_t)nb * M + et] = __fdiv_rn(amax, 448.0f);
           }
-          epilogue_bar_sync();
+          epilogue_bar_sync<PT>();
+          if (ew == 0) {
+            PROF_CTA(13);
+          }
           uint8_t* C = reinterpret_cast<uint8_t*>(C_out);
 #pragma unroll
-          for (int i = 0; i < MP; ++i) {
-            if (i < M) {
-              C[(size_t)i * N + n_glob] = (uint8_t)__nv_cvt_float_to_fp8(acc[i] * bars->inv[i], __NV_SATFINITE, __NV_E4M3);
+          for (int i = 0; i < MPH; ++i) {
+            if (row0 + i < M) {
+              C[(size_t)(row0 + i) * N + n_glob] = (uint8_t)__nv_cvt_float_to_fp8(acc[i] * bars->inv[row0 + i], __NV_SATFINITE, __NV_E4M3);
             }
           }
-          epilogue_bar_sync();  // bars->amax and bars->inv are reused by the next segment
+          epilogue_bar_sync<PT>();  // bars->amax and bars->inv are reused by the next segment
+          if (ew == 0) {
+            PROF_CTA(14);
+          }
         }
       }
     }
@@ -851,8 +874,8 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
 
     if constexpr (!CLUSTER) {
       // ------------------------------------------- reduce-scatter of the split groups ----
-      // Group nb was cut among CTAs c_lo..c_hi.  Its M rows are dealt out to the 4 * (c_hi - c_lo + 1) promotion
-      // warps of those CTAs: warp w of contributor j takes rows 4 j + w, 4 j + w + 4 cnt, ...  A warp reads
+      // Group nb was cut among CTAs c_lo..c_hi.  Its M rows are dealt out to the PW * (c_hi - c_lo + 1) promotion
+      // warps of those CTAs: warp w of contributor j takes rows PW j + w, PW j + w + PW cnt, ...  A warp reads
       // (bounded) until the words of every contributor have landed -- all CTAs of the grid are resident, the
       // grid is never larger than the SM count -- and reduces its rows of both groups this CTA took part in
       // (reduce_split_groups).
@@ -874,7 +897,7 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
           g[k].nb   = k == 0 ? pend_nb0 : pend_nb1;
           g[k].c_lo = (int)__shfl_sync(0xffffffffu, q, 2 * k);
           g[k].cnt  = (int)__shfl_sync(0xffffffffu, q, 2 * k + 1) - g[k].c_lo + 1;
-          g[k].gw   = 4 * ((int)blockIdx.x - g[k].c_lo) + ew;
+          g[k].gw   = PW * ((int)blockIdx.x - g[k].c_lo) + ew;
           g[k].mine = k < n_pend && g[k].gw < M;  // more warps than rows: some have none
           if (g[k].mine) {
             max_cnt = max(max_cnt, g[k].cnt);
@@ -927,9 +950,11 @@ __global__ void __launch_bounds__(deccfg::THREADS, 2) fp8_decode_kernel(const __
 // Profiling build only (python -m llmmm_b200.build --profile): prints the phase stamps of the last decode launch.
 extern "C" void llmmm_profile_dump_decode()
 {
-  static const char* names[11] = {"entry", "released", "first operands", "MMAs issued", "promotion done", "published",
-                                  "first poll back", "rows reduced", "roles done", "TMEM freed", "first batch in"};
-  static unsigned long long c[256][12];
+  // (slot 11 is a count, printed below; 12-14: the last in-place finish of a whole group)
+  static const char* names[15] = {"entry", "released", "first operands", "MMAs issued", "promotion done", "published",
+                                  "first poll back", "rows reduced", "roles done", "TMEM freed", "first batch in", "",
+                                  "row maxima met", "scales ready", "group stored"};
+  static unsigned long long c[256][16];
   cudaMemcpyFromSymbol(c, g_prof_cta, sizeof(c));
   unsigned long long t0 = ~0ull, rel = ~0ull;
   int                n  = 0;
@@ -946,7 +971,10 @@ extern "C" void llmmm_profile_dump_decode()
     return;
   }
   printf("decode launch, %d CTAs; ns after the first release (min / mean / max over CTAs):\n", n);
-  for (int k = 0; k < 11; ++k) {
+  for (int k = 0; k < 15; ++k) {
+    if (k == 11) {
+      continue;
+    }
     double             sum = 0;
     long long          mn = 1ll << 62, mx = -(1ll << 62);
     int                cnt = 0;
@@ -991,7 +1019,7 @@ extern "C" void llmmm_profile_dump_decode()
     static unsigned long long zkb[8][4];
     cudaMemcpyToSymbol(g_prof_kb, zkb, sizeof(zkb));
   }
-  static unsigned long long zero[256][12];
+  static unsigned long long zero[256][16];
   cudaMemcpyToSymbol(g_prof_cta, zero, sizeof(zero));
 }
 #endif
@@ -1098,7 +1126,7 @@ static int launch_decode_t(const void*       A,
   if ((long long)G > U) {
     G = (int)U;
   }
-  LLMMM_CUDA_TRY(launch_pdl(fp8_decode_kernel<MP, OUT_F32, false>, dim3((unsigned)G), dim3(THREADS), L::SMEM_BYTES, stream,
+  LLMMM_CUDA_TRY(launch_pdl(fp8_decode_kernel<MP, OUT_F32, false>, dim3((unsigned)G), dim3(threads(MP)), L::SMEM_BYTES, stream,
                             1, tm_w, tm_x, A_s, B_s, C, C_s, M, N, K, partials, g_static_weights.load(),
                             info->status));
   g_launches.fetch_add(1);
@@ -1133,7 +1161,7 @@ static int launch_decode_cluster_t(const void*       A,
     attr_set[info->device] = true;
   }
   uint32_t* no_partials = nullptr;
-  LLMMM_CUDA_TRY(launch_pdl(fp8_decode_kernel<MP, OUT_F32, true>, dim3((unsigned)((N / 128) * cluster)), dim3(THREADS),
+  LLMMM_CUDA_TRY(launch_pdl(fp8_decode_kernel<MP, OUT_F32, true>, dim3((unsigned)((N / 128) * cluster)), dim3(threads(MP)),
                             L::SMEM_BYTES, stream, (unsigned)cluster, tm_w, tm_x, A_s, B_s, C, C_s, M, N, K, no_partials,
                             g_static_weights.load(), info->status));
   g_launches.fetch_add(1);
@@ -1152,7 +1180,7 @@ int cluster_capacity_t(const DeviceInfo* info, int size)
       == cudaSuccess) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim            = dim3((unsigned)(size * (info->sm_count / size)));
-    cfg.blockDim           = dim3(deccfg::THREADS);
+    cfg.blockDim           = dim3(deccfg::threads(MP));
     cfg.dynamicSmemBytes   = L::SMEM_BYTES;
     cudaLaunchAttribute attr[1];
     attr[0].id               = cudaLaunchAttributeClusterDimension;
