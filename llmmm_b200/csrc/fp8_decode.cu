@@ -49,16 +49,18 @@ namespace deccfg {
 constexpr int      BK            = 128;
 constexpr int      UMMA_K        = 32;
 constexpr int      MAX_STAGES    = 8;    // the ring depth depends on the activation tile, see DecodeSmem
-// warps 0-3: producer, three MMA issuers; warps 4-7 (up to 32 activation columns) or 4-11 (64 columns): promotion.
+// warps 0-3: producer, three MMA issuers; warps 4-7 (up to 16 activation columns) or 4-11 (32, 64 columns): promotion.
 // With 64 columns one promotion warp per scheduler could not keep up with the weight stream (measured: ~600 ns per
 // K-block, all of it latency: shared-memory loads, the barrier, tensor-memory loads, 64 FMAs, one after the other
-// with nothing to overlap; HBM delivers a block every 364 ns): two warps per scheduler take 32 columns each.
+// with nothing to overlap; HBM delivers a block every 364 ns): two warps per scheduler take half of the columns
+// each (M = 64: 9.8 / 8.2 / 22.2 / 12.0 -> 7.6 / 6.9 / 17.0 / 9.6 us on the four Qwen3-4B shapes; M = 32, together
+// with an SM to itself and eight stages: 7.8 / 6.5 / 17.1 / 9.5 -> 6.6 / 5.5 / 14.7 / 8.0 us).
 constexpr int      EPI_WARP0     = 4;    // first promotion warp (setmaxnreg acts on whole warpgroups of 4 warps)
 constexpr int      REGS_CTRL     = 56;   // the control warpgroup gives up registers ...
 constexpr int      REGS_EPI      = 200;  // ... and the promotion warpgroups take them
-__host__ __device__ constexpr int promo_warps(int mp) { return mp > 32 ? 8 : 4; }
+__host__ __device__ constexpr int promo_warps(int mp) { return mp > 16 ? 8 : 4; }
 __host__ __device__ constexpr int threads(int mp) { return 128 + 32 * promo_warps(mp); }
-__host__ __device__ constexpr int ctas_per_sm(int mp) { return mp > 32 ? 1 : 2; }
+__host__ __device__ constexpr int ctas_per_sm(int mp) { return mp > 16 ? 1 : 2; }
 // registers per thread at launch: 128 with 256 threads and two CTAs per SM, 168 with 384 threads and one
 static_assert(128 * REGS_CTRL + 128 * REGS_EPI <= 256 * 128, "setmaxnreg split exceeds the CTA's registers");
 static_assert(128 * REGS_CTRL + 256 * REGS_EPI <= 384 * 168, "setmaxnreg split exceeds the CTA's registers");
@@ -70,11 +72,11 @@ constexpr int      MAX_GROUPS    = 4096; // N <= 524288
 template<int MP>
 struct DecodeSmem {
   static constexpr uint32_t X_BYTES    = MP * deccfg::BK;
-  // Up to 32 activation columns: as deep a ring as lets two CTAs share an SM (113 KB each; tensor memory: 256
+  // Up to 16 activation columns: as deep a ring as lets two CTAs share an SM (113 KB each; tensor memory: 256
   // columns each): the next kernel of a launch chain then sets up, and requests static weights, beside the
-  // running one.  With 64 columns a stage is 24 KB and only four would fit that way; measured, an SM to itself and
-  // eight stages is faster there (cluster shapes 9.9 / 8.2 / 12.1 us against 11.8 / 9.3 / 14.2 us at M = 64).
-  static constexpr int      STAGES     = MP <= 16 ? 6 : (MP <= 32 ? 5 : 8);
+  // running one.  With 32 or 64 columns a stage is 20 or 24 KB; measured, an SM to itself and eight stages is
+  // faster there (cluster shapes 9.9 / 8.2 / 12.1 us against 11.8 / 9.3 / 14.2 us at M = 64).
+  static constexpr int      STAGES     = MP <= 16 ? 6 : 8;
   // K-block `it` uses ring stage it % STAGES and the tensor-memory partial stage of the same index, so ONE
   // tcgen05.commit per K-block tells both the promotion warps (partial ready) and the producer (operands
   // consumed); a second commit would cost the single issuing thread another ~150 clk per K-block.
@@ -94,7 +96,7 @@ struct DecodeSmem {
   // at least 80 KB, so that never more than two CTAs share an SM: a third one would sit in tcgen05.alloc until
   // tensor memory is freed
   static constexpr uint32_t USED_BYTES = OFF_SC + SC_BYTES + 1024;
-  static_assert(MP > 32 || 2 * (USED_BYTES + 1024) <= 228 * 1024, "two CTAs of consecutive launches must fit on one SM");
+  static_assert(MP > 16 || 2 * (USED_BYTES + 1024) <= 228 * 1024, "two CTAs of consecutive launches must fit on one SM");
   static_assert(USED_BYTES <= 227 * 1024, "shared memory of one CTA");
   static constexpr uint32_t SMEM_BYTES = USED_BYTES > 80 * 1024 ? USED_BYTES : 80 * 1024;
 };
