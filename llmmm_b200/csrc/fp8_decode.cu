@@ -10,27 +10,31 @@
 //     activation rows are the narrow N side (16, 32 or 64 columns), so TMEM
 //     lane = output column n and TMEM column = output row m;
 //   * stream-K: all SMs stream the same number of weight blocks whatever N is:
-//     the (N/128 x K/128) grid of weight blocks is cut into one contiguous run
-//     per CTA; a run crosses output groups, giving "segments" (with 64
-//     activation columns and more groups than CTAs, every CTA first takes
-//     floor(groups / CTAs) whole groups and only the left-over groups are cut);
+//     the (N/128 x K/128) grid of weight blocks is cut into contiguous runs, one
+//     or two per CTA; a run crosses output groups, giving "segments".  With at
+//     least as many groups as CTAs every CTA takes floor(groups / CTAs) whole
+//     groups, and only the left-over groups are cut evenly among the CTAs,
+//     which work on those cut pieces FIRST;
 //   * warp 0 streams weight blocks (and the matching activation slab) through
-//     a 4-6-deep TMA ring; warps 1-3 take turns issuing the MMAs of a K-block
+//     a 6-8-deep TMA ring; warps 1-3 take turns issuing the MMAs of a K-block
 //     (four per K-block, from zero, into the tensor-memory partial stage of the
 //     ring slot): a thread that issues four MMAs and a commit is held for about
 //     640 clk whatever their width, so one thread alone could not keep up with
-//     the ring; warps 4-7 promote
+//     the ring; the promotion warps (4, or 8 for 32 and 64 columns) promote
 //     with acc = fma(partial, A_s*B_s, acc) in registers, the scale products of
 //     a whole run staged through shared memory ahead of time (a load per
 //     K-block would put an L2 round trip into every iteration);
 //   * a segment that covers a group's whole K range is finished in place;
 //     otherwise its fp32 partial goes to the caller's scratch buffer as
-//     self-announcing words (zero = not there yet), and the rows of the output group are shared out
-//     among the contributors' warps (a reduce-scatter: one warp polls one
-//     row's words of every contributor, adds them in fixed CTA order, takes the
-//     absmax, quantises and stores the row), so results do not depend on timing,
-//     no single CTA reads every partial tile, and the exchange costs one store
-//     and one load latency instead of store + fence + atomic + poll + load;
+//     self-announcing words (zero = not there yet), and the rows of the output
+//     group are shared out among the contributors' REDUCTION warps, a fourth
+//     warpgroup of the stream-K kernel that works beside the promotion warps (a
+//     reduce-scatter: one warp reads one row's words of every contributor, adds
+//     them in fixed CTA order, takes the absmax, quantises and stores the row),
+//     so results do not depend on timing, no single CTA reads every partial
+//     tile, the exchange costs one store and one load latency instead of store
+//     + fence + atomic + poll + load, and when whole groups follow the cut
+//     pieces that latency passes while the CTA is still streaming;
 //   * the 1x128 output group runs across the 128 lanes in this orientation:
 //     for a whole segment the group absmax is a warp-shuffle reduction plus a
 //     4-entry exchange in shared memory between the four warps.
@@ -57,13 +61,22 @@ constexpr int      MAX_STAGES    = 8;    // the ring depth depends on the activa
 // with an SM to itself and eight stages: 7.8 / 6.5 / 17.1 / 9.5 -> 6.6 / 5.5 / 14.7 / 8.0 us).
 constexpr int      EPI_WARP0     = 4;    // first promotion warp (setmaxnreg acts on whole warpgroups of 4 warps)
 constexpr int      REGS_CTRL     = 56;   // the control warpgroup gives up registers ...
-constexpr int      REGS_EPI      = 200;  // ... and the promotion warpgroups take them
+constexpr int      REGS_EPI      = 200;  // ... and the promotion and reduction warpgroups take them
 __host__ __device__ constexpr int promo_warps(int mp) { return mp > 16 ? 8 : 4; }
-__host__ __device__ constexpr int threads(int mp) { return 128 + 32 * promo_warps(mp); }
-__host__ __device__ constexpr int ctas_per_sm(int mp) { return mp > 16 ? 1 : 2; }
-// registers per thread at launch: 128 with 256 threads and two CTAs per SM, 168 with 384 threads and one
-static_assert(128 * REGS_CTRL + 128 * REGS_EPI <= 256 * 128, "setmaxnreg split exceeds the CTA's registers");
-static_assert(128 * REGS_CTRL + 256 * REGS_EPI <= 384 * 168, "setmaxnreg split exceeds the CTA's registers");
+// The stream-K kernel has one more warpgroup: it adds up the partial tiles of the output groups that were cut
+// among CTAs while the promotion warps are still streaming (see the kernel).  The cluster kernel has none.
+__host__ __device__ constexpr int reduce_warps(bool cluster) { return cluster ? 0 : 4; }
+__host__ __device__ constexpr int threads(int mp, bool cluster) { return 128 + 32 * (promo_warps(mp) + reduce_warps(cluster)); }
+__host__ __device__ constexpr int ctas_per_sm(int mp, bool cluster) { return (mp <= 16 && cluster) ? 2 : 1; }
+// With 512 threads (stream-K, 32 or 64 columns) a thread starts with 128 registers and the promotion warps keep
+// them; everywhere else they take REGS_EPI.
+__host__ __device__ constexpr bool promo_keeps_regs(int mp, bool cluster) { return mp > 16 && !cluster; }
+// registers per thread at launch (what ptxas reports): 128 with 256 threads and two CTAs per SM, 168 with 384
+// threads, 128 with 512; setmaxnreg moves registers inside that allocation and waits for ever if it cannot
+static_assert(128 * REGS_CTRL + 128 * REGS_EPI <= 256 * 128, "cluster kernel, 16 columns");
+static_assert(128 * REGS_CTRL + 256 * REGS_EPI <= 384 * 168, "cluster kernel, 32 / 64 columns");
+static_assert(128 * REGS_CTRL + 128 * REGS_EPI + 128 * REGS_EPI <= 384 * 168, "stream-K kernel, 16 columns");
+static_assert(128 * REGS_CTRL + 256 * 128 + 128 * REGS_EPI <= 512 * 128, "stream-K kernel, 32 / 64 columns");
 constexpr uint32_t W_BYTES       = 128 * BK;
 constexpr int      MAX_CTAS      = 160;  // grid of the stream-K kernel: one CTA per SM, at most this many
 constexpr int      MAX_GROUPS    = 4096; // N <= 524288
@@ -232,6 +245,7 @@ __device__ __forceinline__ bool wait_contributors(const SplitGroup& g, const uin
       if (__all_sync(0xffffffffu, w != 0u)) {
         break;
       }
+      __nanosleep(200);  // the words may be a whole stream away: leave the memory system to the weights
       if ((++spins & 0x7) == 0) {
         if (*abort_flag) {
           return false;
@@ -270,7 +284,7 @@ __device__ __forceinline__ bool reduce_split_groups(const SplitGroup (&g)[NG],
 {
   // (no integer division anywhere in here: a 32-bit division is a dependent chain of ~150 clk, and a dozen of
   // them in a single warp's critical path cost more than the memory round trips)
-  constexpr int PW = deccfg::promo_warps(MP);
+  constexpr int PW = deccfg::reduce_warps(false);  // warps per contributor that take part
   int max_cnt = 0;
 #pragma unroll
   for (int k = 0; k < NG; ++k) {
@@ -343,13 +357,13 @@ __device__ __forceinline__ bool reduce_split_groups(const SplitGroup (&g)[NG],
           }
         }
 #ifdef LLMMM_PROFILE
-        if (threadIdx.x == deccfg::EPI_WARP0 * 32 && pass == 0 && cb == 0 && spins == 0) {
+        if (threadIdx.x == (deccfg::EPI_WARP0 + deccfg::promo_warps(MP)) * 32 && pass == 0 && cb == 0 && spins == 0) {
           g_prof_cta[blockIdx.x][6] = global_timer_ns();  // first poll has returned
         }
 #endif
         if (__all_sync(0xffffffffu, landed)) {
 #ifdef LLMMM_PROFILE
-          if (threadIdx.x == deccfg::EPI_WARP0 * 32 && pass == 0 && cb == 0) {
+          if (threadIdx.x == (deccfg::EPI_WARP0 + deccfg::promo_warps(MP)) * 32 && pass == 0 && cb == 0) {
             g_prof_cta[blockIdx.x][10] = global_timer_ns();  // first batch complete
             g_prof_cta[blockIdx.x][11] = spins + 1;          // polls it took (a count, not a time)
           }
@@ -414,7 +428,7 @@ __device__ __forceinline__ bool reduce_split_groups(const SplitGroup (&g)[NG],
 //   one warp per row; a last cluster barrier keeps everybody until all copies are done.  No scratch, no atomics, no global round trips; used when
 //   the groups times a cluster size of 2-7 fill the GPU.
 template<int MP, bool OUT_F32, bool CLUSTER>
-__global__ void __launch_bounds__(deccfg::threads(MP), deccfg::ctas_per_sm(MP)) fp8_decode_kernel(const __grid_constant__ CUtensorMap tm_w,
+__global__ void __launch_bounds__(deccfg::threads(MP, CLUSTER), deccfg::ctas_per_sm(MP, CLUSTER)) fp8_decode_kernel(const __grid_constant__ CUtensorMap tm_w,
                                                                         const __grid_constant__ CUtensorMap tm_x,
                                                                         const float* __restrict__ A_s,
                                                                         const float* __restrict__ B_s,
@@ -442,11 +456,11 @@ __global__ void __launch_bounds__(deccfg::threads(MP), deccfg::ctas_per_sm(MP)) 
   const uint32_t  U       = (uint32_t)(N / 128) * (uint32_t)KB;  // the launcher keeps U * 256 below 2^31
   const uint32_t  G       = gridDim.x;
   uint32_t        c_size  = 1, c_rank = 0, red_rows = MP;  // (cluster kernel: rows of the group a CTA owns, at most)
-  // A CTA works through two ranges of units, [u_begin, u_end) and then [v_begin, v_end).  Stream-K kernel with 64
-  // activation columns and more output groups than CTAs: every CTA takes floor(groups / G) whole groups (the second
-  // range, finished in place), and only the groups that are left over are cut evenly among the CTAs (the first range, so that their
-  // partial tiles have long landed when the CTA comes to reduce them at its end); otherwise (fewer groups than CTAs,
-  // or narrower activation tiles) everything is "left over".  Cluster kernel: one slice of one group, no second range.
+  // A CTA works through two ranges of units, [u_begin, u_end) and then [v_begin, v_end).  Stream-K kernel with at
+  // least as many output groups as CTAs: every CTA takes floor(groups / G) whole groups (the second range, finished
+  // in place), and only the groups that are left over are cut evenly among the CTAs (the first range: their partial
+  // tiles are published early and added up by the reduction warps while the second range streams); with fewer groups
+  // than CTAs everything is "left over".  Cluster kernel: one slice of one group, no second range.
   uint32_t        u_begin, u_end, v_begin = 0, v_end = 0;
   // the units that are cut: [tail_base, tail_base + tail_units), among the first tail_ctas CTAs (all of them, unless
   // there are fewer such units than CTAs: every CTA that takes part gets at least one)
@@ -460,10 +474,7 @@ __global__ void __launch_bounds__(deccfg::threads(MP), deccfg::ctas_per_sm(MP)) 
     u_end   = group * (uint32_t)KB + ((c_rank + 1) * (uint32_t)KB) / c_size;
   }
   else {
-    // (measured on 19456 x 2560: whole groups + cut left-overs 22.7 us against 24.4 us for cutting everything at
-    // M = 64, where a cut group costs 64 rows of reduction; but 16.3 against 12.7 us at M <= 16, where the 20
-    // one-block contributors of a left-over group cost more than two or three contributors of every group)
-    const uint32_t whole_units = MP > 32 ? ((uint32_t)(N / 128) / G) * (uint32_t)KB : 0u;  // per CTA
+    const uint32_t whole_units = ((uint32_t)(N / 128) / G) * (uint32_t)KB;  // per CTA
     tail_base  = G * whole_units;
     tail_units = U - tail_base;
     v_begin    = blockIdx.x * whole_units;
@@ -507,7 +518,7 @@ __global__ void __launch_bounds__(deccfg::threads(MP), deccfg::ctas_per_sm(MP)) 
   if (warp < EPI_WARP0) {
     setmaxnreg_dec<REGS_CTRL>();
   }
-  else {
+  else if (warp >= EPI_WARP0 + promo_warps(MP) || !promo_keeps_regs(MP, CLUSTER)) {
     setmaxnreg_inc<REGS_EPI>();
   }
   if (warp == 0) {
@@ -603,7 +614,7 @@ __global__ void __launch_bounds__(deccfg::threads(MP), deccfg::ctas_per_sm(MP)) 
       cluster_sync_all();
     }
   }
-  else {
+  else if (warp < EPI_WARP0 + promo_warps(MP)) {
     // ------------------------------------------- promotion + epilogue ----
     constexpr int  PW      = promo_warps(MP);      // promotion warps
     constexpr int  PT      = 32 * PW;              // promotion threads
@@ -652,10 +663,6 @@ __global__ void __launch_bounds__(deccfg::threads(MP), deccfg::ctas_per_sm(MP)) 
     if (run > (uint32_t)CH) {
       fetch_chunk(1);
     }
-
-    // groups this CTA contributed a partial tile to (at most the first and the last segment of its run)
-    int pend_nb0 = 0, pend_nb1 = 0;
-    int n_pend = 0;
 
     for (int range = 0; range < (CLUSTER ? 1 : 2); ++range) {
     uint32_t       u     = range == 0 ? u_begin : v_begin;
@@ -803,7 +810,7 @@ __global__ void __launch_bounds__(deccfg::threads(MP), deccfg::ctas_per_sm(MP)) 
         finish = false;
       }
       else if (!whole) {
-        // publish this CTA's partial tile as flagged words; the reduction follows after the whole run
+        // publish this CTA's partial tile as flagged words; the reduction warps take it from there
         const int slot = blockIdx.x * 2 + (kb0 == 0 ? 1 : 0);  // run begins inside the group -> slot 0
         uint32_t* dst  = partials + (size_t)slot * (MP * 128);
 #pragma unroll
@@ -812,13 +819,6 @@ __global__ void __launch_bounds__(deccfg::threads(MP), deccfg::ctas_per_sm(MP)) 
             st_partial(dst + (row0 + i) * 128 + n_local, acc[i]);
           }
         }
-        if (n_pend == 0) {
-          pend_nb0 = nb;
-        }
-        else {
-          pend_nb1 = nb;
-        }
-        ++n_pend;
       }
 
       if (finish) {
@@ -874,15 +874,46 @@ __global__ void __launch_bounds__(deccfg::threads(MP), deccfg::ctas_per_sm(MP)) 
     }
     }  // range
 
+    if (ew == 0) {
+      PROF_CTA(8);
+    }
+  }
+  else {
+    // ------------------------------------------- reduce-scatter of the split groups ----
+    // (stream-K kernel only.)  The output groups that were cut among CTAs are added up by a warpgroup of their own,
+    // beside the promotion warps: a CTA's cut segments lie in its first range, so their partial tiles are
+    // published early, and when whole groups follow (second range) the sums are finished long before the CTA's
+    // stream ends; otherwise these warps wait, politely (one word per contributor, with a pause between polls),
+    // for the other contributors to get there.
+    // Group nb was cut among CTAs c_lo..c_hi.  Its M rows are dealt out to the RW * (c_hi - c_lo + 1) reduction
+    // warps of those CTAs: warp w of contributor j takes rows RW j + w, RW j + w + RW cnt, ...  A warp reads
+    // (bounded) until the words of every contributor have landed -- all CTAs of the grid are resident, the
+    // grid is never larger than the SM count -- and reduces its rows of both groups this CTA took part in
+    // (reduce_split_groups).
     if constexpr (!CLUSTER) {
-      // ------------------------------------------- reduce-scatter of the split groups ----
-      // Group nb was cut among CTAs c_lo..c_hi.  Its M rows are dealt out to the PW * (c_hi - c_lo + 1) promotion
-      // warps of those CTAs: warp w of contributor j takes rows PW j + w, PW j + w + PW cnt, ...  A warp reads
-      // (bounded) until the words of every contributor have landed -- all CTAs of the grid are resident, the
-      // grid is never larger than the SM count -- and reduces its rows of both groups this CTA took part in
-      // (reduce_split_groups).
+      constexpr int RW = reduce_warps(false);
+      const int     rw = warp - EPI_WARP0 - promo_warps(MP);  // 0..RW-1
+      // the cut segments of this CTA's first range: at most its first and its last one
+      int pend_nb0 = 0, pend_nb1 = 0;
+      int n_pend = 0;
+      for (uint32_t u = u_begin; u < u_end;) {
+        const int      nb   = (int)(u / (uint32_t)KB);
+        const int      kb0  = (int)(u % (uint32_t)KB);
+        const uint32_t left = u_end - u;
+        const int      kb1  = (left < (uint32_t)(KB - kb0)) ? kb0 + (int)left : KB;
+        if (!(kb0 == 0 && kb1 == KB)) {
+          if (n_pend == 0) {
+            pend_nb0 = nb;
+          }
+          else {
+            pend_nb1 = nb;
+          }
+          ++n_pend;
+        }
+        u += (uint32_t)(kb1 - kb0);
+      }
       if (n_pend > 0) {
-        if (ew == 0) {
+        if (rw == 0) {
           PROF_CTA(5);
         }
         // first and last contributor of both groups: four divisions, one per lane
@@ -899,15 +930,20 @@ __global__ void __launch_bounds__(deccfg::threads(MP), deccfg::ctas_per_sm(MP)) 
           g[k].nb   = k == 0 ? pend_nb0 : pend_nb1;
           g[k].c_lo = (int)__shfl_sync(0xffffffffu, q, 2 * k);
           g[k].cnt  = (int)__shfl_sync(0xffffffffu, q, 2 * k + 1) - g[k].c_lo + 1;
-          g[k].gw   = PW * ((int)blockIdx.x - g[k].c_lo) + ew;
+          g[k].gw   = RW * ((int)blockIdx.x - g[k].c_lo) + rw;
           g[k].mine = k < n_pend && g[k].gw < M;  // more warps than rows: some have none
           if (g[k].mine) {
             max_cnt = max(max_cnt, g[k].cnt);
           }
         }
-        // (measured: taking one group after the other with eight rows per pass, for M > 32, was slower than
-        // several passes over both groups: 29.6 against 25.5 us for 64 x 19456 x 2560)
-        if (g[0].mine || g[1].mine) {
+        bool alive = true;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          if (alive && g[k].mine) {
+            alive = wait_contributors<MP>(g[k], partials, lane, abort_flag, status);
+          }
+        }
+        if (alive && (g[0].mine || g[1].mine)) {
           if (max_cnt <= 2) {
             reduce_split_groups<MP, OUT_F32, 2, 4, 2>(g, partials, C_out, C_s, M, N, lane, abort_flag, status);
           }
@@ -929,13 +965,10 @@ __global__ void __launch_bounds__(deccfg::threads(MP), deccfg::ctas_per_sm(MP)) 
             }
           }
         }
-        if (ew == 0) {
+        if (rw == 0) {
           PROF_CTA(7);
         }
       }
-    }
-    if (ew == 0) {
-      PROF_CTA(8);
     }
   }
 
@@ -1128,7 +1161,7 @@ static int launch_decode_t(const void*       A,
   if ((long long)G > U) {
     G = (int)U;
   }
-  LLMMM_CUDA_TRY(launch_pdl(fp8_decode_kernel<MP, OUT_F32, false>, dim3((unsigned)G), dim3(threads(MP)), L::SMEM_BYTES, stream,
+  LLMMM_CUDA_TRY(launch_pdl(fp8_decode_kernel<MP, OUT_F32, false>, dim3((unsigned)G), dim3(threads(MP, false)), L::SMEM_BYTES, stream,
                             1, tm_w, tm_x, A_s, B_s, C, C_s, M, N, K, partials, g_static_weights.load(),
                             info->status));
   g_launches.fetch_add(1);
@@ -1163,7 +1196,7 @@ static int launch_decode_cluster_t(const void*       A,
     attr_set[info->device] = true;
   }
   uint32_t* no_partials = nullptr;
-  LLMMM_CUDA_TRY(launch_pdl(fp8_decode_kernel<MP, OUT_F32, true>, dim3((unsigned)((N / 128) * cluster)), dim3(threads(MP)),
+  LLMMM_CUDA_TRY(launch_pdl(fp8_decode_kernel<MP, OUT_F32, true>, dim3((unsigned)((N / 128) * cluster)), dim3(threads(MP, true)),
                             L::SMEM_BYTES, stream, (unsigned)cluster, tm_w, tm_x, A_s, B_s, C, C_s, M, N, K, no_partials,
                             g_static_weights.load(), info->status));
   g_launches.fetch_add(1);
@@ -1182,7 +1215,7 @@ int cluster_capacity_t(const DeviceInfo* info, int size)
       == cudaSuccess) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim            = dim3((unsigned)(size * (info->sm_count / size)));
-    cfg.blockDim           = dim3(deccfg::threads(MP));
+    cfg.blockDim           = dim3(deccfg::threads(MP, true));
     cfg.dynamicSmemBytes   = L::SMEM_BYTES;
     cudaLaunchAttribute attr[1];
     attr[0].id               = cudaLaunchAttributeClusterDimension;
@@ -1288,11 +1321,11 @@ bool describe_decode_plan(const DeviceInfo* info, int M, int N, int K, char* buf
   const long long U = (long long)(N / 128) * (K / 128);
   long long       G = info->sm_count < deccfg::MAX_CTAS ? info->sm_count : deccfg::MAX_CTAS;
   G                 = G < U ? G : U;
-  const long long whole = mp > 32 ? (N / 128) / G : 0;  // whole output groups per CTA
+  const long long whole = (N / 128) / G;              // whole output groups per CTA
   const long long cut   = (N / 128) - whole * G;      // groups cut evenly among all CTAs
   snprintf(buf, len, "fp8_decode_kernel<%d, stream-K>: %lld weight blocks of 128x128 over %lld CTAs (%.1f each): %lld whole output "
            "group(s) per CTA finished in place, %lld group(s) cut evenly among all CTAs, their partial tiles through the registered "
-           "scratch and their rows reduced by the contributors' warps (choice: %s)", mp, U, G, (double)U / (double)G, whole, cut, how);
+           "scratch and their rows added up by the contributors' reduction warps beside the stream (choice: %s)", mp, U, G, (double)U / (double)G, whole, cut, how);
   return true;
 }
 
