@@ -41,22 +41,37 @@ def test_tune_then_first_call_and_descriptions(capi, cuda):
 
 
 def _time_decode(capi, cuda, M, N, K, copies=24, reps=5):
-    """Median microseconds per launch over weight copies that together exceed L2."""
+    """Median microseconds per launch over weight copies that together exceed L2.  The launches are replayed from
+    a CUDA graph: issued one by one from Python these kernels (5-10 us) would be timed by the host's launch path,
+    which differs between a cluster launch and a plain one, not by the GPU."""
     xq = torch.randint(0, 120, (M, K), dtype=torch.uint8, device=cuda)
     xs = torch.rand(K // 128, M, device=cuda)
     ws = [(torch.randint(0, 120, (N, K), dtype=torch.uint8, device=cuda), torch.rand(N // 128, K // 128, device=cuda))
           for _ in range(copies)]
     cq = torch.empty(M, N, dtype=torch.uint8, device=cuda)
     cs = torch.empty(N // 128, M, device=cuda)
-    times = []
-    for _ in range(reps + 1):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
+
+    def chain():
         for w in ws:
             capi.fp8_blockwise_mm(xq, xs, w[0], w[1], cq, cs, M, N, K)
-        e1.record()
+
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    times = []
+    with torch.cuda.stream(stream):
+        chain()
         torch.cuda.synchronize()
-        times.append(e0.elapsed_time(e1) * 1e3 / copies)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            chain()
+        for _ in range(reps + 1):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e3 / copies)
+    torch.cuda.current_stream().wait_stream(stream)
     return sorted(times[1:])[len(times[1:]) // 2], cq, cs
 
 
