@@ -67,16 +67,23 @@ __host__ __device__ constexpr int promo_warps(int mp) { return mp > 16 ? 8 : 4; 
 // among CTAs while the promotion warps are still streaming (see the kernel).  The cluster kernel has none.
 __host__ __device__ constexpr int reduce_warps(bool cluster) { return cluster ? 0 : 4; }
 __host__ __device__ constexpr int threads(int mp, bool cluster) { return 128 + 32 * (promo_warps(mp) + reduce_warps(cluster)); }
-__host__ __device__ constexpr int ctas_per_sm(int mp, bool cluster) { return (mp <= 16 && cluster) ? 2 : 1; }
-// With 512 threads (stream-K, 32 or 64 columns) a thread starts with 128 registers and the promotion warps keep
-// them; everywhere else they take REGS_EPI.
-__host__ __device__ constexpr bool promo_keeps_regs(int mp, bool cluster) { return mp > 16 && !cluster; }
-// registers per thread at launch (what ptxas reports): 128 with 256 threads and two CTAs per SM, 168 with 384
-// threads, 128 with 512; setmaxnreg moves registers inside that allocation and waits for ever if it cannot
-static_assert(128 * REGS_CTRL + 128 * REGS_EPI <= 256 * 128, "cluster kernel, 16 columns");
-static_assert(128 * REGS_CTRL + 256 * REGS_EPI <= 384 * 168, "cluster kernel, 32 / 64 columns");
-static_assert(128 * REGS_CTRL + 128 * REGS_EPI + 128 * REGS_EPI <= 384 * 168, "stream-K kernel, 16 columns");
-static_assert(128 * REGS_CTRL + 256 * 128 + 128 * REGS_EPI <= 512 * 128, "stream-K kernel, 32 / 64 columns");
+// Up to 16 activation columns a CTA takes half an SM (shared memory, tensor memory, registers), so that the
+// kernels before and after it in a launch chain are resident beside it: set up, waiting for their turn, or
+// finishing.  (Measured on a Qwen3-4B MLP block of four launches: 23.5 us; with the stream-K kernel on a whole SM
+// 26.7 us, although that kernel alone was no slower.)
+__host__ __device__ constexpr int ctas_per_sm(int mp, bool cluster) { return mp <= 16 ? 2 : 1; }
+// Registers per thread after setmaxnreg, by kernel form.  What a thread starts with (ptxas reports it): 128 with
+// 256 threads and two CTAs per SM, 80 with 384 threads and two CTAs, 168 with 384 threads and one, 128 with 512;
+// setmaxnreg moves registers inside the CTA's allocation and waits for ever if it asks for more.
+//   cluster kernel                 : control 56, promotion 200
+//   stream-K, 16 columns (2 / SM)  : control 56, promotion 88, reduction 96   (384 x 80 = 30720)
+//   stream-K, 32 / 64 columns      : control 56, promotion 128 (as launched), reduction 200   (512 x 128 = 65536)
+__host__ __device__ constexpr int regs_promo(int mp, bool cluster) { return cluster ? REGS_EPI : (mp <= 16 ? 88 : 128); }
+__host__ __device__ constexpr int regs_reduce(int mp) { return mp <= 16 ? 96 : REGS_EPI; }
+static_assert(128 * REGS_CTRL + 128 * regs_promo(16, true) <= 256 * 128, "cluster kernel, 16 columns");
+static_assert(128 * REGS_CTRL + 256 * regs_promo(64, true) <= 384 * 168, "cluster kernel, 32 / 64 columns");
+static_assert(128 * REGS_CTRL + 128 * regs_promo(16, false) + 128 * regs_reduce(16) <= 384 * 80, "stream-K kernel, 16 columns");
+static_assert(128 * REGS_CTRL + 256 * regs_promo(64, false) + 128 * regs_reduce(64) <= 512 * 128, "stream-K kernel, 32 / 64 columns");
 constexpr uint32_t W_BYTES       = 128 * BK;
 constexpr int      MAX_CTAS      = 160;  // grid of the stream-K kernel: one CTA per SM, at most this many
 constexpr int      MAX_GROUPS    = 4096; // N <= 524288
@@ -518,8 +525,13 @@ __global__ void __launch_bounds__(deccfg::threads(MP, CLUSTER), deccfg::ctas_per
   if (warp < EPI_WARP0) {
     setmaxnreg_dec<REGS_CTRL>();
   }
-  else if (warp >= EPI_WARP0 + promo_warps(MP) || !promo_keeps_regs(MP, CLUSTER)) {
-    setmaxnreg_inc<REGS_EPI>();
+  else if (warp < EPI_WARP0 + promo_warps(MP)) {
+    if constexpr (CLUSTER || MP <= 16) {  // (the other form keeps the 128 registers it was launched with)
+      setmaxnreg_inc<regs_promo(MP, CLUSTER)>();
+    }
+  }
+  else {
+    setmaxnreg_inc<regs_reduce(MP)>();
   }
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer --
@@ -944,7 +956,25 @@ __global__ void __launch_bounds__(deccfg::threads(MP, CLUSTER), deccfg::ctas_per
           }
         }
         if (alive && (g[0].mine || g[1].mine)) {
-          if (max_cnt <= 2) {
+          if constexpr (MP <= 16) {
+            // (96 registers per thread: eight partial rows of 16 bytes per lane in flight)
+            if (max_cnt <= 2) {
+              reduce_split_groups<MP, OUT_F32, 2, 2, 2>(g, partials, C_out, C_s, M, N, lane, abort_flag, status);
+            }
+            else if (max_cnt <= 4) {
+              reduce_split_groups<MP, OUT_F32, 2, 1, 4>(g, partials, C_out, C_s, M, N, lane, abort_flag, status);
+            }
+            else {
+#pragma unroll
+              for (int k = 0; k < 2; ++k) {
+                if (g[k].mine) {
+                  const SplitGroup one[1] = {g[k]};
+                  reduce_split_groups<MP, OUT_F32, 1, 1, 8>(one, partials, C_out, C_s, M, N, lane, abort_flag, status);
+                }
+              }
+            }
+          }
+          else if (max_cnt <= 2) {
             reduce_split_groups<MP, OUT_F32, 2, 4, 2>(g, partials, C_out, C_s, M, N, lane, abort_flag, status);
           }
           else if (max_cnt <= 4) {
