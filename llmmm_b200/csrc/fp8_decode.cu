@@ -69,8 +69,8 @@ __host__ __device__ constexpr int reduce_warps(bool cluster) { return cluster ? 
 __host__ __device__ constexpr int threads(int mp, bool cluster) { return 128 + 32 * (promo_warps(mp) + reduce_warps(cluster)); }
 // Up to 16 activation columns a CTA takes half an SM (shared memory, tensor memory, registers), so that the
 // kernels before and after it in a launch chain are resident beside it: set up, waiting for their turn, or
-// finishing.  (Measured on a Qwen3-4B MLP block of four launches: 23.5 us; with the stream-K kernel on a whole SM
-// 26.7 us, although that kernel alone was no slower.)
+// finishing.  (Measured on a Qwen3-4B MLP block of four launches at M = 1: 22.7 us; with the stream-K kernel on a
+// whole SM 25.8 us, although that kernel alone is faster that way, 11.1 against 12.1 us.)
 __host__ __device__ constexpr int ctas_per_sm(int mp, bool cluster) { return mp <= 16 ? 2 : 1; }
 // Registers per thread after setmaxnreg, by kernel form.  What a thread starts with (ptxas reports it): 128 with
 // 256 threads and two CTAs per SM, 80 with 384 threads and two CTAs, 168 with 384 threads and one, 128 with 512;
