@@ -27,7 +27,11 @@
 //     fetched one block ahead;
 //   * after the last K-block the same threads reduce their 128 values to the
 //     group absmax (thread-local: no shuffles in this orientation), convert to
-//     e4m3 and store one 128-byte line each, plus the coalesced scale column.
+//     e4m3 and write their 128 bytes into the warp's 4 KB staging tile in
+//     shared memory (128-byte swizzle), which one lane hands to a TMA store:
+//     the tile leaves as whole rows (a thread storing its own row would make
+//     every store instruction of the warp touch 32 rows); the scale column is
+//     stored directly, it is coalesced.
 #include <cuda_fp8.h>
 
 #include "host_common.h"
