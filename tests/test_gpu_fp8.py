@@ -83,8 +83,11 @@ def test_general_kernel_small_shapes(capi, oracle, cuda, shape):
 
 
 @pytest.mark.parametrize("M", [1, 2, 15, 16, 17, 33, 64])
-@pytest.mark.parametrize("NK", [(256, 1024), (384, 128), (2560, 4096), (19072, 256), (37888, 128)])
+@pytest.mark.parametrize("NK", [(256, 1024), (384, 128), (2560, 4096), (19072, 256), (37888, 128), (25600, 512)])
 def test_decode_kernel_ragged_m(capi, oracle, cuda, M, NK):
+    """Among the shapes: 149 groups x 2 K-blocks (one whole group per CTA plus one left-over group cut in two),
+    296 groups x 1 (two whole groups per CTA, nothing cut), 200 groups x 4 (one whole group per CTA and 52
+    left-over groups cut into pieces of one or two K-blocks that cross group boundaries)."""
     N, K = NK
     case = make_case(oracle, 41 + M, M, N, K)
     gq, gs, gf = gpu_mm(capi, cuda, *case)
